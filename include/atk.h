@@ -1,0 +1,156 @@
+/*
+ * atk.h — C ABI of libatk.so, the sm_100a implementation of bucketed approximate
+ * top-k (stage 1: per-bucket top-j; stage 2: exact select over the candidates).
+ *
+ * This is the boundary a host binding uses in place of the reference's
+ * JIT-compiled pybind module.  Every function is plain `extern "C"`, takes raw
+ * device (or, where stated, host) pointers and sizes, launches on the stream it
+ * is given, never allocates device memory (the caller owns all buffers and the
+ * workspace), never synchronises unless stated, never throws and never aborts:
+ * it returns ATK_OK (0) or a negative ATK_ERR_* code.  All entry points are
+ * re-entrant and may be called concurrently from several host threads on
+ * different streams.  The device the pointers live on must be current.
+ *
+ * Reference interfaces replaced (paths inside the reference project):
+ *   approx_topk/priority_queue_approx_topk.cu:378-387,523-525  PriorityQueueTopK (pybind)
+ *   approx_topk/priority_queue.py:85-88                        stage 2 (torch.topk + gather)
+ *   approx_topk/experimental/bucketed_argmax.py:18-42,145-202  topk_torch / topk_triton
+ *   approx_topk/cuda_extensions.py:12-27                       JIT loader (now: dlopen of this library)
+ */
+#ifndef ATK_H_
+#define ATK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types of the input / value output. */
+enum { ATK_F32 = 0, ATK_F16 = 1, ATK_BF16 = 2 };
+
+/* Status codes.  The Python host maps them to the exception types the
+ * reference raises for the same condition. */
+enum {
+  ATK_OK = 0,
+  ATK_ERR_BAD_J = -1,        /* j outside 1..4            (reference .cu:425-435) */
+  ATK_ERR_J_DIVIDES_K = -2,  /* k0 % j != 0               (reference .cu:402)     */
+  ATK_ERR_K_TOO_LARGE = -3,  /* k0 > n                    (reference .cu:329-330) */
+  ATK_ERR_BAD_DTYPE = -4,
+  ATK_ERR_BAD_ARG = -5,      /* null pointer, negative size, k_mult < 1, k > k0 ... */
+  ATK_ERR_WORKSPACE = -6,    /* workspace missing or smaller than *_workspace_bytes */
+  ATK_ERR_TOO_LARGE = -7,    /* a size exceeds what the kernels index (see each function) */
+  ATK_ERR_CUDA = -8          /* a CUDA runtime call failed; see cudaGetLastError */
+};
+
+/* Library version, major*10000 + minor*100 + patch. */
+int atk_version(void);
+
+/* Static, human-readable text for a status code. */
+const char* atk_strerror(int status);
+
+/* Compute-capability check: returns ATK_OK when the current device can run the
+ * kernels in this library (sm_100), ATK_ERR_CUDA otherwise. */
+int atk_device_supported(void);
+
+/*
+ * Stage 1 — per-bucket top-j.  Replaces PriorityQueueTopK
+ * (priority_queue_approx_topk.cu:378-521) with largest = true.
+ *
+ *   x              rows x n elements of `dtype`, row r at x + r*row_stride (elements)
+ *   k0             number of candidates per row, k0 = j * buckets; needs k0 % j == 0, k0 <= n
+ *   interleaved    1: bucket c = {c, c+b, c+2b, ...};  0: contiguous segments whose
+ *                  sizes differ by at most one, larger ones first (.cu:25-56)
+ *   mode           -1 auto / 0 / 1 — the reference's multithread_buckets switch.
+ *                  Accepted for signature parity; one kernel family serves all modes.
+ *   out_vals       rows x k0 of `dtype`, row r at out_vals + r*out_row_stride
+ *   out_idx        rows x k0 int64 positions along the row, same layout
+ *
+ * Slot layout and tie rule are the reference's thread-per-bucket kernel's:
+ * bucket c owns slots c*j .. c*j+j-1 in ascending (value, index) order, and of
+ * equal values the later position wins (.cu:58-79,190-200).  Unlike the
+ * reference the queue starts at -inf, so -inf inputs are selectable and every
+ * output slot is a real element.
+ * k0 == 0 is a no-op.  Limits: n / buckets < 2^31.
+ */
+int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
+               int64_t k0, int j, int interleaved, int mode,
+               void* out_vals, int64_t* out_idx, int64_t out_row_stride, void* stream);
+
+/*
+ * Stage 1 over a column slab of one long interleaved row that is sharded over
+ * several GPUs (no counterpart in the reference, which is single-GPU; needed
+ * for the bucket-group sharding of a single long row).  `slab` is a dense
+ * stripes x cols array holding columns [col_offset, col_offset+cols) of the
+ * stripes x total_buckets view of the row; every bucket here has exactly
+ * `stripes` elements.  Writes cols*j candidates whose indices are positions in
+ * the full row: stripe*total_buckets + col_offset + col.
+ */
+int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols,
+                    int64_t total_buckets, int64_t col_offset, int j,
+                    void* out_vals, int64_t* out_idx, void* stream);
+
+/*
+ * Stage 2 — exact top-k of k0 candidates per row, indices carried along.
+ * Replaces torch.topk(sorted=False) + gather (priority_queue.py:85-88).
+ * Output order is unspecified but deterministic; of equal values at the k-th
+ * boundary the lowest candidate slots are kept.
+ * workspace: atk_select_workspace_bytes() bytes of device memory, 256-byte
+ * aligned, contents irrelevant on entry (may be NULL when that returns 0).
+ */
+size_t atk_select_workspace_bytes(int dtype, int64_t rows, int64_t k0, int64_t k);
+int atk_select(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_t rows,
+               int64_t k0, int64_t cand_row_stride, int64_t k,
+               void* out_vals, int64_t* out_idx, int64_t out_row_stride,
+               void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The whole operator approx_topk.topk(x, k, dim=-1, j, k_mult, interleaved)
+ * (priority_queue.py:14-88): stage 1 with k0 = k*k_mult and, when k_mult > 1,
+ * the exact select.  Candidates stay on chip when one thread block can own a
+ * row's candidates; otherwise they pass through the workspace.
+ */
+size_t atk_topk_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j,
+                                int64_t k_mult);
+int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
+             int64_t k, int j, int64_t k_mult, int interleaved, int mode,
+             void* out_vals, int64_t* out_idx, int64_t out_row_stride,
+             void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * k_b = 1 bucketed arg-max with the conventions of
+ * experimental/bucketed_argmax.py (topk_torch :18-42, Triton kernels :70-142):
+ * k buckets, rows padded to a multiple of k with the dtype's lowest value,
+ * contiguous buckets are fixed chunks of ceil(n/k), the FIRST maximum wins a
+ * tie, outputs in bucket order.  k may exceed n (all-padding buckets return
+ * the lowest value and the first padded position).
+ */
+int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
+                        int64_t k, int interleaved,
+                        void* out_vals, int64_t* out_idx, int64_t out_row_stride, void* stream);
+
+/*
+ * Host-buffer form of atk_topk: x_host / out_*_host are HOST pointers (pinned
+ * memory gives full PCIe speed, pageable memory works).  Rows are processed in
+ * chunks so that the upload of chunk i+1, the kernels of chunk i and the
+ * download of chunk i-1 overlap.  `device_scratch` is caller-allocated device
+ * memory of atk_topk_host_scratch_bytes() bytes.  Creates two internal streams
+ * per call, synchronises before returning.  chunk_rows <= 0 picks a default.
+ */
+size_t atk_topk_host_scratch_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j,
+                                   int64_t k_mult, int64_t chunk_rows);
+int atk_topk_host(const void* x_host, int dtype, int64_t rows, int64_t n, int64_t row_stride,
+                  int64_t k, int j, int64_t k_mult, int interleaved,
+                  void* out_vals_host, int64_t* out_idx_host,
+                  void* device_scratch, size_t scratch_bytes, int64_t chunk_rows);
+
+/* Number of kernel launches issued by this library on the calling thread since
+ * the last atk_reset_launch_count(); benchmarks use it to report launches. */
+int64_t atk_launch_count(void);
+void atk_reset_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATK_H_ */

@@ -1,0 +1,359 @@
+// C ABI of libatk.so: argument validation, dispatch to the kernel launchers and
+// the host-buffer pipeline.  See include/atk.h for the contract of every entry
+// point and the reference interface each one replaces.
+#include <atomic>
+
+#include "atk_contig.cuh"
+#include "atk_select.cuh"
+#include "atk_sweep.cuh"
+
+namespace atk {
+
+static thread_local long long g_launches = 0;
+void note_launch(int n) { g_launches += n; }
+
+namespace {
+
+int elem_size(int dtype) {
+  switch (dtype) {
+    case ATK_F32: return 4;
+    case ATK_F16: return 2;
+    case ATK_BF16: return 2;
+    default: return 0;
+  }
+}
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+// Lazily cached SM count per device (the only global state of the library).
+int sm_count_of_current_device() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < 64) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0 && dev < 64) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+int sweep_dispatch(const SweepLaunch& a, int dtype) {
+  switch (dtype) {
+    case ATK_F32: return launch_sweep_f32(a);
+    case ATK_F16: return launch_sweep_f16(a);
+    case ATK_BF16: return launch_sweep_bf16(a);
+    default: return ATK_ERR_BAD_DTYPE;
+  }
+}
+
+int check_common(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
+                 const void* out_vals, const void* out_idx, int64_t out_row_stride) {
+  if (elem_size(dtype) == 0) return ATK_ERR_BAD_DTYPE;
+  if (rows < 0 || n < 0 || row_stride < 0 || out_row_stride < 0) return ATK_ERR_BAD_ARG;
+  if (rows > 0 && n > 0 && (x == nullptr || out_vals == nullptr || out_idx == nullptr)) return ATK_ERR_BAD_ARG;
+  return ATK_OK;
+}
+
+}  // namespace
+}  // namespace atk
+
+using namespace atk;
+
+extern "C" {
+
+int atk_version(void) { return 10000; }
+
+const char* atk_strerror(int status) {
+  switch (status) {
+    case ATK_OK: return "ok";
+    case ATK_ERR_BAD_J: return "topk: j must 0 < j < 5";
+    case ATK_ERR_J_DIVIDES_K: return "topk: j must divide k";
+    case ATK_ERR_K_TOO_LARGE: return "topk: k must not be larger than topk size";
+    case ATK_ERR_BAD_DTYPE: return "topk: unsupported dtype (float32, float16 and bfloat16 are supported)";
+    case ATK_ERR_BAD_ARG: return "topk: invalid argument";
+    case ATK_ERR_WORKSPACE: return "topk: workspace missing or too small";
+    case ATK_ERR_TOO_LARGE: return "topk: problem size exceeds the kernel's index range";
+    case ATK_ERR_CUDA: return "topk: CUDA runtime error";
+    default: return "topk: unknown status";
+  }
+}
+
+int atk_device_supported(void) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return ATK_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return ATK_ERR_CUDA;
+  return major == 10 ? ATK_OK : ATK_ERR_CUDA;
+}
+
+int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k0,
+               int j, int interleaved, int mode, void* out_vals, int64_t* out_idx,
+               int64_t out_row_stride, void* stream) {
+  (void)mode;
+  int rc = check_common(x, dtype, rows, n, row_stride, out_vals, out_idx, out_row_stride);
+  if (rc != ATK_OK) return rc;
+  if (k0 < 0) return ATK_ERR_BAD_ARG;
+  if (k0 == 0 || rows == 0) return ATK_OK;
+  if (j < 1 || j > 4) return ATK_ERR_BAD_J;
+  if (k0 % j != 0) return ATK_ERR_J_DIVIDES_K;
+  if (k0 > n) return ATK_ERR_K_TOO_LARGE;
+  const int64_t b = k0 / j;
+  if (interleaved) {
+    SweepLaunch a;
+    a.x = x;
+    a.out_vals = out_vals;
+    a.out_idx = reinterpret_cast<long long*>(out_idx);
+    a.rows = rows;
+    a.n = n;
+    a.row_stride = row_stride;
+    a.out_row_stride = out_row_stride;
+    a.b = b;
+    a.stripe_stride = b;
+    a.idx_stride = b;
+    a.idx_offset = 0;
+    a.j = j;
+    a.first_wins = false;
+    a.sm_count = sm_count_of_current_device();
+    a.stream = static_cast<cudaStream_t>(stream);
+    return sweep_dispatch(a, dtype);
+  }
+  ContigLaunch c;
+  c.x = x;
+  c.out_vals = out_vals;
+  c.out_idx = reinterpret_cast<long long*>(out_idx);
+  c.rows = rows;
+  c.n = n;
+  c.row_stride = row_stride;
+  c.out_row_stride = out_row_stride;
+  c.b = b;
+  c.j = j;
+  c.first_wins = false;
+  c.fixed_chunks = false;
+  c.stream = static_cast<cudaStream_t>(stream);
+  return launch_contig(c, dtype);
+}
+
+int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols, int64_t total_buckets,
+                    int64_t col_offset, int j, void* out_vals, int64_t* out_idx, void* stream) {
+  if (elem_size(dtype) == 0) return ATK_ERR_BAD_DTYPE;
+  if (stripes < 0 || cols < 0 || total_buckets < cols || col_offset < 0) return ATK_ERR_BAD_ARG;
+  if (stripes == 0 || cols == 0) return ATK_OK;
+  if (slab == nullptr || out_vals == nullptr || out_idx == nullptr) return ATK_ERR_BAD_ARG;
+  if (j < 1 || j > 4) return ATK_ERR_BAD_J;
+  if (j > stripes) return ATK_ERR_K_TOO_LARGE;
+  SweepLaunch a;
+  a.x = slab;
+  a.out_vals = out_vals;
+  a.out_idx = reinterpret_cast<long long*>(out_idx);
+  a.rows = 1;
+  a.n = stripes * cols;
+  a.row_stride = stripes * cols;
+  a.out_row_stride = cols * j;
+  a.b = cols;
+  a.stripe_stride = cols;
+  a.idx_stride = total_buckets;
+  a.idx_offset = col_offset;
+  a.j = j;
+  a.first_wins = false;
+  a.sm_count = sm_count_of_current_device();
+  a.stream = static_cast<cudaStream_t>(stream);
+  return sweep_dispatch(a, dtype);
+}
+
+size_t atk_select_workspace_bytes(int dtype, int64_t rows, int64_t k0, int64_t k) {
+  (void)k;
+  if (rows <= 0 || k0 <= 0) return 0;
+  return select_workspace_bytes(dtype, rows, k0);
+}
+
+int atk_select(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_t rows, int64_t k0,
+               int64_t cand_row_stride, int64_t k, void* out_vals, int64_t* out_idx,
+               int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  if (elem_size(dtype) == 0) return ATK_ERR_BAD_DTYPE;
+  if (rows < 0 || k0 < 0 || k < 0 || k > k0 || cand_row_stride < 0 || out_row_stride < 0) return ATK_ERR_BAD_ARG;
+  if (rows == 0 || k == 0) return ATK_OK;
+  if (cand_vals == nullptr || cand_idx == nullptr || out_vals == nullptr || out_idx == nullptr) return ATK_ERR_BAD_ARG;
+  SelectLaunch a;
+  a.cand_vals = cand_vals;
+  a.cand_idx = reinterpret_cast<const long long*>(cand_idx);
+  a.rows = rows;
+  a.k0 = k0;
+  a.cand_row_stride = cand_row_stride;
+  a.k = k;
+  a.out_vals = out_vals;
+  a.out_idx = reinterpret_cast<long long*>(out_idx);
+  a.out_row_stride = out_row_stride;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_select(a, dtype);
+}
+
+size_t atk_topk_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j, int64_t k_mult) {
+  (void)n;
+  (void)j;
+  const int s = elem_size(dtype);
+  if (s == 0 || rows <= 0 || k <= 0 || k_mult <= 1) return 0;
+  const int64_t k0 = k * k_mult;
+  return align256(static_cast<size_t>(rows) * k0 * s) + align256(static_cast<size_t>(rows) * k0 * 8) +
+         select_workspace_bytes(dtype, rows, k0);
+}
+
+int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k, int j,
+             int64_t k_mult, int interleaved, int mode, void* out_vals, int64_t* out_idx,
+             int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  if (k_mult < 1 || k < 0) return ATK_ERR_BAD_ARG;
+  if (k_mult == 1)
+    return atk_stage1(x, dtype, rows, n, row_stride, k, j, interleaved, mode, out_vals, out_idx,
+                      out_row_stride, stream);
+  const int s = elem_size(dtype);
+  if (s == 0) return ATK_ERR_BAD_DTYPE;
+  if (k == 0 || rows == 0) return ATK_OK;
+  const int64_t k0 = k * k_mult;
+  const size_t need = atk_topk_workspace_bytes(dtype, rows, n, k, j, k_mult);
+  if (workspace == nullptr || workspace_bytes < need) return ATK_ERR_WORKSPACE;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  void* cand_vals = ws;
+  ws += align256(static_cast<size_t>(rows) * k0 * s);
+  int64_t* cand_idx = reinterpret_cast<int64_t*>(ws);
+  ws += align256(static_cast<size_t>(rows) * k0 * 8);
+  const size_t sel_ws = select_workspace_bytes(dtype, rows, k0);
+  int rc = atk_stage1(x, dtype, rows, n, row_stride, k0, j, interleaved, mode, cand_vals, cand_idx, k0, stream);
+  if (rc != ATK_OK) return rc;
+  return atk_select(cand_vals, cand_idx, dtype, rows, k0, k0, k, out_vals, out_idx, out_row_stride,
+                    sel_ws ? ws : nullptr, sel_ws, stream);
+}
+
+int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k,
+                        int interleaved, void* out_vals, int64_t* out_idx, int64_t out_row_stride,
+                        void* stream) {
+  int rc = check_common(x, dtype, rows, n, row_stride, out_vals, out_idx, out_row_stride);
+  if (rc != ATK_OK) return rc;
+  if (k < 0) return ATK_ERR_BAD_ARG;
+  if (k == 0 || rows == 0) return ATK_OK;
+  if (n == 0) return ATK_ERR_K_TOO_LARGE;
+  if (interleaved) {
+    SweepLaunch a;
+    a.x = x;
+    a.out_vals = out_vals;
+    a.out_idx = reinterpret_cast<long long*>(out_idx);
+    a.rows = rows;
+    a.n = n;
+    a.row_stride = row_stride;
+    a.out_row_stride = out_row_stride;
+    a.b = k;
+    a.stripe_stride = k;
+    a.idx_stride = k;
+    a.idx_offset = 0;
+    a.j = 1;
+    a.first_wins = true;
+    a.sm_count = sm_count_of_current_device();
+    a.stream = static_cast<cudaStream_t>(stream);
+    return sweep_dispatch(a, dtype);
+  }
+  ContigLaunch c;
+  c.x = x;
+  c.out_vals = out_vals;
+  c.out_idx = reinterpret_cast<long long*>(out_idx);
+  c.rows = rows;
+  c.n = n;
+  c.row_stride = row_stride;
+  c.out_row_stride = out_row_stride;
+  c.b = k;
+  c.j = 1;
+  c.first_wins = true;
+  c.fixed_chunks = true;
+  c.stream = static_cast<cudaStream_t>(stream);
+  return launch_contig(c, dtype);
+}
+
+// ---- host-buffer pipeline ---------------------------------------------------
+namespace {
+struct HostPlan {
+  int64_t chunk_rows;
+  size_t x_bytes, v_bytes, i_bytes, ws_bytes, slot_bytes;
+};
+HostPlan plan_host(int dtype, int64_t rows, int64_t n, int64_t k, int j, int64_t k_mult, int64_t chunk_rows) {
+  HostPlan p{};
+  const int s = elem_size(dtype);
+  if (chunk_rows <= 0) {
+    // about 32 MiB of input per chunk, at least 4 chunks when there are rows to split
+    const int64_t row_bytes = n * s > 0 ? n * s : 1;
+    chunk_rows = (32ll << 20) / row_bytes;
+    if (chunk_rows < 1) chunk_rows = 1;
+    if (chunk_rows > (rows + 3) / 4) chunk_rows = (rows + 3) / 4;
+    if (chunk_rows < 1) chunk_rows = 1;
+  }
+  if (chunk_rows > rows) chunk_rows = rows > 0 ? rows : 1;
+  p.chunk_rows = chunk_rows;
+  p.x_bytes = align256(static_cast<size_t>(chunk_rows) * n * s);
+  p.v_bytes = align256(static_cast<size_t>(chunk_rows) * k * s);
+  p.i_bytes = align256(static_cast<size_t>(chunk_rows) * k * 8);
+  p.ws_bytes = align256(atk_topk_workspace_bytes(dtype, chunk_rows, n, k, j, k_mult));
+  p.slot_bytes = p.x_bytes + p.v_bytes + p.i_bytes + p.ws_bytes;
+  return p;
+}
+}  // namespace
+
+size_t atk_topk_host_scratch_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j, int64_t k_mult,
+                                   int64_t chunk_rows) {
+  if (elem_size(dtype) == 0 || rows <= 0 || n <= 0 || k < 0 || k_mult < 1) return 0;
+  return 2 * plan_host(dtype, rows, n, k, j, k_mult, chunk_rows).slot_bytes;
+}
+
+int atk_topk_host(const void* x_host, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k,
+                  int j, int64_t k_mult, int interleaved, void* out_vals_host, int64_t* out_idx_host,
+                  void* device_scratch, size_t scratch_bytes, int64_t chunk_rows) {
+  const int s = elem_size(dtype);
+  if (s == 0) return ATK_ERR_BAD_DTYPE;
+  if (rows < 0 || n < 0 || k < 0 || k_mult < 1 || row_stride < n) return ATK_ERR_BAD_ARG;
+  if (rows == 0 || k == 0) return ATK_OK;
+  if (x_host == nullptr || out_vals_host == nullptr || out_idx_host == nullptr) return ATK_ERR_BAD_ARG;
+  const HostPlan p = plan_host(dtype, rows, n, k, j, k_mult, chunk_rows);
+  if (device_scratch == nullptr || scratch_bytes < 2 * p.slot_bytes) return ATK_ERR_WORKSPACE;
+
+  cudaStream_t st[2] = {nullptr, nullptr};
+  if (cudaStreamCreateWithFlags(&st[0], cudaStreamNonBlocking) != cudaSuccess) return ATK_ERR_CUDA;
+  if (cudaStreamCreateWithFlags(&st[1], cudaStreamNonBlocking) != cudaSuccess) {
+    cudaStreamDestroy(st[0]);
+    return ATK_ERR_CUDA;
+  }
+  int rc = ATK_OK;
+  int64_t chunk = 0;
+  for (int64_t r0 = 0; r0 < rows && rc == ATK_OK; r0 += p.chunk_rows, ++chunk) {
+    const int64_t nr = rows - r0 < p.chunk_rows ? rows - r0 : p.chunk_rows;
+    const int slot = static_cast<int>(chunk & 1);
+    unsigned char* base = static_cast<unsigned char*>(device_scratch) + slot * p.slot_bytes;
+    void* dx = base;
+    void* dv = base + p.x_bytes;
+    int64_t* di = reinterpret_cast<int64_t*>(base + p.x_bytes + p.v_bytes);
+    void* dws = p.ws_bytes ? base + p.x_bytes + p.v_bytes + p.i_bytes : nullptr;
+    const unsigned char* hx = static_cast<const unsigned char*>(x_host) + static_cast<size_t>(r0) * row_stride * s;
+    // Work queued on a stream runs in order, so a slot is reused only after
+    // its previous download has been issued on the same stream.
+    cudaError_t e = cudaMemcpy2DAsync(dx, static_cast<size_t>(n) * s, hx, static_cast<size_t>(row_stride) * s,
+                                      static_cast<size_t>(n) * s, static_cast<size_t>(nr),
+                                      cudaMemcpyHostToDevice, st[slot]);
+    if (e != cudaSuccess) { rc = ATK_ERR_CUDA; break; }
+    rc = atk_topk(dx, dtype, nr, n, n, k, j, k_mult, interleaved, -1, dv, di, k, dws, p.ws_bytes, st[slot]);
+    if (rc != ATK_OK) break;
+    e = cudaMemcpyAsync(static_cast<unsigned char*>(out_vals_host) + static_cast<size_t>(r0) * k * s, dv,
+                        static_cast<size_t>(nr) * k * s, cudaMemcpyDeviceToHost, st[slot]);
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(out_idx_host + r0 * k, di, static_cast<size_t>(nr) * k * 8, cudaMemcpyDeviceToHost,
+                          st[slot]);
+    if (e != cudaSuccess) rc = ATK_ERR_CUDA;
+  }
+  for (int i = 0; i < 2; ++i) {
+    if (cudaStreamSynchronize(st[i]) != cudaSuccess && rc == ATK_OK) rc = ATK_ERR_CUDA;
+    cudaStreamDestroy(st[i]);
+  }
+  return rc;
+}
+
+int64_t atk_launch_count(void) { return g_launches; }
+void atk_reset_launch_count(void) { g_launches = 0; }
+
+}  // extern "C"

@@ -1,0 +1,416 @@
+// Stage 2: exact top-k of the k0 stage-1 candidates of every row, indices
+// carried along.  Replaces torch.topk(sorted=False) + gather of the reference
+// (approx_topk/priority_queue.py:85-88).
+//
+// Method: MSB-first radix select on an order-preserving integer image of the
+// value finds the k-th largest key T and how many candidates equal to T are
+// still needed; an ordered compaction then writes every candidate above T
+// followed by the first `need` candidates equal to T, both in candidate-slot
+// order, so the result is deterministic.
+//
+//  * small rows (k0 <= kSmallMaxK0): one block per row, keys live in shared
+//    memory, a single launch;
+//  * large rows: several blocks per row; digit histograms, block counts and
+//    the running (prefix, need) state live in a caller-provided workspace.
+#include "atk_select.cuh"
+
+namespace atk {
+namespace {
+
+constexpr int kSmallMaxK0 = 32768;   // 128 KB of keys in shared memory
+constexpr int kChunk = 16384;        // candidates per block on the large path
+constexpr int kLargeThreads = 256;
+
+template <typename T> struct KeyOf;
+template <> struct KeyOf<float> {
+  static constexpr int kPasses = 4;
+  static __device__ __forceinline__ uint32_t key(uint32_t u) {
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  }
+};
+template <> struct KeyOf<__half> {
+  static constexpr int kPasses = 2;
+  static __device__ __forceinline__ uint32_t key(uint16_t h) {
+    const uint32_t u = h;
+    return ((u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u)) << 16;
+  }
+};
+template <> struct KeyOf<__nv_bfloat16> {
+  static constexpr int kPasses = 2;
+  static __device__ __forceinline__ uint32_t key(uint16_t h) { return KeyOf<__half>::key(h); }
+};
+
+// One warp: given a 256-bin histogram of the digit under inspection (only keys
+// that match the prefix found so far are counted) pick the bin that contains
+// the need-th largest key.  Bins are walked from 255 downwards.
+__device__ __forceinline__ void pick_digit(const uint32_t* hist, uint32_t need, uint32_t* out_digit,
+                                           uint32_t* out_need) {
+  const int lane = threadIdx.x & 31;
+  uint32_t h[8];
+  uint32_t total = 0;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    h[t] = hist[255 - 8 * lane - t];
+    total += h[t];
+  }
+  uint32_t incl = total;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += nb;
+  }
+  uint32_t running = incl - total;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    if (running < need && running + h[t] >= need) {
+      *out_digit = 255 - 8 * lane - t;
+      *out_need = need - running;
+    }
+    running += h[t];
+  }
+}
+
+// Exclusive block scan of two boolean flags.  Returns this thread's ranks and
+// the block totals.  wsum: >= 32 words of shared memory; contains one
+// __syncthreads pair, so all threads of the block must call it.
+__device__ __forceinline__ void block_rank2(bool f0, bool f1, uint32_t* wsum, uint32_t& r0,
+                                            uint32_t& r1, uint32_t& t0, uint32_t& t1) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  const uint32_t m0 = __ballot_sync(0xffffffffu, f0);
+  const uint32_t m1 = __ballot_sync(0xffffffffu, f1);
+  const uint32_t lt = (1u << lane) - 1u;
+  if (lane == 0) wsum[warp] = __popc(m0) | (__popc(m1) << 16);
+  __syncthreads();
+  uint32_t before = 0, all = 0;
+  for (int w = 0; w < nwarps; ++w) {
+    const uint32_t s = wsum[w];
+    if (w < warp) before += s;
+    all += s;
+  }
+  __syncthreads();
+  r0 = (before & 0xffffu) + __popc(m0 & lt);
+  r1 = (before >> 16) + __popc(m1 & lt);
+  t0 = all & 0xffffu;
+  t1 = all >> 16;
+}
+
+// ------------------------------------------------------------------ small path
+template <typename T>
+__global__ void __launch_bounds__(1024)
+select_small_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
+                    const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride,
+                    long long k, typename ElemTraits<T>::Bits* __restrict__ out_vals,
+                    long long* __restrict__ out_idx, long long out_row_stride) {
+  using K = KeyOf<T>;
+  extern __shared__ __align__(16) uint32_t select_smem[];
+  uint32_t* keys = select_smem;
+  uint32_t* hist = keys + k0;
+  uint32_t* misc = hist + 256;   // [0] digit, [1] need
+  uint32_t* wsum = misc + 2;     // 32 words
+
+  const int tid = threadIdx.x;
+  const int nthr = blockDim.x;
+  const long long row = blockIdx.x;
+  const auto* vrow = cand_vals + row * cand_row_stride;
+  const long long* irow = cand_idx + row * cand_row_stride;
+
+  for (int i = tid; i < k0; i += nthr) keys[i] = K::key(vrow[i]);
+
+  uint32_t prefix = 0, mask = 0, need = static_cast<uint32_t>(k);
+#pragma unroll 1
+  for (int pass = 0; pass < K::kPasses; ++pass) {
+    const int shift = 24 - 8 * pass;
+    for (int i = tid; i < 256; i += nthr) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < k0; i += nthr) {
+      const uint32_t key = keys[i];
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (tid < 32) pick_digit(hist, need, &misc[0], &misc[1]);
+    __syncthreads();
+    prefix |= misc[0] << shift;
+    mask |= 255u << shift;
+    need = misc[1];
+  }
+  // prefix is now the k-th largest key; `need` of its copies are taken.
+  const uint32_t n_gt = static_cast<uint32_t>(k) - need;
+  uint32_t gt_base = 0, eq_base = 0;
+  auto* ovrow = out_vals + row * out_row_stride;
+  long long* oirow = out_idx + row * out_row_stride;
+  for (int base = 0; base < k0; base += nthr) {
+    const int i = base + tid;
+    const bool in = i < k0;
+    const uint32_t key = in ? keys[i] : 0u;
+    const bool gt = in && key > prefix;
+    const bool eq = in && key == prefix;
+    uint32_t r_gt, r_eq, t_gt, t_eq;
+    block_rank2(gt, eq, wsum, r_gt, r_eq, t_gt, t_eq);
+    long long pos = -1;
+    if (gt) pos = gt_base + r_gt;
+    else if (eq && eq_base + r_eq < need) pos = static_cast<long long>(n_gt) + eq_base + r_eq;
+    if (pos >= 0) {
+      ovrow[pos] = vrow[i];
+      oirow[pos] = irow[i];
+    }
+    gt_base += t_gt;
+    eq_base += t_eq;
+  }
+}
+
+// ------------------------------------------------------------------ large path
+struct RowState {
+  uint32_t prefix, mask, need, pad;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kLargeThreads)
+select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
+                   long long cand_row_stride, int pass, const RowState* __restrict__ state,
+                   uint32_t* __restrict__ hist /* [rows][passes][256] */) {
+  using K = KeyOf<T>;
+  __shared__ uint32_t sh[256];
+  const long long row = blockIdx.y;
+  uint32_t prefix = 0, mask = 0;
+  if (pass > 0) {
+    prefix = state[row].prefix;
+    mask = state[row].mask;
+  }
+  const int shift = 24 - 8 * pass;
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const long long begin = static_cast<long long>(blockIdx.x) * kChunk;
+  long long end = begin + kChunk;
+  if (end > k0) end = k0;
+  const auto* vrow = cand_vals + row * cand_row_stride;
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const uint32_t key = K::key(vrow[i]);
+    if ((key & mask) == prefix) atomicAdd(&sh[(key >> shift) & 255u], 1u);
+  }
+  __syncthreads();
+  uint32_t* gh = hist + (row * K::kPasses + pass) * 256;
+  for (int i = threadIdx.x; i < 256; i += blockDim.x)
+    if (sh[i]) atomicAdd(&gh[i], sh[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32)
+select_pick_kernel(int pass, long long k, RowState* __restrict__ state,
+                   const uint32_t* __restrict__ hist) {
+  using K = KeyOf<T>;
+  __shared__ uint32_t res[2];
+  const long long row = blockIdx.x;
+  RowState st;
+  if (pass == 0) {
+    st.prefix = 0;
+    st.mask = 0;
+    st.need = static_cast<uint32_t>(k);
+    st.pad = 0;
+  } else {
+    st = state[row];
+  }
+  pick_digit(hist + (row * K::kPasses + pass) * 256, st.need, &res[0], &res[1]);
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const int shift = 24 - 8 * pass;
+    st.prefix |= res[0] << shift;
+    st.mask |= 255u << shift;
+    st.need = res[1];
+    state[row] = st;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLargeThreads)
+select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
+                    long long cand_row_stride, const RowState* __restrict__ state,
+                    uint2* __restrict__ counts /* [rows][chunks] */) {
+  using K = KeyOf<T>;
+  __shared__ uint32_t s_gt, s_eq;
+  if (threadIdx.x == 0) {
+    s_gt = 0;
+    s_eq = 0;
+  }
+  __syncthreads();
+  const long long row = blockIdx.y;
+  const uint32_t thr = state[row].prefix;
+  const long long begin = static_cast<long long>(blockIdx.x) * kChunk;
+  long long end = begin + kChunk;
+  if (end > k0) end = k0;
+  const auto* vrow = cand_vals + row * cand_row_stride;
+  uint32_t gt = 0, eq = 0;
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const uint32_t key = K::key(vrow[i]);
+    gt += key > thr;
+    eq += key == thr;
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    gt += __shfl_xor_sync(0xffffffffu, gt, off);
+    eq += __shfl_xor_sync(0xffffffffu, eq, off);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(&s_gt, gt);
+    atomicAdd(&s_eq, eq);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) counts[row * gridDim.x + blockIdx.x] = make_uint2(s_gt, s_eq);
+}
+
+// One warp per row: exclusive scan of the per-chunk (greater, equal) counts.
+__global__ void __launch_bounds__(32) select_scan_kernel(uint2* __restrict__ counts, int chunks) {
+  const long long row = blockIdx.x;
+  uint2* c = counts + row * chunks;
+  const int lane = threadIdx.x;
+  uint32_t carry_gt = 0, carry_eq = 0;
+  for (int base = 0; base < chunks; base += 32) {
+    const int i = base + lane;
+    const uint2 v = i < chunks ? c[i] : make_uint2(0, 0);
+    uint32_t gt = v.x, eq = v.y;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t a = __shfl_up_sync(0xffffffffu, gt, off);
+      const uint32_t b = __shfl_up_sync(0xffffffffu, eq, off);
+      if (lane >= off) {
+        gt += a;
+        eq += b;
+      }
+    }
+    if (i < chunks) c[i] = make_uint2(carry_gt + gt - v.x, carry_eq + eq - v.y);
+    carry_gt += __shfl_sync(0xffffffffu, gt, 31);
+    carry_eq += __shfl_sync(0xffffffffu, eq, 31);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLargeThreads)
+select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
+                    const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride,
+                    long long k, const RowState* __restrict__ state,
+                    const uint2* __restrict__ bases, typename ElemTraits<T>::Bits* __restrict__ out_vals,
+                    long long* __restrict__ out_idx, long long out_row_stride) {
+  using K = KeyOf<T>;
+  __shared__ uint32_t wsum[32];
+  const long long row = blockIdx.y;
+  const uint32_t thr = state[row].prefix;
+  const uint32_t need = state[row].need;
+  const long long n_gt = k - need;
+  const uint2 b = bases[row * gridDim.x + blockIdx.x];
+  uint32_t gt_base = b.x, eq_base = b.y;
+  const long long begin = static_cast<long long>(blockIdx.x) * kChunk;
+  long long end = begin + kChunk;
+  if (end > k0) end = k0;
+  const auto* vrow = cand_vals + row * cand_row_stride;
+  const long long* irow = cand_idx + row * cand_row_stride;
+  auto* ovrow = out_vals + row * out_row_stride;
+  long long* oirow = out_idx + row * out_row_stride;
+  for (long long base = begin; base < end; base += blockDim.x) {
+    const long long i = base + threadIdx.x;
+    const bool in = i < end;
+    typename ElemTraits<T>::Bits raw = 0;
+    if (in) raw = vrow[i];
+    const uint32_t key = K::key(raw);
+    const bool gt = in && key > thr;
+    const bool eq = in && key == thr;
+    uint32_t r_gt, r_eq, t_gt, t_eq;
+    block_rank2(gt, eq, wsum, r_gt, r_eq, t_gt, t_eq);
+    long long pos = -1;
+    if (gt) pos = static_cast<long long>(gt_base) + r_gt;
+    else if (eq && eq_base + r_eq < need) pos = n_gt + eq_base + r_eq;
+    if (pos >= 0) {
+      ovrow[pos] = raw;
+      oirow[pos] = irow[i];
+    }
+    gt_base += t_gt;
+    eq_base += t_eq;
+  }
+}
+
+inline long long chunks_of(long long k0) { return (k0 + kChunk - 1) / kChunk; }
+inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+template <typename T>
+size_t workspace_typed(long long rows, long long k0) {
+  if (k0 <= kSmallMaxK0) return 0;
+  const size_t state = align256(sizeof(RowState) * rows);
+  const size_t hist = align256(sizeof(uint32_t) * 256 * KeyOf<T>::kPasses * rows);
+  const size_t counts = align256(sizeof(uint2) * chunks_of(k0) * rows);
+  return state + hist + counts;
+}
+
+template <typename T>
+int select_typed(const SelectLaunch& a) {
+  using Bits = typename ElemTraits<T>::Bits;
+  using K = KeyOf<T>;
+  const Bits* cv = static_cast<const Bits*>(a.cand_vals);
+  Bits* ov = static_cast<Bits*>(a.out_vals);
+  if (a.k0 <= kSmallMaxK0) {
+    int threads = 128;
+    while (threads < 1024 && threads * 8 < a.k0) threads *= 2;
+    const size_t smem = sizeof(uint32_t) * (static_cast<size_t>(a.k0) + 256 + 2 + 32);
+    if (smem > 48 * 1024) {
+      if (cudaFuncSetAttribute(select_small_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)) != cudaSuccess)
+        return ATK_ERR_CUDA;
+    }
+    if (a.rows >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+    select_small_kernel<T><<<static_cast<unsigned>(a.rows), threads, smem, a.stream>>>(
+        cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, ov, a.out_idx, a.out_row_stride);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+  }
+
+  if (a.k0 >= (1ll << 32) || a.rows > 65535) return ATK_ERR_TOO_LARGE;
+  const size_t need_ws = workspace_typed<T>(a.rows, a.k0);
+  if (a.workspace == nullptr || a.workspace_bytes < need_ws) return ATK_ERR_WORKSPACE;
+  const long long chunks = chunks_of(a.k0);
+  unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+  RowState* state = reinterpret_cast<RowState*>(ws);
+  ws += align256(sizeof(RowState) * a.rows);
+  uint32_t* hist = reinterpret_cast<uint32_t*>(ws);
+  const size_t hist_bytes = sizeof(uint32_t) * 256 * K::kPasses * a.rows;
+  ws += align256(hist_bytes);
+  uint2* counts = reinterpret_cast<uint2*>(ws);
+
+  if (cudaMemsetAsync(hist, 0, hist_bytes, a.stream) != cudaSuccess) return ATK_ERR_CUDA;
+  const dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(a.rows));
+  for (int pass = 0; pass < K::kPasses; ++pass) {
+    select_hist_kernel<T><<<grid, kLargeThreads, 0, a.stream>>>(cv, a.k0, a.cand_row_stride, pass,
+                                                                 state, hist);
+    select_pick_kernel<T><<<static_cast<unsigned>(a.rows), 32, 0, a.stream>>>(pass, a.k, state, hist);
+  }
+  select_count_kernel<T><<<grid, kLargeThreads, 0, a.stream>>>(cv, a.k0, a.cand_row_stride, state,
+                                                                counts);
+  select_scan_kernel<<<static_cast<unsigned>(a.rows), 32, 0, a.stream>>>(counts,
+                                                                          static_cast<int>(chunks));
+  select_write_kernel<T><<<grid, kLargeThreads, 0, a.stream>>>(cv, a.cand_idx, a.k0,
+                                                                a.cand_row_stride, a.k, state, counts,
+                                                                ov, a.out_idx, a.out_row_stride);
+  note_launch(2 * K::kPasses + 3);
+  return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+}
+
+}  // namespace
+
+size_t select_workspace_bytes(int dtype, long long rows, long long k0) {
+  switch (dtype) {
+    case ATK_F32: return workspace_typed<float>(rows, k0);
+    case ATK_F16: return workspace_typed<__half>(rows, k0);
+    case ATK_BF16: return workspace_typed<__nv_bfloat16>(rows, k0);
+    default: return 0;
+  }
+}
+
+int launch_select(const SelectLaunch& a, int dtype) {
+  if (a.rows <= 0 || a.k <= 0) return ATK_OK;
+  switch (dtype) {
+    case ATK_F32: return select_typed<float>(a);
+    case ATK_F16: return select_typed<__half>(a);
+    case ATK_BF16: return select_typed<__nv_bfloat16>(a);
+    default: return ATK_ERR_BAD_DTYPE;
+  }
+}
+
+}  // namespace atk

@@ -1,0 +1,108 @@
+// Host-side launch logic of the column sweep, included by one translation unit
+// per element type so the template instantiations compile in parallel.
+#pragma once
+
+#include "atk_sweep.cuh"
+
+namespace atk {
+
+namespace sweep_detail {
+
+inline long long floor_pow2(long long v) {
+  long long r = 1;
+  while (r * 2 <= v) r *= 2;
+  return r;
+}
+inline long long ceil_pow2(long long v) {
+  long long r = 1;
+  while (r < v) r *= 2;
+  return r;
+}
+
+template <typename T, int J, int V, bool FIRST>
+int launch_typed(const SweepLaunch& a) {
+  constexpr int s = static_cast<int>(sizeof(T));
+  SweepParams p;
+  p.x = a.x;
+  p.out_vals = a.out_vals;
+  p.out_idx = a.out_idx;
+  p.rows = a.rows;
+  p.row_stride = a.row_stride;
+  p.out_row_stride = a.out_row_stride;
+  p.b = a.b;
+  p.l_full = a.n / a.b;
+  p.rem = a.n - p.l_full * a.b;
+  p.stripe_stride = a.stripe_stride;
+  p.idx_stride = a.idx_stride;
+  p.idx_offset = a.idx_offset;
+  if (p.l_full + 1 >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+
+  const long long col_threads = (a.b + V - 1) / V;
+  long long cw = col_threads < kSweepMaxThreads ? col_threads : kSweepMaxThreads;
+  const long long tiles = (col_threads + cw - 1) / cw;
+  p.tiles = tiles;
+  p.cw = static_cast<int>(cw);
+  if (a.rows * tiles >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+
+  // Stripe splits inside the block: only when the columns alone cannot fill
+  // the machine, never more than the block size or the stripe count allow.
+  long long S = 1;
+  const long long want_threads = static_cast<long long>(a.sm_count) * 1024;
+  const long long have_threads = a.rows * tiles * cw;
+  if (have_threads < want_threads && p.l_full >= 8) {
+    const long long by_block = floor_pow2(kSweepMaxThreads / cw);
+    const long long by_work = floor_pow2(p.l_full / 4);
+    const long long by_need = ceil_pow2((want_threads + have_threads - 1) / have_threads);
+    S = by_block;
+    if (by_work < S) S = by_work;
+    if (by_need < S) S = by_need;
+    if (S < 1) S = 1;
+  }
+  p.s = static_cast<int>(S);
+
+  const uintptr_t ov = reinterpret_cast<uintptr_t>(a.out_vals);
+  const uintptr_t oi = reinterpret_cast<uintptr_t>(a.out_idx);
+  p.vec_out = (ov % 16 == 0) && (oi % 16 == 0) && ((a.out_row_stride * s) % 16 == 0) &&
+              ((a.out_row_stride * 8) % 16 == 0);
+
+  const size_t smem = S > 1 ? static_cast<size_t>(S / 2) * (V * J) * cw * 8 : 0;
+  const dim3 grid(static_cast<unsigned>(a.rows * tiles));
+  const dim3 block(static_cast<unsigned>(cw), static_cast<unsigned>(S));
+  // The head test pays off once a thread walks a long column.
+  const bool skip = (p.l_full / S) >= 256;
+  if (skip)
+    sweep_kernel<T, J, V, FIRST, true><<<grid, block, smem, a.stream>>>(p);
+  else
+    sweep_kernel<T, J, V, FIRST, false><<<grid, block, smem, a.stream>>>(p);
+  note_launch();
+  return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+}
+
+template <typename T, int V>
+int launch_by_j(const SweepLaunch& a) {
+  if (a.first_wins) {
+    if (a.j != 1) return ATK_ERR_BAD_J;
+    return launch_typed<T, 1, V, true>(a);
+  }
+  switch (a.j) {
+    case 1: return launch_typed<T, 1, V, false>(a);
+    case 2: return launch_typed<T, 2, V, false>(a);
+    case 3: return launch_typed<T, 3, V, false>(a);
+    case 4: return launch_typed<T, 4, V, false>(a);
+    default: return ATK_ERR_BAD_J;
+  }
+}
+
+// Vector path: every 16-byte load must be aligned and lie inside one stripe.
+template <typename T>
+int launch_sweep(const SweepLaunch& a) {
+  constexpr int s = static_cast<int>(sizeof(T));
+  constexpr int kVec = ElemTraits<T>::kVec;
+  if (a.rows <= 0 || a.b <= 0) return ATK_OK;
+  const bool vec = (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) && ((a.row_stride * s) % 16 == 0) &&
+                   ((a.stripe_stride * s) % 16 == 0) && (a.b % kVec == 0);
+  return vec ? launch_by_j<T, kVec>(a) : launch_by_j<T, 1>(a);
+}
+
+}  // namespace sweep_detail
+}  // namespace atk

@@ -1,0 +1,33 @@
+"""pytest configuration: the `gpu` marker and import paths."""
+
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+PACKAGE_DIR = ROOT / "pytorch-approx-topk_b200"
+for p in (str(ROOT), str(PACKAGE_DIR)):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100); run with -m gpu on a B200")
+
+
+def pytest_collection_modifyitems(config, items):
+    # GPU tests must never be silently skipped on a GPU box: they fail loudly
+    # if CUDA is missing when explicitly selected with -m gpu.
+    pass
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import json
+
+    import numpy as np
+
+    data = np.load(ROOT / "tests" / "golden" / "reference_cpu_vectors.npz")
+    meta = json.loads(bytes(data["meta"]).decode())
+    return data, meta

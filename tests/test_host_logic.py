@@ -1,0 +1,166 @@
+"""CPU-only checks: the C-ABI library loads and exports every symbol the header
+declares, status texts, the Python operator's argument handling and meta
+implementation, and the torch-composition helpers of approx_topk.experimental."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from approx_topk import Topk, _native, topk
+from approx_topk.cuda_extensions import load_cuda_extension
+from approx_topk.experimental.autobucket import bucket, bucketed_torch_topk
+from approx_topk.experimental.bucketed_argmax import _batch_contiguous, _min_value, topk_torch, topk_triton
+from tests.helper_funcs import assert_close_up_to_permutation
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_functions() -> list[str]:
+    text = (ROOT / "include" / "atk.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return re.findall(r"\b(atk_[a-z0-9_]+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_functions()
+    assert len(names) >= 12
+    handle = ctypes.CDLL(str(_native.library_path()))
+    for name in names:
+        assert hasattr(handle, name), f"libatk.so lacks {name}"
+    assert set(names) == set(_native.SIGNATURES), "python prototypes and header differ"
+
+
+def test_version_and_status_texts():
+    lib = load_cuda_extension("priority_queue_approx_topk.cu", compile_mode="optimize")
+    assert lib is _native.lib()
+    assert lib.atk_version() >= 10000
+    assert _native.strerror(0) == "ok"
+    assert "j must divide k" in _native.strerror(_native.ATK_ERR_J_DIVIDES_K)
+    assert "0 < j < 5" in _native.strerror(_native.ATK_ERR_BAD_J)
+    assert "must not be larger" in _native.strerror(_native.ATK_ERR_K_TOO_LARGE)
+    assert lib.atk_topk_workspace_bytes(0, 8, 4096, 64, 2, 1) == 0
+    need = lib.atk_topk_workspace_bytes(0, 8, 4096, 64, 2, 4)
+    assert need >= 8 * 256 * (4 + 8)
+    assert lib.atk_select_workspace_bytes(0, 1, 1 << 21, 1 << 20) > 0
+    assert lib.atk_select_workspace_bytes(2, 1024, 4096, 2048) == 0
+
+
+def test_python_checks_come_before_any_native_call():
+    xs = torch.randn(8, 64)
+    with pytest.raises(NotImplementedError):
+        topk(xs, 4, dim=0, j=2)
+    with pytest.raises(ValueError):
+        topk(xs, 4, dim=-1, k_mult=0)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        topk(xs, 4, dim=-1)          # no CPU path, and it says so
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        topk_torch(xs, 4, dim=-1, interleaved=True)
+    with pytest.raises(ValueError):
+        topk_triton(xs, 4, dim=-1, interleaved=True, block_size=8, kernel="nope")
+
+
+def test_meta_implementation_shapes():
+    xs = torch.empty(5, 7, 64, device="meta", dtype=torch.bfloat16)
+    v, i = topk(xs, 8, -1, 2, 2)
+    assert v.shape == (5, 7, 8) and v.dtype == torch.bfloat16 and v.device.type == "meta"
+    assert i.shape == (5, 7, 8) and i.dtype == torch.int64
+    v, i = topk(torch.empty(6, 4, device="meta"), 4, 0, 4)
+    assert v.shape == (4, 4)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setenv("ATK_LIBRARY", str(tmp_path / "nope.so"))
+    _native.lib.cache_clear()
+    try:
+        with pytest.raises(RuntimeError, match="not found"):
+            _native.lib()
+    finally:
+        monkeypatch.delenv("ATK_LIBRARY")
+        _native.lib.cache_clear()
+        _native.lib()
+
+
+def test_as_rows_layouts():
+    x = torch.arange(6 * 10.0).reshape(6, 10)
+    t, rows, n, stride = _native.as_rows(x)
+    assert t is x and (rows, n, stride) == (6, 10, 10)
+    t, rows, n, stride = _native.as_rows(x[:, :8])
+    assert t.data_ptr() == x.data_ptr() and (rows, n, stride) == (6, 8, 10)
+    t, rows, n, stride = _native.as_rows(x[:, ::2])
+    assert t.is_contiguous() and (rows, n, stride) == (6, 5, 5)
+    y = torch.arange(2 * 3 * 4.0).reshape(2, 3, 4)
+    t, rows, n, stride = _native.as_rows(y.movedim(0, -1))
+    assert t.is_contiguous() and (rows, n, stride) == (12, 2, 2)
+
+
+def test_min_value():
+    assert _min_value(torch.float16) == -65504.0
+    assert _min_value(torch.int16) == -32768
+
+
+def test_batch_contiguous():
+    x = torch.arange(3 * 4 * 5).view(3, 4, 5)
+    for t, same in [(x, True), (x[:, :, :-1], True), (x[:, :, ::2], False), (x[:, :-1, :], False),
+                    (x.swapdims(0, 1), False)]:
+        t2 = _batch_contiguous(t)
+        if same:
+            assert t2 is t
+        else:
+            assert torch.equal(t, t2) and t2.is_contiguous()
+        assert t2.stride(-1) == 1
+
+
+# --- the generic bucketed construction (runs on CPU tensors) ----------------
+
+def exact(xs, k, dim):
+    return torch.topk(xs, k, dim, sorted=False)
+
+
+def test_bucket_rejects_indivisible_k():
+    with pytest.raises(NotImplementedError):
+        bucket(exact, k_mult=1, k_per_bucket=12, interleaved=True)(torch.randn(1024), 13, dim=0)
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_bucket_single_bucket_is_exact(interleaved):
+    xs = torch.randn(1024)
+    v, i = bucket(exact, k_mult=1, k_per_bucket=128, interleaved=interleaved)(xs, 128, dim=0)
+    ev, ei = exact(xs, 128, 0)
+    assert_close_up_to_permutation(v, ev)
+    assert_close_up_to_permutation(i, ei)
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("k_mult", [1, 2, 4])
+@pytest.mark.parametrize("k_per_bucket", [1, 2, 4])
+def test_bucket_shapes(interleaved, k_mult, k_per_bucket):
+    v, i = bucketed_torch_topk(torch.randn(5, 32, 1000), 16, -1, k_mult, k_per_bucket, interleaved)
+    assert v.shape == (5, 32, 16) and i.shape == (5, 32, 16)
+
+
+@pytest.mark.parametrize("interleaved,k_mult,k,n,expected", [
+    (False, 1, 3, 10, [3, 6, 9]), (True, 1, 3, 10, [9, 7, 8]),
+    (False, 2, 4, 16, [15, 13, 11, 9]), (True, 2, 4, 16, [15, 14, 13, 12]),
+])
+def test_bucket_arange_cases(interleaved, k_mult, k, n, expected):
+    v, i = bucket(torch.topk, k_mult=k_mult, k_per_bucket=1, interleaved=interleaved)(torch.arange(n), k=k, dim=-1)
+    assert_close_up_to_permutation(v, torch.tensor(expected))
+    assert_close_up_to_permutation(i, torch.tensor(expected))
+
+
+def test_bucket_matches_reference_fixtures(golden):
+    data, meta = golden
+    for idx, m in enumerate(meta):
+        if m["kind"] != "bucketed_torch_topk" or m["dtype"] != "float32":
+            continue
+        x = torch.from_numpy(data[f"c{idx}_x"])
+        v, i = bucketed_torch_topk(x, m["k"], -1, m["k_mult"], m["j"], m["interleaved"])
+        assert torch.equal(v.sort(dim=-1).values, torch.from_numpy(data[f"c{idx}_values"])), m
+        assert torch.equal(i.sort(dim=-1).values, torch.from_numpy(data[f"c{idx}_indices"])), m
+
+
+def test_topk_protocol_is_exported():
+    assert hasattr(Topk, "__call__")

@@ -1,0 +1,212 @@
+"""GPU parity tests proper: the CUDA kernels, called through the C ABI, against
+the CPU oracle (bit-exact values and indices, slot by slot) and, when it has
+been built, against the reference's own CUDA operator."""
+
+import pytest
+import torch
+
+from oracle import cpu_oracle as oracle
+from tests import native_api as api
+from tests import reference_cuda as refcuda
+from tests.helper_funcs import assert_pairs_identical, assert_valid_selection
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+def make(rows, n, dtype, seed, dist="randn"):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if dist == "randn":
+        x = torch.randn(rows, n, generator=g, device="cuda")
+    elif dist == "ties":       # few distinct values: ties at every bucket boundary
+        x = torch.randint(-3, 4, (rows, n), generator=g, device="cuda").float()
+    elif dist == "linspace":   # correlated rows
+        x = torch.linspace(0, 1, n, device="cuda")[None] + 0.01 * torch.randn(rows, n, generator=g, device="cuda")
+    else:
+        raise ValueError(dist)
+    return x.to(dtype)
+
+
+def bits(t):
+    t = t.detach().cpu()
+    return t.view(torch.int32) if t.dtype == torch.float32 else t.view(torch.int16)
+
+
+def check_stage1_exact(x, k0, j, interleaved):
+    v, i = api.stage1(x, k0, j, interleaved)
+    ov, oi = oracle.stage1(x.cpu(), k0, j, interleaved)
+    assert torch.equal(bits(v), bits(ov)), f"values differ ({tuple(x.shape)}, k0={k0}, j={j}, il={interleaved})"
+    assert torch.equal(i.cpu(), oi), f"indices differ ({tuple(x.shape)}, k0={k0}, j={j}, il={interleaved})"
+    return v, i
+
+
+# (rows, n, k0) geometries: aligned/unaligned, b | n and b !| n, tiny rows,
+# few-row long-column shapes that take the split-and-merge path.
+GEOMETRIES = [
+    (4, 1024, 256), (3, 1001, 48), (5, 17, 8), (2, 1000, 500), (2, 4096, 4096),
+    (7, 8192, 64), (1, 65536, 64), (2, 100000, 1024), (1, 12, 12), (33, 515, 24),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j", [1, 2, 3, 4])
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_stage1_matches_oracle_slot_for_slot(dtype, j, interleaved):
+    for seed, (rows, n, k0) in enumerate(GEOMETRIES):
+        if k0 % j:
+            k0 = (k0 // j) * j
+        if k0 == 0:
+            continue
+        check_stage1_exact(make(rows, n, dtype, 10 + seed), k0, j, interleaved)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j", [1, 2, 4])
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_stage1_tie_rule(dtype, j, interleaved):
+    # Later position wins among equal values, exactly like the reference scan.
+    for seed, (rows, n, k0) in enumerate([(4, 1024, 128), (2, 777, 28), (1, 65536, 32), (3, 30000, 512)]):
+        check_stage1_exact(make(rows, n, dtype, 50 + seed, "ties"), k0, j, interleaved)
+
+
+def test_stage1_all_equal_row():
+    x = torch.ones(2, 4096, device="cuda")
+    v, i = check_stage1_exact(x, 64, 2, True)
+    # 32 buckets of 128: the two last positions of every bucket survive
+    assert i[0, :4].tolist() == [32 * 126, 32 * 127, 32 * 126 + 1, 32 * 127 + 1]
+
+
+def test_stage1_neg_inf_is_selectable():
+    x = torch.full((2, 256), float("-inf"), device="cuda")
+    x[0, 5] = 1.0
+    v, i = check_stage1_exact(x, 16, 2, True)
+    assert (i >= 0).all() and (i < 256).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_stage1_long_columns_head_test_path(dtype):
+    # l_full / splits >= 256 selects the variant that tests queue heads first.
+    for j in (1, 2, 4):
+        check_stage1_exact(make(64, 1 << 18, dtype, 7), 64 * j, j, True)
+    check_stage1_exact(make(1, 1 << 20, dtype, 8, "ties"), 8, 4, True)
+
+
+def test_stage1_row_stride_and_unaligned_base():
+    base = make(9, 1100, torch.float32, 3)
+    view = base[:, 3:1027]            # base pointer only 4-byte aligned, row stride 1100
+    v, i = api.stage1(view, 128, 2, True)
+    ov, oi = oracle.stage1(view.cpu().contiguous(), 128, 2, True)
+    assert torch.equal(bits(v), bits(ov)) and torch.equal(i.cpu(), oi)
+
+
+@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j", [1, 2, 3, 4])
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_stage1_matches_reference_cuda_operator(dtype, j, interleaved):
+    for seed, (rows, n, k0) in enumerate(GEOMETRIES):
+        k0 = (k0 // j) * j
+        if k0 == 0:
+            continue
+        for dist in ("randn", "ties"):
+            x = make(rows, n, dtype, 90 + seed, dist)
+            v, i = api.stage1(x, k0, j, interleaved)
+            rv, ri = refcuda.reference_stage1(x, k0, j, interleaved, multithread_buckets=False)
+            # same slots, same order: the thread-per-bucket kernel's layout is kept
+            assert torch.equal(bits(v), bits(rv)), (dtype, j, interleaved, rows, n, k0, dist)
+            assert torch.equal(i, ri), (dtype, j, interleaved, rows, n, k0, dist)
+
+
+@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j,k_mult", [(1, 1), (2, 1), (4, 2), (2, 4), (1, 4)])
+def test_topk_matches_reference_cuda_operator(dtype, j, k_mult):
+    for seed, (rows, n, k) in enumerate([(8, 4096, 64), (3, 10007, 32), (2, 65536, 1024)]):
+        x = make(rows, n, dtype, 200 + seed)
+        v, i = api.topk(x, k, j, k_mult, True)
+        rv, ri = refcuda.reference_topk(x, k, -1, j, k_mult, True, False)
+        if dtype == torch.float32:
+            assert_pairs_identical(v, i, rv, ri)       # tie-free rows: bit-exact pairs
+        else:
+            assert_valid_selection(x, v, i, rv)        # ties: multiset + valid distinct indices
+        assert oracle.recall(x.cpu(), v.cpu()) == oracle.recall(x.cpu(), rv.cpu())
+
+
+@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
+@pytest.mark.parametrize("j", [1, 2, 4])
+def test_block_per_bucket_reference_kernel_same_selection(j):
+    # The reference's 64-thread-per-bucket kernel must select the same set on tie-free rows.
+    x = make(4, 16384, torch.float32, 77)
+    v, i = api.stage1(x, 32 * j, j, True)
+    rv, ri = refcuda.reference_stage1(x, 32 * j, j, True, multithread_buckets=True)
+    assert_pairs_identical(v, i, rv, ri)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,k0,k", [(4, 256, 64), (16, 4096, 2048), (3, 1000, 1), (2, 1000, 1000),
+                                       (5, 777, 300), (2, 32768, 5000), (1, 40000, 20000),
+                                       (2, 100000, 777), (1, 1 << 21, 1 << 20)])
+def test_select_matches_oracle(dtype, rows, k0, k):
+    for dist in ("randn", "ties"):
+        cv = make(rows, k0, dtype, 300 + k, dist)
+        cv = torch.where(cv == 0, torch.zeros_like(cv), cv)      # no negative zeros
+        ci = torch.randperm(rows * k0, device="cuda", generator=torch.Generator(device="cuda").manual_seed(k)
+                            ).reshape(rows, k0)
+        v, i = api.select(cv, ci, k)
+        ov, oi = oracle.select(cv.cpu(), ci.cpu(), k)
+        # lowest candidate slots win ties in both: identical pairs
+        assert_pairs_identical(v, i, ov, oi)
+        v2, i2 = api.select(cv, ci, k)
+        assert torch.equal(v, v2) and torch.equal(i, i2)         # deterministic, order included
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j,k_mult", [(1, 2), (2, 2), (4, 2), (2, 4), (1, 16)])
+def test_topk_two_stage_matches_oracle(dtype, j, k_mult):
+    for seed, (rows, n, k) in enumerate([(8, 4096, 64), (3, 10007, 32), (2, 65536, 1024), (1, 300000, 20000)]):
+        if k * k_mult > n:
+            continue
+        x = make(rows, n, dtype, 400 + seed)
+        v, i = api.topk(x, k, j, k_mult, True)
+        ov, oi = oracle.topk(x.cpu(), k, j, k_mult, True)
+        assert_valid_selection(x, v, i, ov)
+        if dtype == torch.float32:
+            assert_pairs_identical(v, i, ov, oi)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_bucketed_argmax_matches_oracle(dtype, interleaved):
+    for seed, (rows, n, k) in enumerate([(2, 20, 3), (3, 1000, 7), (4, 4096, 256), (2, 10, 4), (1, 5, 8),
+                                         (16, 65536, 256), (2, 1001, 64)]):
+        for dist in ("randn", "ties"):
+            x = make(rows, n, dtype, 500 + seed, dist)
+            v, i = api.bucketed_argmax(x, k, interleaved)
+            ov, oi = oracle.bucketed_argmax(x.cpu(), k, interleaved)
+            assert torch.equal(bits(v), bits(ov)), (rows, n, k, dist)
+            assert torch.equal(i.cpu(), oi), (rows, n, k, dist)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j", [1, 4])
+def test_slab_gives_the_matching_slice_of_the_full_row(dtype, j):
+    stripes, b, groups = 512, 2048, 4
+    x = make(1, stripes * b, dtype, 600)
+    full_v, full_i = api.stage1(x, b * j, j, True)
+    cols = b // groups
+    for g in range(groups):
+        slab = x.view(stripes, b)[:, g * cols:(g + 1) * cols].contiguous()
+        v, i = api.stage1_slab(slab, b, g * cols, j)
+        assert torch.equal(bits(v), bits(full_v[0, g * cols * j:(g + 1) * cols * j]))
+        assert torch.equal(i, full_i[0, g * cols * j:(g + 1) * cols * j])
+
+
+@pytest.mark.parametrize("dtype,j,k_mult", [(torch.float32, 2, 1), (torch.bfloat16, 4, 2)])
+def test_host_buffer_entry_point_equals_device_path(dtype, j, k_mult):
+    x = make(37, 8192, dtype, 700)
+    v, i = api.topk(x, 128, j, k_mult, True)
+    hv, hi = api.topk_host(x.cpu().pin_memory(), 128, j, k_mult, True, chunk_rows=5)
+    assert torch.equal(bits(hv), bits(v)) and torch.equal(hi, i.cpu())
+    hv, hi = api.topk_host(x.cpu(), 128, j, k_mult, True)      # pageable memory, default chunking
+    assert torch.equal(bits(hv), bits(v)) and torch.equal(hi, i.cpu())
