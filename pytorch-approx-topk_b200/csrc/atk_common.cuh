@@ -120,13 +120,21 @@ template <> struct VecLoad<__half, 1> {
 // LAST wins  (reference operator): enters when !(q > v), passes equal slots.
 // FIRST wins (k_b = 1 arg-max entry): needs the explicit position test so a
 // real -inf element replaces the sentinel.
+//
+// `head` is the caller-evaluated test !(qv[0] > v).  It is passed in rather
+// than recomputed here on purpose: when this code sits behind a branch on the
+// same comparison (the head test of long columns), nvcc 12.9 was seen to fold
+// the re-evaluated `head ? v : qv[0]` to qv[0] inside rolled loops, leaving a
+// stale value next to the right index.  Reusing the branch predicate itself
+// gives the optimiser nothing to "correlate".
 template <int J, bool FIRST>
-__device__ __forceinline__ void queue_push_scan(float (&qv)[J], int (&qi)[J], float v, int pos) {
+__device__ __forceinline__ void queue_push_scan(float (&qv)[J], int (&qi)[J], float v, int pos, bool head) {
   bool p[J + 1];
 #pragma unroll
   for (int i = 0; i < J; ++i) {
-    if (FIRST) p[i] = (v > qv[i]) || (v == qv[i] && pos < qi[i]);
-    else       p[i] = !(qv[i] > v);
+    if (FIRST)       p[i] = (v > qv[i]) || (v == qv[i] && pos < qi[i]);
+    else if (i == 0) p[i] = head;
+    else             p[i] = !(qv[i] > v);
     // The reference loop stops at the first slot that holds; chaining the
     // predicates reproduces that even when NaNs make the queue unordered.
     if (i > 0) p[i] = p[i] && p[i - 1];
@@ -141,6 +149,10 @@ __device__ __forceinline__ void queue_push_scan(float (&qv)[J], int (&qi)[J], fl
     qv[i] = nv;
     qi[i] = ni;
   }
+}
+template <int J, bool FIRST>
+__device__ __forceinline__ void queue_push_scan(float (&qv)[J], int (&qi)[J], float v, int pos) {
+  queue_push_scan<J, FIRST>(qv, qi, v, pos, !(qv[0] > v));
 }
 
 // Order-independent insertion used when partial queues are merged: the rank is

@@ -43,7 +43,11 @@ constexpr int kSweepMaxThreads = 256;
 
 template <int V, int J> struct SweepUnroll {
   // independent 16-byte loads kept in flight per thread
+#ifdef ATK_DEBUG_U
+  static constexpr int kU = ATK_DEBUG_U;
+#else
   static constexpr int kU = (V * J <= 16) ? 8 : 4;
+#endif
 };
 
 template <typename T, int J, int V, bool FIRST, bool SKIP>
@@ -51,16 +55,23 @@ __device__ __forceinline__ void sweep_consume(float (&qv)[V][J], int (&qi)[V][J]
                                               const typename VecLoad<T, V>::Raw& raw, int stripe) {
   float v[V];
   VecLoad<T, V>::widen(raw, v);
+  bool head[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) head[e] = !(qv[e][0] > v[e]);
   if (SKIP) {
     // Long columns: almost no element beats the current J-th best, so test
     // the V heads first and only run the insertion network when one does.
     bool any = false;
 #pragma unroll
-    for (int e = 0; e < V; ++e) any = any || !(qv[e][0] > v[e]);
-    if (!any) return;
-  }
+    for (int e = 0; e < V; ++e) any = any || head[e];
+    if (any) {
 #pragma unroll
-  for (int e = 0; e < V; ++e) queue_push_scan<J, FIRST>(qv[e], qi[e], v[e], stripe);
+      for (int e = 0; e < V; ++e) queue_push_scan<J, FIRST>(qv[e], qi[e], v[e], stripe, head[e]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < V; ++e) queue_push_scan<J, FIRST>(qv[e], qi[e], v[e], stripe, head[e]);
+  }
 }
 
 template <typename T, int J, int V, bool FIRST, bool SKIP>

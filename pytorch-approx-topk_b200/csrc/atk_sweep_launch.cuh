@@ -69,7 +69,10 @@ int launch_typed(const SweepLaunch& a) {
   const dim3 grid(static_cast<unsigned>(a.rows * tiles));
   const dim3 block(static_cast<unsigned>(cw), static_cast<unsigned>(S));
   // The head test pays off once a thread walks a long column.
-  const bool skip = (p.l_full / S) >= 256;
+  bool skip = (p.l_full / S) >= 256;
+#ifdef ATK_DEBUG_NO_SKIP
+  skip = false;
+#endif
   if (skip)
     sweep_kernel<T, J, V, FIRST, true><<<grid, block, smem, a.stream>>>(p);
   else

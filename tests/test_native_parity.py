@@ -46,6 +46,8 @@ def check_stage1_exact(x, k0, j, interleaved):
 GEOMETRIES = [
     (4, 1024, 256), (3, 1001, 48), (5, 17, 8), (2, 1000, 500), (2, 4096, 4096),
     (7, 8192, 64), (1, 65536, 64), (2, 100000, 1024), (1, 12, 12), (33, 515, 24),
+    # long columns (head-test kernel variant): unsplit aligned / unaligned, and split
+    (2, 300000, 1024), (2, 300001, 1020), (1, 600000, 96), (3, 2 * 5000 * 300, 2 * 5000),
 ]
 
 
@@ -179,7 +181,8 @@ def test_topk_two_stage_matches_oracle(dtype, j, k_mult):
 @pytest.mark.parametrize("interleaved", [True, False])
 def test_bucketed_argmax_matches_oracle(dtype, interleaved):
     for seed, (rows, n, k) in enumerate([(2, 20, 3), (3, 1000, 7), (4, 4096, 256), (2, 10, 4), (1, 5, 8),
-                                         (16, 65536, 256), (2, 1001, 64)]):
+                                         (16, 65536, 256), (2, 1001, 64), (2, 300000, 64), (2, 300001, 63),
+                                         (2, 400000, 1024), (1, 400003, 1021)]):
         for dist in ("randn", "ties"):
             x = make(rows, n, dtype, 500 + seed, dist)
             v, i = api.bucketed_argmax(x, k, interleaved)
