@@ -48,8 +48,41 @@ template <> struct ElemTraits<__nv_bfloat16> {
 
 // ---- streaming loads: the input is read exactly once, keep it out of L1 and
 // mark it evict-first in L2 ------------------------------------------------
+#ifndef ATK_LD_MODE
+#define ATK_LD_MODE 3
+#endif
 __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+#if ATK_LD_MODE == 0
   return __ldcs(reinterpret_cast<const uint4*>(p));
+#elif ATK_LD_MODE == 1
+  return __ldg(reinterpret_cast<const uint4*>(p));
+#elif ATK_LD_MODE == 2
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+#elif ATK_LD_MODE == 3
+  return *reinterpret_cast<const uint4*>(p);
+#elif ATK_LD_MODE == 4
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+#endif
+}
+#ifndef ATK_ST_MODE
+#define ATK_ST_MODE 0
+#endif
+__device__ __forceinline__ void st_out_16(uint4* p, const uint4& v) {
+#if ATK_ST_MODE == 0
+  *p = v;
+#elif ATK_ST_MODE == 1
+  __stcs(p, v);
+#elif ATK_ST_MODE == 2
+  __stcg(p, v);
+#elif ATK_ST_MODE == 3
+  __stwt(p, v);
+#endif
 }
 __device__ __forceinline__ uint32_t ld_stream_4(const void* p) {
   return __ldcs(reinterpret_cast<const unsigned int*>(p));

@@ -39,7 +39,13 @@ struct SweepParams {
   int vec_out;               // 16-byte stores are legal for both outputs
 };
 
-constexpr int kSweepMaxThreads = 256;
+#ifndef ATK_SWEEP_THREADS
+#define ATK_SWEEP_THREADS 128
+#endif
+#ifndef ATK_SWEEP_MINBLOCKS
+#define ATK_SWEEP_MINBLOCKS 1
+#endif
+constexpr int kSweepMaxThreads = ATK_SWEEP_THREADS;
 
 template <int V, int J> struct SweepUnroll {
   // independent 16-byte loads kept in flight per thread
@@ -75,7 +81,7 @@ __device__ __forceinline__ void sweep_consume(float (&qv)[V][J], int (&qi)[V][J]
 }
 
 template <typename T, int J, int V, bool FIRST, bool SKIP>
-__global__ void __launch_bounds__(kSweepMaxThreads)
+__global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
 sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
   using VL = VecLoad<T, V>;
@@ -109,6 +115,44 @@ sweep_kernel(const SweepParams p) {
     long long l = ty;
     // Main loop: U independent loads in flight, then U insertions, stripes in
     // increasing order so the scan rule resolves ties like the reference.
+#if defined(ATK_SWEEP_PIPE)
+    // Software-pipelined: the next batch of U loads is issued before the
+    // current batch is consumed (two register buffers, ping-pong).
+    {
+      const long long batch = static_cast<long long>(U) * S;
+      typename VL::Raw ra[U], rb[U];
+      bool have = l + static_cast<long long>(U - 1) * S < lf;
+      if (have) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) ra[u] = VL::load(ptr + u * step);
+        ptr += U * step;
+      }
+      while (have) {
+        const bool have_b = l + batch + static_cast<long long>(U - 1) * S < lf;
+        if (have_b) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) rb[u] = VL::load(ptr + u * step);
+          ptr += U * step;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          sweep_consume<T, J, V, FIRST, SKIP>(qv, qi, ra[u], static_cast<int>(l) + u * S);
+        l += batch;
+        if (!have_b) break;
+        const bool have_a = l + batch + static_cast<long long>(U - 1) * S < lf;
+        if (have_a) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) ra[u] = VL::load(ptr + u * step);
+          ptr += U * step;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          sweep_consume<T, J, V, FIRST, SKIP>(qv, qi, rb[u], static_cast<int>(l) + u * S);
+        l += batch;
+        have = have_a;
+      }
+    }
+#else
     for (; l + static_cast<long long>(U - 1) * S < lf; l += static_cast<long long>(U) * S) {
       typename VL::Raw raw[U];
 #pragma unroll
@@ -118,6 +162,7 @@ sweep_kernel(const SweepParams p) {
       for (int u = 0; u < U; ++u)
         sweep_consume<T, J, V, FIRST, SKIP>(qv, qi, raw[u], static_cast<int>(l) + u * S);
     }
+#endif
     for (; l < lf; l += S) {
       const typename VL::Raw raw = VL::load(ptr);
       ptr += step;
@@ -197,10 +242,10 @@ sweep_kernel(const SweepParams p) {
   if (kValBytes % 16 == 0 && p.vec_out) {
     const uint4* src = reinterpret_cast<const uint4*>(ov);
 #pragma unroll
-    for (int i = 0; i < kValBytes / 16; ++i) reinterpret_cast<uint4*>(vdst)[i] = src[i];
+    for (int i = 0; i < kValBytes / 16; ++i) st_out_16(reinterpret_cast<uint4*>(vdst) + i, src[i]);
+    const uint4* isrc = reinterpret_cast<const uint4*>(oi);
 #pragma unroll
-    for (int i = 0; i < V * J / 2; ++i)
-      reinterpret_cast<longlong2*>(idst)[i] = make_longlong2(oi[2 * i], oi[2 * i + 1]);
+    for (int i = 0; i < V * J / 2; ++i) st_out_16(reinterpret_cast<uint4*>(idst) + i, isrc[i]);
   } else {
 #pragma unroll
     for (int i = 0; i < V * J; ++i) {
