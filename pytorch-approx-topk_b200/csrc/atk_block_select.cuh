@@ -1,0 +1,99 @@
+// Block-level pieces of the exact select (stage 2), shared by the stand-alone
+// select kernel and by the fused row kernel.
+//
+// Keys are order-preserving 32-bit images of the candidate values, possibly
+// with payload in low bits that `vmask` hides from every comparison.
+#pragma once
+
+#include "atk_common.cuh"
+
+namespace atk {
+
+// One warp: given a 256-bin histogram of the digit under inspection (only keys
+// that match the prefix found so far are counted) pick the bin that contains
+// the need-th largest key.  Bins are walked from 255 downwards.
+// `lane` is the caller's lane id within its warp (blocks may be 2-D, so it is
+// not derived from threadIdx.x here).
+__device__ __forceinline__ void pick_digit(const uint32_t* hist, uint32_t need, int lane, uint32_t* out_digit,
+                                           uint32_t* out_need) {
+  uint32_t h[8];
+  uint32_t total = 0;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    h[t] = hist[255 - 8 * lane - t];
+    total += h[t];
+  }
+  uint32_t incl = total;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += nb;
+  }
+  uint32_t running = incl - total;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    if (running < need && running + h[t] >= need) {
+      *out_digit = 255 - 8 * lane - t;
+      *out_need = need - running;
+    }
+    running += h[t];
+  }
+}
+
+// Exclusive block scan of two boolean flags.  Returns this thread's ranks and
+// the block totals.  wsum: >= 32 words of shared memory; contains one
+// __syncthreads pair, so all threads of the block must call it.  `tid` is the
+// linear thread index, `nthreads` the block size (a multiple of 32, <= 1024).
+__device__ __forceinline__ void block_rank2(bool f0, bool f1, uint32_t* wsum, int tid, int nthreads,
+                                            uint32_t& r0, uint32_t& r1, uint32_t& t0, uint32_t& t1) {
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nwarps = (nthreads + 31) >> 5;
+  const uint32_t m0 = __ballot_sync(0xffffffffu, f0);
+  const uint32_t m1 = __ballot_sync(0xffffffffu, f1);
+  const uint32_t lt = (1u << lane) - 1u;
+  if (lane == 0) wsum[warp] = __popc(m0) | (__popc(m1) << 16);
+  __syncthreads();
+  uint32_t before = 0, all = 0;
+  for (int w = 0; w < nwarps; ++w) {
+    const uint32_t s = wsum[w];
+    if (w < warp) before += s;
+    all += s;
+  }
+  __syncthreads();
+  r0 = (before & 0xffffu) + __popc(m0 & lt);
+  r1 = (before >> 16) + __popc(m1 & lt);
+  t0 = all & 0xffffu;
+  t1 = all >> 16;
+}
+
+// MSB-first radix select over n keys in shared memory: finds the k-th largest
+// masked key `thr` and how many keys equal to it belong to the top k (`need`).
+// `passes` 8-bit digits are examined starting at bit 31.  hist: 256 words,
+// misc: 2 words of shared memory.  All threads of the block must call it; on
+// return every thread holds the same (thr, need).
+__device__ __forceinline__ void block_select_threshold(const uint32_t* keys, int n, uint32_t k, int passes,
+                                                       uint32_t* hist, uint32_t* misc, int tid, int nthreads,
+                                                       uint32_t& thr, uint32_t& need) {
+  uint32_t prefix = 0, mask = 0;
+  need = k;
+#pragma unroll 1
+  for (int pass = 0; pass < passes; ++pass) {
+    const int shift = 24 - 8 * pass;
+    for (int i = tid; i < 256; i += nthreads) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += nthreads) {
+      const uint32_t key = keys[i];
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (tid < 32) pick_digit(hist, need, tid, &misc[0], &misc[1]);
+    __syncthreads();
+    prefix |= misc[0] << shift;
+    mask |= 255u << shift;
+    need = misc[1];
+  }
+  thr = prefix;
+}
+
+}  // namespace atk

@@ -13,6 +13,7 @@
 //  * large rows: several blocks per row; digit histograms, block counts and
 //    the running (prefix, need) state live in a caller-provided workspace.
 #include "atk_select.cuh"
+#include "atk_block_select.cuh"
 
 namespace atk {
 namespace {
@@ -40,62 +41,6 @@ template <> struct KeyOf<__nv_bfloat16> {
   static __device__ __forceinline__ uint32_t key(uint16_t h) { return KeyOf<__half>::key(h); }
 };
 
-// One warp: given a 256-bin histogram of the digit under inspection (only keys
-// that match the prefix found so far are counted) pick the bin that contains
-// the need-th largest key.  Bins are walked from 255 downwards.
-__device__ __forceinline__ void pick_digit(const uint32_t* hist, uint32_t need, uint32_t* out_digit,
-                                           uint32_t* out_need) {
-  const int lane = threadIdx.x & 31;
-  uint32_t h[8];
-  uint32_t total = 0;
-#pragma unroll
-  for (int t = 0; t < 8; ++t) {
-    h[t] = hist[255 - 8 * lane - t];
-    total += h[t];
-  }
-  uint32_t incl = total;
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
-    if (lane >= off) incl += nb;
-  }
-  uint32_t running = incl - total;
-#pragma unroll
-  for (int t = 0; t < 8; ++t) {
-    if (running < need && running + h[t] >= need) {
-      *out_digit = 255 - 8 * lane - t;
-      *out_need = need - running;
-    }
-    running += h[t];
-  }
-}
-
-// Exclusive block scan of two boolean flags.  Returns this thread's ranks and
-// the block totals.  wsum: >= 32 words of shared memory; contains one
-// __syncthreads pair, so all threads of the block must call it.
-__device__ __forceinline__ void block_rank2(bool f0, bool f1, uint32_t* wsum, uint32_t& r0,
-                                            uint32_t& r1, uint32_t& t0, uint32_t& t1) {
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  const int nwarps = (blockDim.x + 31) >> 5;
-  const uint32_t m0 = __ballot_sync(0xffffffffu, f0);
-  const uint32_t m1 = __ballot_sync(0xffffffffu, f1);
-  const uint32_t lt = (1u << lane) - 1u;
-  if (lane == 0) wsum[warp] = __popc(m0) | (__popc(m1) << 16);
-  __syncthreads();
-  uint32_t before = 0, all = 0;
-  for (int w = 0; w < nwarps; ++w) {
-    const uint32_t s = wsum[w];
-    if (w < warp) before += s;
-    all += s;
-  }
-  __syncthreads();
-  r0 = (before & 0xffffu) + __popc(m0 & lt);
-  r1 = (before >> 16) + __popc(m1 & lt);
-  t0 = all & 0xffffu;
-  t1 = all >> 16;
-}
-
 // ------------------------------------------------------------------ small path
 template <typename T>
 __global__ void __launch_bounds__(1024)
@@ -118,23 +63,10 @@ select_small_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 
   for (int i = tid; i < k0; i += nthr) keys[i] = K::key(vrow[i]);
 
-  uint32_t prefix = 0, mask = 0, need = static_cast<uint32_t>(k);
-#pragma unroll 1
-  for (int pass = 0; pass < K::kPasses; ++pass) {
-    const int shift = 24 - 8 * pass;
-    for (int i = tid; i < 256; i += nthr) hist[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < k0; i += nthr) {
-      const uint32_t key = keys[i];
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-    }
-    __syncthreads();
-    if (tid < 32) pick_digit(hist, need, &misc[0], &misc[1]);
-    __syncthreads();
-    prefix |= misc[0] << shift;
-    mask |= 255u << shift;
-    need = misc[1];
-  }
+  __syncthreads();
+  uint32_t prefix, need;
+  block_select_threshold(keys, static_cast<int>(k0), static_cast<uint32_t>(k), K::kPasses, hist, misc, tid, nthr,
+                         prefix, need);
   // prefix is now the k-th largest key; `need` of its copies are taken.
   const uint32_t n_gt = static_cast<uint32_t>(k) - need;
   uint32_t gt_base = 0, eq_base = 0;
@@ -147,7 +79,7 @@ select_small_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
     const bool gt = in && key > prefix;
     const bool eq = in && key == prefix;
     uint32_t r_gt, r_eq, t_gt, t_eq;
-    block_rank2(gt, eq, wsum, r_gt, r_eq, t_gt, t_eq);
+    block_rank2(gt, eq, wsum, tid, nthr, r_gt, r_eq, t_gt, t_eq);
     long long pos = -1;
     if (gt) pos = gt_base + r_gt;
     else if (eq && eq_base + r_eq < need) pos = static_cast<long long>(n_gt) + eq_base + r_eq;
@@ -211,7 +143,7 @@ select_pick_kernel(int pass, long long k, RowState* __restrict__ state,
   } else {
     st = state[row];
   }
-  pick_digit(hist + (row * K::kPasses + pass) * 256, st.need, &res[0], &res[1]);
+  pick_digit(hist + (row * K::kPasses + pass) * 256, st.need, threadIdx.x, &res[0], &res[1]);
   __syncwarp();
   if (threadIdx.x == 0) {
     const int shift = 24 - 8 * pass;
@@ -315,7 +247,7 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
     const bool gt = in && key > thr;
     const bool eq = in && key == thr;
     uint32_t r_gt, r_eq, t_gt, t_eq;
-    block_rank2(gt, eq, wsum, r_gt, r_eq, t_gt, t_eq);
+    block_rank2(gt, eq, wsum, threadIdx.x, blockDim.x, r_gt, r_eq, t_gt, t_eq);
     long long pos = -1;
     if (gt) pos = static_cast<long long>(gt_base) + r_gt;
     else if (eq && eq_base + r_eq < need) pos = n_gt + eq_base + r_eq;

@@ -1,22 +1,26 @@
-// Stage 1 for interleaved buckets: the "column sweep".
+// Stage 1 for interleaved buckets: the "column sweep", and its fused form that
+// also runs the exact select of stage 2 ("row kernel").
 //
 // With interleaved buckets a row of n elements is a row-major matrix of
 // `stripes x b` (b = number of buckets): element i sits in stripe i / b and
 // column (= bucket) i % b, so the per-bucket top-J is a column-wise reduction
 // and every stripe is contiguous in memory.  A thread owns V adjacent columns
 // (V elements = one 16-byte load per stripe when alignment allows, else V = 1)
-// and keeps V queues of J (value, stripe) pairs in registers; threads with the
-// same threadIdx.y walk the same stripes, so a warp always reads contiguous
-// memory whatever b is.  When a row offers too few columns to fill the GPU the
+// and keeps V queues of J entries in registers; threads with the same
+// threadIdx.y walk the same stripes, so a warp always reads contiguous memory
+// whatever b is.  When a row offers too few columns to fill the GPU the
 // stripes are split S ways inside the block (threadIdx.y) and the partial
 // queues are merged through shared memory with the tie rule made explicit.
 //
 // Semantics follow the reference's thread-per-bucket kernel
 // (approx_topk/priority_queue_approx_topk.cu: geometry :25-56, insertion
-// :58-79, scan :81-107, index fix-up :109-119, slot layout :190-200).
+// :58-79, scan :81-107, index fix-up :109-119, slot layout :190-200); the
+// fused form adds what approx_topk/priority_queue.py:85-88 does with
+// torch.topk + gather, without the candidates ever leaving the SM.
 #pragma once
 
-#include "atk_common.cuh"
+#include "atk_block_select.cuh"
+#include "atk_queue.cuh"
 
 namespace atk {
 
@@ -34,6 +38,7 @@ struct SweepParams {
   long long tiles;           // column tiles (blocks) per row
   long long idx_stride;      // reported position = stripe*idx_stride + idx_offset + column
   long long idx_offset;
+  long long k;               // row kernel only: size of the final selection
   int cw;                    // blockDim.x: threads across columns
   int s;                     // blockDim.y: stripe splits inside the block (power of two)
   int vec_out;               // 16-byte stores are legal for both outputs
@@ -46,48 +51,84 @@ struct SweepParams {
 #define ATK_SWEEP_MINBLOCKS 1
 #endif
 constexpr int kSweepMaxThreads = ATK_SWEEP_THREADS;
+constexpr int kRowMaxThreads = 512;
 
-template <int V, int J> struct SweepUnroll {
-  // independent 16-byte loads kept in flight per thread
+template <int V, int WORDS> struct SweepUnroll {
+  // independent 16-byte loads kept in flight per thread; fewer when the
+  // queues themselves take many registers
 #ifdef ATK_DEBUG_U
   static constexpr int kU = ATK_DEBUG_U;
 #else
-  static constexpr int kU = (V * J <= 16) ? 8 : 4;
+  static constexpr int kU = (V * WORDS <= 32) ? 8 : 4;
 #endif
 };
 
-template <typename T, int J, int V, bool FIRST, bool SKIP>
-__device__ __forceinline__ void sweep_consume(float (&qv)[V][J], int (&qi)[V][J],
-                                              const typename VecLoad<T, V>::Raw& raw, int stripe) {
-  float v[V];
-  VecLoad<T, V>::widen(raw, v);
-  bool head[V];
+// Scan this thread's stripes (ty, ty+S, ...) of its V columns starting at c0.
+template <typename T, typename Q, int V, bool SKIP>
+__device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, const T* xrow, long long c0,
+                                           int ty, int S) {
+  using VL = VecLoad<T, V>;
+  constexpr int U = SweepUnroll<V, Q::kWords>::kU;
+  const long long lf = p.l_full;
+  const long long step = static_cast<long long>(S) * p.stripe_stride;
+  const T* ptr = xrow + c0 + static_cast<long long>(ty) * p.stripe_stride;
+  long long l = ty;
+  // Main loop: U independent loads in flight, then U insertions, stripes in
+  // increasing order so the scan rule resolves ties like the reference.
+  for (; l + static_cast<long long>(U - 1) * S < lf; l += static_cast<long long>(U) * S) {
+    typename VL::Raw raw[U];
 #pragma unroll
-  for (int e = 0; e < V; ++e) head[e] = !(qv[e][0] > v[e]);
-  if (SKIP) {
-    // Long columns: almost no element beats the current J-th best, so test
-    // the V heads first and only run the insertion network when one does.
-    bool any = false;
+    for (int u = 0; u < U; ++u) raw[u] = VL::load(ptr + u * step);
+    ptr += U * step;
 #pragma unroll
-    for (int e = 0; e < V; ++e) any = any || head[e];
-    if (any) {
+    for (int u = 0; u < U; ++u) Q::template consume<V, SKIP>(q, raw[u], static_cast<int>(l) + u * S);
+  }
+  for (; l < lf; l += S) {
+    const typename VL::Raw raw = VL::load(ptr);
+    ptr += step;
+    Q::template consume<V, SKIP>(q, raw, static_cast<int>(l));
+  }
+  // Ragged last stripe (b does not divide n): only columns < rem exist.  It
+  // belongs to the split that would visit stripe l_full, and is that thread's
+  // highest stripe, so scan order is preserved.
+  if (p.rem > 0 && l == lf) {
+    const T* last = xrow + lf * p.stripe_stride + c0;
 #pragma unroll
-      for (int e = 0; e < V; ++e) queue_push_scan<J, FIRST>(qv[e], qi[e], v[e], stripe, head[e]);
+    for (int e = 0; e < V; ++e) {
+      if (c0 + e < p.rem) q[e].push_tail(VecLoad<T, 1>::load(last + e), static_cast<int>(lf));
     }
-  } else {
-#pragma unroll
-    for (int e = 0; e < V; ++e) queue_push_scan<J, FIRST>(qv[e], qi[e], v[e], stripe, head[e]);
   }
 }
 
-template <typename T, int J, int V, bool FIRST, bool SKIP>
+// Merge the S partial queues of every column: a binary tree over threadIdx.y.
+// Word w of column-thread tx in plane y lives at ((y * V*kWords) + w) * cw + tx,
+// so a warp touches consecutive words.  Needs (S/2) * V*kWords * cw words.
+template <typename Q, int V>
+__device__ __forceinline__ void sweep_merge(Q (&q)[V], uint32_t* smem, int cw, int tx, int ty, int S) {
+  constexpr int W = Q::kWords;
+  for (int h = S >> 1; h >= 1; h >>= 1) {
+    if (ty >= h && ty < 2 * h) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) q[e].store(smem + (static_cast<size_t>(ty - h) * (V * W) + e * W) * cw + tx, cw);
+    }
+    __syncthreads();
+    if (ty < h) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) q[e].merge(smem + (static_cast<size_t>(ty) * (V * W) + e * W) * cw + tx, cw);
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Stage 1 only: every block handles one tile of columns of one row and writes
+// the J candidates of each bucket (slot = bucket*J + q, ascending).
+template <typename T, typename Q, int J, int V, bool SKIP>
 __global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
 sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
-  using VL = VecLoad<T, V>;
   using Bits = typename Tr::Bits;
-  constexpr int U = SweepUnroll<V, J>::kU;
-  extern __shared__ __align__(16) unsigned char sweep_smem[];
+  extern __shared__ __align__(16) uint32_t sweep_smem[];
 
   const int tx = threadIdx.x;
   const int ty = threadIdx.y;
@@ -98,125 +139,12 @@ sweep_kernel(const SweepParams p) {
   const bool active = c0 < p.b;
   const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
 
-  float qv[V][J];
-  int qi[V][J];
+  Q q[V];
 #pragma unroll
-  for (int e = 0; e < V; ++e)
-#pragma unroll
-    for (int q = 0; q < J; ++q) {
-      qv[e][q] = -INFINITY;
-      qi[e][q] = FIRST ? kSentinelFirst : kSentinelLast;
-    }
+  for (int e = 0; e < V; ++e) q[e].init();
 
-  if (active) {
-    const long long lf = p.l_full;
-    const long long step = static_cast<long long>(S) * p.stripe_stride;
-    const T* ptr = xrow + c0 + static_cast<long long>(ty) * p.stripe_stride;
-    long long l = ty;
-    // Main loop: U independent loads in flight, then U insertions, stripes in
-    // increasing order so the scan rule resolves ties like the reference.
-#if defined(ATK_SWEEP_PIPE)
-    // Software-pipelined: the next batch of U loads is issued before the
-    // current batch is consumed (two register buffers, ping-pong).
-    {
-      const long long batch = static_cast<long long>(U) * S;
-      typename VL::Raw ra[U], rb[U];
-      bool have = l + static_cast<long long>(U - 1) * S < lf;
-      if (have) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) ra[u] = VL::load(ptr + u * step);
-        ptr += U * step;
-      }
-      while (have) {
-        const bool have_b = l + batch + static_cast<long long>(U - 1) * S < lf;
-        if (have_b) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) rb[u] = VL::load(ptr + u * step);
-          ptr += U * step;
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          sweep_consume<T, J, V, FIRST, SKIP>(qv, qi, ra[u], static_cast<int>(l) + u * S);
-        l += batch;
-        if (!have_b) break;
-        const bool have_a = l + batch + static_cast<long long>(U - 1) * S < lf;
-        if (have_a) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) ra[u] = VL::load(ptr + u * step);
-          ptr += U * step;
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          sweep_consume<T, J, V, FIRST, SKIP>(qv, qi, rb[u], static_cast<int>(l) + u * S);
-        l += batch;
-        have = have_a;
-      }
-    }
-#else
-    for (; l + static_cast<long long>(U - 1) * S < lf; l += static_cast<long long>(U) * S) {
-      typename VL::Raw raw[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) raw[u] = VL::load(ptr + u * step);
-      ptr += U * step;
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-        sweep_consume<T, J, V, FIRST, SKIP>(qv, qi, raw[u], static_cast<int>(l) + u * S);
-    }
-#endif
-    for (; l < lf; l += S) {
-      const typename VL::Raw raw = VL::load(ptr);
-      ptr += step;
-      sweep_consume<T, J, V, FIRST, SKIP>(qv, qi, raw, static_cast<int>(l));
-    }
-    // Ragged last stripe (b does not divide n): only columns < rem exist.
-    // It belongs to the split that would visit stripe l_full, and is that
-    // thread's highest stripe, so scan order is preserved.
-    if (p.rem > 0 && l == lf) {
-      const T* last = xrow + lf * p.stripe_stride + c0;
-#pragma unroll
-      for (int e = 0; e < V; ++e) {
-        if (c0 + e < p.rem) {
-          float v1[1];
-          VecLoad<T, 1>::widen(VecLoad<T, 1>::load(last + e), v1);
-          queue_push_scan<J, FIRST>(qv[e], qi[e], v1[0], static_cast<int>(lf));
-        }
-      }
-    }
-  }
-
-  // Merge the S partial queues of every column: a binary tree over
-  // threadIdx.y.  Entry (e, q) of column-thread tx in plane y lives at
-  // ((y * V*J) + e*J + q) * cw + tx, so a warp touches consecutive words.
-  if (S > 1) {
-    const int cw = p.cw;
-    float* mv = reinterpret_cast<float*>(sweep_smem);
-    int* mi = reinterpret_cast<int*>(mv + static_cast<size_t>(S / 2) * (V * J) * cw);
-    for (int h = S >> 1; h >= 1; h >>= 1) {
-      if (ty >= h && ty < 2 * h) {
-        const int plane = ty - h;
-#pragma unroll
-        for (int e = 0; e < V; ++e)
-#pragma unroll
-          for (int q = 0; q < J; ++q) {
-            const int off = (plane * (V * J) + e * J + q) * cw + tx;
-            mv[off] = qv[e][q];
-            mi[off] = qi[e][q];
-          }
-      }
-      __syncthreads();
-      if (ty < h) {
-#pragma unroll
-        for (int e = 0; e < V; ++e)
-#pragma unroll
-          for (int q = 0; q < J; ++q) {
-            const int off = (ty * (V * J) + e * J + q) * cw + tx;
-            queue_push_ranked<J, FIRST>(qv[e], qi[e], mv[off], mi[off]);
-          }
-      }
-      __syncthreads();
-    }
-  }
-
+  if (active) sweep_scan<T, Q, V, SKIP>(q, p, xrow, c0, ty, S);
+  if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
   if (!active || ty != 0) return;
 
   // Write-out: bucket c owns slots c*J .. c*J+J-1, ascending queue order.
@@ -225,15 +153,15 @@ sweep_kernel(const SweepParams p) {
 #pragma unroll
   for (int e = 0; e < V; ++e)
 #pragma unroll
-    for (int q = 0; q < J; ++q) {
-      float val = qv[e][q];
-      long long stripe = qi[e][q];
-      if (FIRST && qi[e][q] == kSentinelFirst) {  // empty (all padding) bucket
-        val = Tr::lowest();
-        stripe = 0;
+    for (int j = 0; j < J; ++j) {
+      if (q[e].empty(j)) {  // all-padding bucket of the arg-max entry point
+        ov[e * J + j] = Tr::narrow(Tr::lowest());
+        oi[e * J + j] = p.idx_offset + c0 + e;
+      } else {
+        const long long stripe = q[e].stripe(j);
+        ov[e * J + j] = q[e].value_bits(j, xrow + stripe * p.stripe_stride + c0 + e);
+        oi[e * J + j] = stripe * p.idx_stride + p.idx_offset + c0 + e;
       }
-      ov[e * J + q] = Tr::narrow(val);
-      oi[e * J + q] = stripe * p.idx_stride + p.idx_offset + c0 + e;
     }
   const long long out_base = row * p.out_row_stride + c0 * J;
   Bits* vdst = static_cast<Bits*>(p.out_vals) + out_base;
@@ -255,6 +183,103 @@ sweep_kernel(const SweepParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Fused stage 1 + stage 2: one block owns a whole row (all b columns), so the
+// b*J candidates are gathered in shared memory, the k-th largest is found by
+// radix select and the k winners are written directly.  The candidate buffer
+// never touches global memory.  Ordering of the output and the treatment of
+// ties equal the stand-alone select kernel's (candidates above the threshold
+// in slot order, then the lowest slots among those equal to it).
+template <typename T, typename Q, int J, int V, bool SKIP>
+__global__ void __launch_bounds__(kRowMaxThreads)
+row_kernel(const SweepParams p) {
+  using Tr = ElemTraits<T>;
+  using Bits = typename Tr::Bits;
+  extern __shared__ __align__(16) uint32_t sweep_smem[];
+
+  const int tx = threadIdx.x;
+  const int ty = threadIdx.y;
+  const int S = p.s;
+  const int nthr = p.cw * S;
+  const int tid = ty * p.cw + tx;
+  const long long row = blockIdx.x;
+  const long long c0 = static_cast<long long>(tx) * V;
+  const bool active = c0 < p.b;
+  const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
+
+  Q q[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) q[e].init();
+  if (active) sweep_scan<T, Q, V, SKIP>(q, p, xrow, c0, ty, S);
+  if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
+
+  // Candidate buffers (reuse the merge scratch; the merge ended with a barrier).
+  const int k0 = static_cast<int>(p.b) * J;
+  uint32_t* ckey = sweep_smem;                       // [k0] masked compare key (+ stripe when packed)
+  uint32_t* cstripe = ckey + k0;                     // [k0] stripe (float queues only)
+  uint32_t* hist = Q::kPacked ? ckey + k0 : cstripe + k0;  // [256]
+  uint32_t* misc = hist + 256;                       // [2]
+  uint32_t* wsum = misc + 2;                         // [32]
+  if (active && ty == 0) {
+#pragma unroll
+    for (int e = 0; e < V; ++e)
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const int slot = static_cast<int>(c0 + e) * J + j;
+        if (Q::kPacked) {
+          ckey[slot] = q[e].select_key(j) | static_cast<uint32_t>(q[e].stripe(j));
+        } else {
+          ckey[slot] = q[e].select_key(j);
+          cstripe[slot] = static_cast<uint32_t>(q[e].stripe(j));
+        }
+      }
+  }
+  __syncthreads();
+
+  constexpr uint32_t kValMask = Q::kPacked ? 0xffff0000u : 0xffffffffu;
+  constexpr int kPasses = Q::kPacked ? 2 : 4;
+  uint32_t thr, need;
+  block_select_threshold(ckey, k0, static_cast<uint32_t>(p.k), kPasses, hist, misc, tid, nthr, thr, need);
+  thr &= kValMask;
+
+  const uint32_t n_gt = static_cast<uint32_t>(p.k) - need;
+  uint32_t gt_base = 0, eq_base = 0;
+  Bits* ovrow = static_cast<Bits*>(p.out_vals) + row * p.out_row_stride;
+  long long* oirow = p.out_idx + row * p.out_row_stride;
+  for (int base = 0; base < k0; base += nthr) {
+    const int slot = base + tid;
+    const bool in = slot < k0;
+    const uint32_t full = in ? ckey[slot] : 0u;
+    const uint32_t key = full & kValMask;
+    const bool gt = in && key > thr;
+    const bool eq = in && key == thr;
+    uint32_t r_gt, r_eq, t_gt, t_eq;
+    block_rank2(gt, eq, wsum, tid, nthr, r_gt, r_eq, t_gt, t_eq);
+    long long pos = -1;
+    if (gt) pos = gt_base + r_gt;
+    else if (eq && eq_base + r_eq < need) pos = static_cast<long long>(n_gt) + eq_base + r_eq;
+    if (pos >= 0) {
+      const long long col = slot / J;
+      long long stripe;
+      Bits bits;
+      if (Q::kPacked) {
+        stripe = full & 0xffffu;
+        const uint32_t o = full >> 16;
+        bits = (o == 0x8000u) ? static_cast<Bits>(ld_stream_2(xrow + stripe * p.stripe_stride + col))
+                              : static_cast<Bits>(ord16_inverse(o));
+      } else {
+        stripe = cstripe[slot];
+        const uint32_t u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+        bits = Tr::narrow(__uint_as_float(u));
+      }
+      ovrow[pos] = bits;
+      oirow[pos] = stripe * p.idx_stride + p.idx_offset + col;
+    }
+    gt_base += t_gt;
+    eq_base += t_eq;
+  }
+}
+
 // Arguments of the typed launchers (one translation unit per element type).
 struct SweepLaunch {
   const void* x;
@@ -265,12 +290,17 @@ struct SweepLaunch {
   long long stripe_stride;  // == b for a plain row
   long long idx_stride;     // == b for a plain row
   long long idx_offset;
+  long long k;              // > 0: fuse the exact select of the k best of the b*j candidates
   int j;
   bool first_wins;          // k_b = 1 arg-max conventions (J must be 1)
   int sm_count;
   cudaStream_t stream;
 };
 
+// Each returns ATK_OK or an error; with a.k > 0 they return kRowKernelDeclined
+// without launching when the fused kernel does not fit the geometry, and the
+// caller then runs stage 1 and the select separately.
+constexpr int kRowKernelDeclined = 1;
 int launch_sweep_f32(const SweepLaunch& a);
 int launch_sweep_f16(const SweepLaunch& a);
 int launch_sweep_bf16(const SweepLaunch& a);

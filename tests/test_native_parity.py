@@ -178,6 +178,31 @@ def test_topk_two_stage_matches_oracle(dtype, j, k_mult):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j,k_mult", [(1, 2), (2, 2), (3, 2), (4, 2), (2, 4), (1, 4)])
+def test_fused_row_kernel_matches_oracle(dtype, j, k_mult):
+    # Enough rows for the one-block-per-row kernel that keeps the candidates in
+    # shared memory: aligned, ragged (b does not divide n), unaligned rows, long
+    # columns, and the largest candidate count it takes.
+    for seed, (rows, n, k) in enumerate([(96, 4096, 96), (80, 10007, 48), (77, 8190, 24), (100, 131072, 12),
+                                         (75, 65536, 2040)]):
+        k = (k // j) * j if (k * k_mult) % j else k
+        if (k * k_mult) % j:
+            continue
+        for dist in ("randn", "ties"):
+            x = make(rows, n, dtype, 800 + seed, dist)
+            v, i = api.topk(x, k, j, k_mult, True)
+            ov, oi = oracle.topk(x.cpu(), k, j, k_mult, True)
+            assert_valid_selection(x, v, i, ov)
+            if dtype == torch.float32 and dist == "randn":
+                assert_pairs_identical(v, i, ov, oi)
+            # the fused kernel and the two-kernel path agree bit for bit (same tie choices)
+            cv, ci = api.stage1(x, k * k_mult, j, True)
+            sv, si = api.select(cv, ci, k)
+            if not (dtype != torch.float32 and dist == "ties"):
+                assert torch.equal(bits(v), bits(sv)) and torch.equal(i, si), (rows, n, k, dist)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("interleaved", [True, False])
 def test_bucketed_argmax_matches_oracle(dtype, interleaved):
     for seed, (rows, n, k) in enumerate([(2, 20, 3), (3, 1000, 7), (4, 4096, 256), (2, 10, 4), (1, 5, 8),
