@@ -113,7 +113,6 @@ int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_st
     a.stripe_stride = b;
     a.idx_stride = b;
     a.idx_offset = 0;
-    a.k = 0;
     a.j = j;
     a.first_wins = false;
     a.sm_count = sm_count_of_current_device();
@@ -156,7 +155,6 @@ int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols, 
   a.stripe_stride = cols;
   a.idx_stride = total_buckets;
   a.idx_offset = col_offset;
-  a.k = 0;
   a.j = j;
   a.first_wins = false;
   a.sm_count = sm_count_of_current_device();
@@ -214,30 +212,6 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
   if (s == 0) return ATK_ERR_BAD_DTYPE;
   if (k == 0 || rows == 0) return ATK_OK;
   const int64_t k0 = k * k_mult;
-  if (interleaved && j >= 1 && j <= 4 && k0 % j == 0 && k0 <= n) {
-    // Fused path: one block per row keeps the candidates in shared memory.
-    int rc0 = check_common(x, dtype, rows, n, row_stride, out_vals, out_idx, out_row_stride);
-    if (rc0 != ATK_OK) return rc0;
-    SweepLaunch a;
-    a.x = x;
-    a.out_vals = out_vals;
-    a.out_idx = reinterpret_cast<long long*>(out_idx);
-    a.rows = rows;
-    a.n = n;
-    a.row_stride = row_stride;
-    a.out_row_stride = out_row_stride;
-    a.b = k0 / j;
-    a.stripe_stride = a.b;
-    a.idx_stride = a.b;
-    a.idx_offset = 0;
-    a.k = k;
-    a.j = j;
-    a.first_wins = false;
-    a.sm_count = sm_count_of_current_device();
-    a.stream = static_cast<cudaStream_t>(stream);
-    rc0 = sweep_dispatch(a, dtype);
-    if (rc0 != kRowKernelDeclined) return rc0;
-  }
   const size_t need = atk_topk_workspace_bytes(dtype, rows, n, k, j, k_mult);
   if (workspace == nullptr || workspace_bytes < need) return ATK_ERR_WORKSPACE;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
@@ -273,7 +247,6 @@ int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64
     a.stripe_stride = k;
     a.idx_stride = k;
     a.idx_offset = 0;
-    a.k = 0;
     a.j = 1;
     a.first_wins = true;
     a.sm_count = sm_count_of_current_device();

@@ -67,6 +67,17 @@ __device__ __forceinline__ void block_rank2(bool f0, bool f1, uint32_t* wsum, in
   t1 = all >> 16;
 }
 
+// Histogram update for a whole (converged) warp: lanes holding the same digit
+// elect one of them to add their count, so keys that concentrate on a few
+// digits (16-bit floats do) cost one shared-memory atomic per distinct digit
+// instead of one per key.
+__device__ __forceinline__ void hist_add_warp(uint32_t* hist, uint32_t digit, bool valid, int lane) {
+  const uint32_t active = __ballot_sync(0xffffffffu, valid);
+  if (!valid) return;
+  const uint32_t peers = __match_any_sync(active, digit);
+  if (lane == __ffs(peers) - 1) atomicAdd(&hist[digit], static_cast<uint32_t>(__popc(peers)));
+}
+
 // MSB-first radix select over n keys in shared memory: finds the k-th largest
 // masked key `thr` and how many keys equal to it belong to the top k (`need`).
 // `passes` 8-bit digits are examined starting at bit 31.  hist: 256 words,
@@ -82,9 +93,10 @@ __device__ __forceinline__ void block_select_threshold(const uint32_t* keys, int
     const int shift = 24 - 8 * pass;
     for (int i = tid; i < 256; i += nthreads) hist[i] = 0;
     __syncthreads();
-    for (int i = tid; i < n; i += nthreads) {
-      const uint32_t key = keys[i];
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+    for (int base = 0; base < n; base += nthreads) {  // warp-uniform trip count
+      const int i = base + tid;
+      const uint32_t key = i < n ? keys[i] : 0u;
+      hist_add_warp(hist, (key >> shift) & 255u, i < n && (key & mask) == prefix, tid & 31);
     }
     __syncthreads();
     if (tid < 32) pick_digit(hist, need, tid, &misc[0], &misc[1]);

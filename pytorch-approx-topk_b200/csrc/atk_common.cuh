@@ -70,6 +70,15 @@ __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
   return r;
 #endif
 }
+__device__ __forceinline__ uint2 ld_stream_8(const void* p) {
+#if ATK_LD_MODE == 0
+  return __ldcs(reinterpret_cast<const uint2*>(p));
+#elif ATK_LD_MODE == 1
+  return __ldg(reinterpret_cast<const uint2*>(p));
+#else
+  return *reinterpret_cast<const uint2*>(p);
+#endif
+}
 #ifndef ATK_ST_MODE
 #define ATK_ST_MODE 0
 #endif
@@ -117,6 +126,14 @@ template <> struct VecLoad<__nv_bfloat16, 8> {
     v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
   }
 };
+template <> struct VecLoad<__nv_bfloat16, 4> {
+  using Raw = uint2;
+  static __device__ __forceinline__ Raw load(const __nv_bfloat16* p) { return ld_stream_8(p); }
+  static __device__ __forceinline__ void widen(const Raw& r, float (&v)[4]) {
+    v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+    v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+  }
+};
 template <> struct VecLoad<__nv_bfloat16, 1> {
   using Raw = uint16_t;
   static __device__ __forceinline__ Raw load(const __nv_bfloat16* p) { return ld_stream_2(p); }
@@ -131,6 +148,19 @@ template <> struct VecLoad<__half, 8> {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+};
+template <> struct VecLoad<__half, 4> {
+  using Raw = uint2;
+  static __device__ __forceinline__ Raw load(const __half* p) { return ld_stream_8(p); }
+  static __device__ __forceinline__ void widen(const Raw& r, float (&v)[4]) {
+    const uint32_t w[2] = {r.x, r.y};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
       const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
       v[2 * i] = f.x;
       v[2 * i + 1] = f.y;

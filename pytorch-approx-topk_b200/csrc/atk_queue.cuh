@@ -28,6 +28,9 @@ template <typename T, int J, bool FIRST>
 struct FloatQueue {
   static constexpr int kWords = 2 * J;  // 32-bit words per queue in shared memory
   static constexpr bool kPacked = false;
+  static constexpr int kCols = 1;       // columns served by one queue object
+  static constexpr int kJ = J;
+  static constexpr bool kFirst = FIRST;
   float v[J];
   int s[J];
 
@@ -108,11 +111,22 @@ __device__ __forceinline__ uint16_t ord16_inverse(uint32_t o) {
   return static_cast<uint16_t>(o >= 0x8000u ? (o ^ 0x8000u) : (0x8000u | (0x8000u - o)));
 }
 
+// The 32-bit words of a vector load of 16-bit elements (two columns per word).
+__device__ __forceinline__ void raw_words(const uint4& r, uint32_t (&w)[4]) {
+  w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+}
+__device__ __forceinline__ void raw_words(const uint2& r, uint32_t (&w)[2]) {
+  w[0] = r.x; w[1] = r.y;
+}
+
 template <typename T, int J, bool FIRST>
 struct PackedQueue {
   static_assert(sizeof(T) == 2, "packed queues are for 16-bit element types");
   static constexpr int kWords = J;
   static constexpr bool kPacked = true;
+  static constexpr int kCols = 1;
+  static constexpr int kJ = J;
+  static constexpr bool kFirst = FIRST;
   uint32_t k[J];  // ascending; 0 = never filled
 
   __device__ __forceinline__ void init() {
@@ -143,10 +157,11 @@ struct PackedQueue {
       const uint32_t key = ((ord16x2(raw) & 0xffffu) << 16) | lo;
       if (!SKIP || key > q[0].k[0]) q[0].push(key);
     } else {
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t w[V / 2];
+      raw_words(raw, w);
       uint32_t key[V];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < V / 2; ++i) {
         const uint32_t o = ord16x2(w[i]);
         key[2 * i] = (o << 16) | lo;
         key[2 * i + 1] = (o & 0xffff0000u) | lo;
@@ -188,6 +203,113 @@ struct PackedQueue {
     return ord16_inverse(o);
   }
   __device__ __forceinline__ uint32_t select_key(int q) const { return k[q] & 0xffff0000u; }
+};
+
+
+// ---------------------------------------------------------------- Simd16Queue
+// Scan-time layout for 16-bit inputs on the vector path: one queue serves TWO
+// adjacent columns, values kept as raw fp16x2 / bf16x2 words and stripes as
+// 16-bit pairs.  The J compares and 2J-1 min/max of an insertion are packed
+// half-precision instructions that work on both columns at once (and issue on
+// the FMA pipe), the stripe moves are bitwise selects under the compare masks.
+// Elements arrive in increasing stripe order, so `>=` lets the later element
+// pass equal ones (LAST wins) and `>` keeps the earlier one (FIRST wins), the
+// same rule as the reference's scan.  NaNs never enter.  After the scan the
+// queues are converted to PackedQueue entries, which carry the merge across
+// stripe splits and the write-out.
+template <typename T> struct Half2Ops;
+template <> struct Half2Ops<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static constexpr uint32_t kNegInf2 = 0xff80ff80u;
+  static __device__ __forceinline__ T2 as2(uint32_t w) { return *reinterpret_cast<T2*>(&w); }
+  static __device__ __forceinline__ uint32_t bits(T2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) { return bits(__hmax2(as2(a), as2(b))); }
+  static __device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) { return bits(__hmin2(as2(a), as2(b))); }
+  static __device__ __forceinline__ uint32_t ge(uint32_t a, uint32_t b) { return __hge2_mask(as2(a), as2(b)); }
+  static __device__ __forceinline__ uint32_t gt(uint32_t a, uint32_t b) { return __hgt2_mask(as2(a), as2(b)); }
+};
+template <> struct Half2Ops<__half> {
+  using T2 = __half2;
+  static constexpr uint32_t kNegInf2 = 0xfc00fc00u;
+  static __device__ __forceinline__ T2 as2(uint32_t w) { return *reinterpret_cast<T2*>(&w); }
+  static __device__ __forceinline__ uint32_t bits(T2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) { return bits(__hmax2(as2(a), as2(b))); }
+  static __device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) { return bits(__hmin2(as2(a), as2(b))); }
+  static __device__ __forceinline__ uint32_t ge(uint32_t a, uint32_t b) { return __hge2_mask(as2(a), as2(b)); }
+  static __device__ __forceinline__ uint32_t gt(uint32_t a, uint32_t b) { return __hgt2_mask(as2(a), as2(b)); }
+};
+
+template <typename T, int J, bool FIRST>
+struct Simd16Queue {
+  static_assert(sizeof(T) == 2, "SIMD queues are for 16-bit element types");
+  using Ops = Half2Ops<T>;
+  static constexpr int kCols = 2;
+  static constexpr int kWords = 2 * J;
+  uint32_t v[J];  // value pairs, ascending per half; low half = even column
+  uint32_t s[J];  // stripe pairs
+
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int q = 0; q < J; ++q) {
+      v[q] = Ops::kNegInf2;
+      s[q] = 0u;
+    }
+  }
+
+  static __device__ __forceinline__ uint32_t pass_mask(uint32_t x, uint32_t q) {
+    return FIRST ? Ops::gt(x, q) : Ops::ge(x, q);
+  }
+  static __device__ __forceinline__ uint32_t sel(uint32_t m, uint32_t a, uint32_t b) { return (a & m) | (b & ~m); }
+
+  // x: value pair, sp: stripe pair, m0: pass_mask(x, v[0]) already evaluated
+  __device__ __forceinline__ void push(uint32_t x, uint32_t sp, uint32_t m0) {
+    uint32_t m[J];
+    m[0] = m0;
+#pragma unroll
+    for (int q = 1; q < J; ++q) m[q] = pass_mask(x, v[q]);
+    uint32_t nv[J], ns[J];
+#pragma unroll
+    for (int q = 0; q + 1 < J; ++q) {
+      nv[q] = Ops::min2(Ops::max2(x, v[q]), v[q + 1]);
+      ns[q] = sel(m[q + 1], s[q + 1], sel(m[q], sp, s[q]));
+    }
+    nv[J - 1] = Ops::max2(x, v[J - 1]);
+    ns[J - 1] = sel(m[J - 1], sp, s[J - 1]);
+#pragma unroll
+    for (int q = 0; q < J; ++q) {
+      v[q] = nv[q];
+      s[q] = ns[q];
+    }
+  }
+
+  // One vector load of V columns feeds V/2 queues.
+  template <int V, bool SKIP>
+  static __device__ __forceinline__ void consume(Simd16Queue (&q)[V / 2], const typename VecLoad<T, V>::Raw& raw,
+                                                 int stripe) {
+    static_assert(V == 8 || V == 4, "the SIMD queues need a vector path");
+    uint32_t w[V / 2];
+    raw_words(raw, w);
+    const uint32_t sp = static_cast<uint32_t>(stripe) * 0x00010001u;
+    uint32_t m0[V / 2];
+    uint32_t any = 0u;
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      m0[i] = pass_mask(w[i], q[i].v[0]);
+      any |= m0[i];
+    }
+    if (SKIP) {
+      if (any == 0u) return;
+    }
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) q[i].push(w[i], sp, m0[i]);
+  }
+
+  // Entry j of column `half` (0 = even column) as a PackedQueue key.
+  __device__ __forceinline__ uint32_t packed_key(int j, int half) const {
+    const uint32_t raw = half ? (v[j] >> 16) : (v[j] & 0xffffu);
+    const uint32_t st = half ? (s[j] >> 16) : (s[j] & 0xffffu);
+    return ((ord16x2(raw) & 0xffffu) << 16) | PackedQueue<T, J, FIRST>::low(static_cast<int>(st));
+  }
 };
 
 }  // namespace atk

@@ -8,8 +8,8 @@
 // followed by the first `need` candidates equal to T, both in candidate-slot
 // order, so the result is deterministic.
 //
-//  * small rows (k0 <= kSmallMaxK0): one block per row, keys live in shared
-//    memory, a single launch;
+//  * small rows (k0 <= kSmallMaxK0): one block per row, keys live in
+//    registers, a single launch;
 //  * large rows: several blocks per row; digit histograms, block counts and
 //    the running (prefix, need) state live in a caller-provided workspace.
 #include "atk_select.cuh"
@@ -18,7 +18,7 @@
 namespace atk {
 namespace {
 
-constexpr int kSmallMaxK0 = 32768;   // 128 KB of keys in shared memory
+constexpr int kSmallMaxK0 = 32768;   // 1024 threads x 32 candidates in registers
 constexpr int kChunk = 16384;        // candidates per block on the large path
 constexpr int kLargeThreads = 256;
 
@@ -42,53 +42,111 @@ template <> struct KeyOf<__nv_bfloat16> {
 };
 
 // ------------------------------------------------------------------ small path
-template <typename T>
+// One block per row.  Thread t owns the ITEMS consecutive candidate slots
+// [t*ITEMS, (t+1)*ITEMS): keys stay in registers through the radix passes, and
+// because slots are blocked per thread one block-wide scan of the per-thread
+// (greater, equal) counts gives every winner its output position in slot order.
+template <typename T, int ITEMS>
 __global__ void __launch_bounds__(1024)
-select_small_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
-                    const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride,
-                    long long k, typename ElemTraits<T>::Bits* __restrict__ out_vals,
-                    long long* __restrict__ out_idx, long long out_row_stride) {
+select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
+                  const long long* __restrict__ cand_idx, int k0, long long cand_row_stride, int k,
+                  typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
+                  long long out_row_stride, int vec_ok) {
   using K = KeyOf<T>;
-  extern __shared__ __align__(16) uint32_t select_smem[];
-  uint32_t* keys = select_smem;
-  uint32_t* hist = keys + k0;
-  uint32_t* misc = hist + 256;   // [0] digit, [1] need
-  uint32_t* wsum = misc + 2;     // 32 words
+  using Bits = typename ElemTraits<T>::Bits;
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t misc[2];
+  __shared__ uint32_t wsum[32];
 
   const int tid = threadIdx.x;
   const int nthr = blockDim.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
   const long long row = blockIdx.x;
-  const auto* vrow = cand_vals + row * cand_row_stride;
+  const Bits* vrow = cand_vals + row * cand_row_stride;
   const long long* irow = cand_idx + row * cand_row_stride;
+  const int slot0 = tid * ITEMS;
 
-  for (int i = tid; i < k0; i += nthr) keys[i] = K::key(vrow[i]);
+  __align__(16) Bits raw[ITEMS];
+  uint32_t key[ITEMS];
+  constexpr int kRawBytes = ITEMS * static_cast<int>(sizeof(Bits));
+  if (vec_ok && kRawBytes % 16 == 0 && slot0 + ITEMS <= k0) {
+#pragma unroll
+    for (int i = 0; i < kRawBytes / 16; ++i)
+      reinterpret_cast<uint4*>(raw)[i] = reinterpret_cast<const uint4*>(vrow + slot0)[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) raw[i] = slot0 + i < k0 ? vrow[slot0 + i] : Bits(0);
+  }
+  // Slots past the end get key 0; every use below is guarded by the slot bound.
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) key[i] = slot0 + i < k0 ? K::key(raw[i]) : 0u;
 
+  uint32_t prefix = 0, mask = 0, need = static_cast<uint32_t>(k);
+#pragma unroll 1
+  for (int pass = 0; pass < K::kPasses; ++pass) {
+    const int shift = 24 - 8 * pass;
+    for (int i = tid; i < 256; i += nthr) hist[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i)
+      if (slot0 + i < k0 && (key[i] & mask) == prefix) atomicAdd(&hist[(key[i] >> shift) & 255u], 1u);
+    __syncthreads();
+    if (tid < 32) pick_digit(hist, need, tid, &misc[0], &misc[1]);
+    __syncthreads();
+    prefix |= misc[0] << shift;
+    mask |= 255u << shift;
+    need = misc[1];
+  }
+
+  // per-thread counts, then one block-wide exclusive scan of (greater | equal << 16)
+  uint32_t mine = 0;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const bool in = slot0 + i < k0;
+    mine += (in && key[i] > prefix) ? 1u : 0u;
+    mine += (in && key[i] == prefix) ? 0x10000u : 0u;
+  }
+  uint32_t incl = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += nb;
+  }
+  if (lane == 31) wsum[warp] = incl;
   __syncthreads();
-  uint32_t prefix, need;
-  block_select_threshold(keys, static_cast<int>(k0), static_cast<uint32_t>(k), K::kPasses, hist, misc, tid, nthr,
-                         prefix, need);
-  // prefix is now the k-th largest key; `need` of its copies are taken.
-  const uint32_t n_gt = static_cast<uint32_t>(k) - need;
-  uint32_t gt_base = 0, eq_base = 0;
-  auto* ovrow = out_vals + row * out_row_stride;
-  long long* oirow = out_idx + row * out_row_stride;
-  for (int base = 0; base < k0; base += nthr) {
-    const int i = base + tid;
-    const bool in = i < k0;
-    const uint32_t key = in ? keys[i] : 0u;
-    const bool gt = in && key > prefix;
-    const bool eq = in && key == prefix;
-    uint32_t r_gt, r_eq, t_gt, t_eq;
-    block_rank2(gt, eq, wsum, tid, nthr, r_gt, r_eq, t_gt, t_eq);
-    long long pos = -1;
-    if (gt) pos = gt_base + r_gt;
-    else if (eq && eq_base + r_eq < need) pos = static_cast<long long>(n_gt) + eq_base + r_eq;
-    if (pos >= 0) {
-      ovrow[pos] = vrow[i];
-      oirow[pos] = irow[i];
+  if (warp == 0) {
+    const int nwarps = (nthr + 31) >> 5;
+    const uint32_t w = lane < nwarps ? wsum[lane] : 0u;
+    uint32_t wi = w;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t nb = __shfl_up_sync(0xffffffffu, wi, off);
+      if (lane >= off) wi += nb;
     }
-    gt_base += t_gt;
-    eq_base += t_eq;
+    wsum[lane] = wi - w;  // exclusive prefix of the warp totals
+  }
+  __syncthreads();
+  const uint32_t excl = wsum[warp] + incl - mine;
+  uint32_t gt_rank = excl & 0xffffu;
+  uint32_t eq_rank = excl >> 16;
+  const uint32_t n_gt = static_cast<uint32_t>(k) - need;
+  Bits* ovrow = out_vals + row * out_row_stride;
+  long long* oirow = out_idx + row * out_row_stride;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    if (slot0 + i >= k0) break;
+    long long pos = -1;
+    if (key[i] > prefix) {
+      pos = gt_rank++;
+    } else if (key[i] == prefix) {
+      if (eq_rank < need) pos = static_cast<long long>(n_gt) + eq_rank;
+      ++eq_rank;
+    }
+    if (pos >= 0) {
+      ovrow[pos] = raw[i];
+      oirow[pos] = irow[slot0 + i];
+    }
   }
 }
 
@@ -117,9 +175,11 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   long long end = begin + kChunk;
   if (end > k0) end = k0;
   const auto* vrow = cand_vals + row * cand_row_stride;
-  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
-    const uint32_t key = K::key(vrow[i]);
-    if ((key & mask) == prefix) atomicAdd(&sh[(key >> shift) & 255u], 1u);
+  for (long long base = begin; base < end; base += blockDim.x) {  // warp-uniform trip count
+    const long long i = base + threadIdx.x;
+    uint32_t key = 0u;
+    if (i < end) key = K::key(vrow[i]);
+    hist_add_warp(sh, (key >> shift) & 255u, i < end && (key & mask) == prefix, threadIdx.x & 31);
   }
   __syncthreads();
   uint32_t* gh = hist + (row * K::kPasses + pass) * 256;
@@ -279,17 +339,31 @@ int select_typed(const SelectLaunch& a) {
   const Bits* cv = static_cast<const Bits*>(a.cand_vals);
   Bits* ov = static_cast<Bits*>(a.out_vals);
   if (a.k0 <= kSmallMaxK0) {
-    int threads = 128;
-    while (threads < 1024 && threads * 8 < a.k0) threads *= 2;
-    const size_t smem = sizeof(uint32_t) * (static_cast<size_t>(a.k0) + 256 + 2 + 32);
-    if (smem > 48 * 1024) {
-      if (cudaFuncSetAttribute(select_small_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem)) != cudaSuccess)
-        return ATK_ERR_CUDA;
-    }
     if (a.rows >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
-    select_small_kernel<T><<<static_cast<unsigned>(a.rows), threads, smem, a.stream>>>(
-        cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, ov, a.out_idx, a.out_row_stride);
+    const int k0 = static_cast<int>(a.k0);
+    const int k = static_cast<int>(a.k);
+    const int s = static_cast<int>(sizeof(Bits));
+    const int vec_ok = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * s) % 16 == 0);
+    const unsigned rows = static_cast<unsigned>(a.rows);
+    auto threads_for = [&](int items) {
+      int t = (k0 + items - 1) / items;
+      return ((t + 31) / 32) * 32;
+    };
+    // 16 bytes of values per thread when that keeps the block within 1024
+    // threads, more items per thread for longer rows.
+    constexpr int kBase = 16 / static_cast<int>(sizeof(Bits));
+    if (threads_for(kBase) <= 1024)
+      select_row_kernel<T, kBase><<<rows, threads_for(kBase), 0, a.stream>>>(
+          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
+    else if (threads_for(2 * kBase) <= 1024)
+      select_row_kernel<T, 2 * kBase><<<rows, threads_for(2 * kBase), 0, a.stream>>>(
+          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
+    else if (threads_for(4 * kBase) <= 1024)
+      select_row_kernel<T, 4 * kBase><<<rows, threads_for(4 * kBase), 0, a.stream>>>(
+          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
+    else
+      select_row_kernel<T, 32><<<rows, threads_for(32), 0, a.stream>>>(
+          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
   }

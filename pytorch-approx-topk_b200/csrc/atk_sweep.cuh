@@ -1,5 +1,4 @@
-// Stage 1 for interleaved buckets: the "column sweep", and its fused form that
-// also runs the exact select of stage 2 ("row kernel").
+// Stage 1 for interleaved buckets: the "column sweep".
 //
 // With interleaved buckets a row of n elements is a row-major matrix of
 // `stripes x b` (b = number of buckets): element i sits in stripe i / b and
@@ -14,12 +13,9 @@
 //
 // Semantics follow the reference's thread-per-bucket kernel
 // (approx_topk/priority_queue_approx_topk.cu: geometry :25-56, insertion
-// :58-79, scan :81-107, index fix-up :109-119, slot layout :190-200); the
-// fused form adds what approx_topk/priority_queue.py:85-88 does with
-// torch.topk + gather, without the candidates ever leaving the SM.
+// :58-79, scan :81-107, index fix-up :109-119, slot layout :190-200).
 #pragma once
 
-#include "atk_block_select.cuh"
 #include "atk_queue.cuh"
 
 namespace atk {
@@ -38,7 +34,6 @@ struct SweepParams {
   long long tiles;           // column tiles (blocks) per row
   long long idx_stride;      // reported position = stripe*idx_stride + idx_offset + column
   long long idx_offset;
-  long long k;               // row kernel only: size of the final selection
   int cw;                    // blockDim.x: threads across columns
   int s;                     // blockDim.y: stripe splits inside the block (power of two)
   int vec_out;               // 16-byte stores are legal for both outputs
@@ -51,7 +46,6 @@ struct SweepParams {
 #define ATK_SWEEP_MINBLOCKS 1
 #endif
 constexpr int kSweepMaxThreads = ATK_SWEEP_THREADS;
-constexpr int kRowMaxThreads = 512;
 
 template <int V, int WORDS> struct SweepUnroll {
   // independent 16-byte loads kept in flight per thread; fewer when the
@@ -63,12 +57,15 @@ template <int V, int WORDS> struct SweepUnroll {
 #endif
 };
 
-// Scan this thread's stripes (ty, ty+S, ...) of its V columns starting at c0.
-template <typename T, typename Q, int V, bool SKIP>
-__device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, const T* xrow, long long c0,
-                                           int ty, int S) {
+// Walk this thread's complete stripes (ty, ty+S, ...) of its V columns starting
+// at c0, feeding every 16-byte (or scalar) load to QS::consume.  Returns the
+// first stripe number not visited (== l_full for the thread that owns the
+// ragged last stripe).
+template <typename T, typename QS, int V, bool SKIP>
+__device__ __forceinline__ long long sweep_walk(QS (&qs)[V / QS::kCols], const SweepParams& p, const T* xrow,
+                                                long long c0, int ty, int S) {
   using VL = VecLoad<T, V>;
-  constexpr int U = SweepUnroll<V, Q::kWords>::kU;
+  constexpr int U = SweepUnroll<V / QS::kCols, QS::kWords>::kU;
   const long long lf = p.l_full;
   const long long step = static_cast<long long>(S) * p.stripe_stride;
   const T* ptr = xrow + c0 + static_cast<long long>(ty) * p.stripe_stride;
@@ -81,21 +78,43 @@ __device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, cons
     for (int u = 0; u < U; ++u) raw[u] = VL::load(ptr + u * step);
     ptr += U * step;
 #pragma unroll
-    for (int u = 0; u < U; ++u) Q::template consume<V, SKIP>(q, raw[u], static_cast<int>(l) + u * S);
+    for (int u = 0; u < U; ++u) QS::template consume<V, SKIP>(qs, raw[u], static_cast<int>(l) + u * S);
   }
   for (; l < lf; l += S) {
     const typename VL::Raw raw = VL::load(ptr);
     ptr += step;
-    Q::template consume<V, SKIP>(q, raw, static_cast<int>(l));
+    QS::template consume<V, SKIP>(qs, raw, static_cast<int>(l));
+  }
+  return l;
+}
+
+// Scan into q[V].  With SIMD (16-bit inputs on the vector path) the walk runs
+// on two-column SIMD queues that are then converted to packed entries.
+template <typename T, typename Q, int V, bool SKIP, bool SIMD>
+__device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, const T* xrow, long long c0,
+                                           int ty, int S) {
+  long long l;
+  if constexpr (SIMD) {
+    using QS = Simd16Queue<T, Q::kJ, Q::kFirst>;
+    QS qs[V / 2];
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) qs[i].init();
+    l = sweep_walk<T, QS, V, SKIP>(qs, p, xrow, c0, ty, S);
+#pragma unroll
+    for (int e = 0; e < V; ++e)
+#pragma unroll
+      for (int j = 0; j < Q::kJ; ++j) q[e].k[j] = qs[e / 2].packed_key(j, e & 1);
+  } else {
+    l = sweep_walk<T, Q, V, SKIP>(q, p, xrow, c0, ty, S);
   }
   // Ragged last stripe (b does not divide n): only columns < rem exist.  It
   // belongs to the split that would visit stripe l_full, and is that thread's
   // highest stripe, so scan order is preserved.
-  if (p.rem > 0 && l == lf) {
-    const T* last = xrow + lf * p.stripe_stride + c0;
+  if (p.rem > 0 && l == p.l_full) {
+    const T* last = xrow + p.l_full * p.stripe_stride + c0;
 #pragma unroll
     for (int e = 0; e < V; ++e) {
-      if (c0 + e < p.rem) q[e].push_tail(VecLoad<T, 1>::load(last + e), static_cast<int>(lf));
+      if (c0 + e < p.rem) q[e].push_tail(VecLoad<T, 1>::load(last + e), static_cast<int>(p.l_full));
     }
   }
 }
@@ -123,7 +142,7 @@ __device__ __forceinline__ void sweep_merge(Q (&q)[V], uint32_t* smem, int cw, i
 // ---------------------------------------------------------------------------
 // Stage 1 only: every block handles one tile of columns of one row and writes
 // the J candidates of each bucket (slot = bucket*J + q, ascending).
-template <typename T, typename Q, int J, int V, bool SKIP>
+template <typename T, typename Q, int J, int V, bool SKIP, bool SIMD>
 __global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
 sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
@@ -143,7 +162,7 @@ sweep_kernel(const SweepParams p) {
 #pragma unroll
   for (int e = 0; e < V; ++e) q[e].init();
 
-  if (active) sweep_scan<T, Q, V, SKIP>(q, p, xrow, c0, ty, S);
+  if (active) sweep_scan<T, Q, V, SKIP, SIMD>(q, p, xrow, c0, ty, S);
   if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
   if (!active || ty != 0) return;
 
@@ -154,7 +173,8 @@ sweep_kernel(const SweepParams p) {
   for (int e = 0; e < V; ++e)
 #pragma unroll
     for (int j = 0; j < J; ++j) {
-      if (q[e].empty(j)) {  // all-padding bucket of the arg-max entry point
+      // all-padding bucket of the arg-max entry point (k > n, or the padded tail)
+      if (Q::kFirst && p.l_full + (c0 + e < p.rem ? 1 : 0) == 0) {
         ov[e * J + j] = Tr::narrow(Tr::lowest());
         oi[e * J + j] = p.idx_offset + c0 + e;
       } else {
@@ -183,103 +203,6 @@ sweep_kernel(const SweepParams p) {
   }
 }
 
-// ---------------------------------------------------------------------------
-// Fused stage 1 + stage 2: one block owns a whole row (all b columns), so the
-// b*J candidates are gathered in shared memory, the k-th largest is found by
-// radix select and the k winners are written directly.  The candidate buffer
-// never touches global memory.  Ordering of the output and the treatment of
-// ties equal the stand-alone select kernel's (candidates above the threshold
-// in slot order, then the lowest slots among those equal to it).
-template <typename T, typename Q, int J, int V, bool SKIP>
-__global__ void __launch_bounds__(kRowMaxThreads)
-row_kernel(const SweepParams p) {
-  using Tr = ElemTraits<T>;
-  using Bits = typename Tr::Bits;
-  extern __shared__ __align__(16) uint32_t sweep_smem[];
-
-  const int tx = threadIdx.x;
-  const int ty = threadIdx.y;
-  const int S = p.s;
-  const int nthr = p.cw * S;
-  const int tid = ty * p.cw + tx;
-  const long long row = blockIdx.x;
-  const long long c0 = static_cast<long long>(tx) * V;
-  const bool active = c0 < p.b;
-  const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
-
-  Q q[V];
-#pragma unroll
-  for (int e = 0; e < V; ++e) q[e].init();
-  if (active) sweep_scan<T, Q, V, SKIP>(q, p, xrow, c0, ty, S);
-  if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
-
-  // Candidate buffers (reuse the merge scratch; the merge ended with a barrier).
-  const int k0 = static_cast<int>(p.b) * J;
-  uint32_t* ckey = sweep_smem;                       // [k0] masked compare key (+ stripe when packed)
-  uint32_t* cstripe = ckey + k0;                     // [k0] stripe (float queues only)
-  uint32_t* hist = Q::kPacked ? ckey + k0 : cstripe + k0;  // [256]
-  uint32_t* misc = hist + 256;                       // [2]
-  uint32_t* wsum = misc + 2;                         // [32]
-  if (active && ty == 0) {
-#pragma unroll
-    for (int e = 0; e < V; ++e)
-#pragma unroll
-      for (int j = 0; j < J; ++j) {
-        const int slot = static_cast<int>(c0 + e) * J + j;
-        if (Q::kPacked) {
-          ckey[slot] = q[e].select_key(j) | static_cast<uint32_t>(q[e].stripe(j));
-        } else {
-          ckey[slot] = q[e].select_key(j);
-          cstripe[slot] = static_cast<uint32_t>(q[e].stripe(j));
-        }
-      }
-  }
-  __syncthreads();
-
-  constexpr uint32_t kValMask = Q::kPacked ? 0xffff0000u : 0xffffffffu;
-  constexpr int kPasses = Q::kPacked ? 2 : 4;
-  uint32_t thr, need;
-  block_select_threshold(ckey, k0, static_cast<uint32_t>(p.k), kPasses, hist, misc, tid, nthr, thr, need);
-  thr &= kValMask;
-
-  const uint32_t n_gt = static_cast<uint32_t>(p.k) - need;
-  uint32_t gt_base = 0, eq_base = 0;
-  Bits* ovrow = static_cast<Bits*>(p.out_vals) + row * p.out_row_stride;
-  long long* oirow = p.out_idx + row * p.out_row_stride;
-  for (int base = 0; base < k0; base += nthr) {
-    const int slot = base + tid;
-    const bool in = slot < k0;
-    const uint32_t full = in ? ckey[slot] : 0u;
-    const uint32_t key = full & kValMask;
-    const bool gt = in && key > thr;
-    const bool eq = in && key == thr;
-    uint32_t r_gt, r_eq, t_gt, t_eq;
-    block_rank2(gt, eq, wsum, tid, nthr, r_gt, r_eq, t_gt, t_eq);
-    long long pos = -1;
-    if (gt) pos = gt_base + r_gt;
-    else if (eq && eq_base + r_eq < need) pos = static_cast<long long>(n_gt) + eq_base + r_eq;
-    if (pos >= 0) {
-      const long long col = slot / J;
-      long long stripe;
-      Bits bits;
-      if (Q::kPacked) {
-        stripe = full & 0xffffu;
-        const uint32_t o = full >> 16;
-        bits = (o == 0x8000u) ? static_cast<Bits>(ld_stream_2(xrow + stripe * p.stripe_stride + col))
-                              : static_cast<Bits>(ord16_inverse(o));
-      } else {
-        stripe = cstripe[slot];
-        const uint32_t u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
-        bits = Tr::narrow(__uint_as_float(u));
-      }
-      ovrow[pos] = bits;
-      oirow[pos] = stripe * p.idx_stride + p.idx_offset + col;
-    }
-    gt_base += t_gt;
-    eq_base += t_eq;
-  }
-}
-
 // Arguments of the typed launchers (one translation unit per element type).
 struct SweepLaunch {
   const void* x;
@@ -290,17 +213,12 @@ struct SweepLaunch {
   long long stripe_stride;  // == b for a plain row
   long long idx_stride;     // == b for a plain row
   long long idx_offset;
-  long long k;              // > 0: fuse the exact select of the k best of the b*j candidates
   int j;
   bool first_wins;          // k_b = 1 arg-max conventions (J must be 1)
   int sm_count;
   cudaStream_t stream;
 };
 
-// Each returns ATK_OK or an error; with a.k > 0 they return kRowKernelDeclined
-// without launching when the fused kernel does not fit the geometry, and the
-// caller then runs stage 1 and the select separately.
-constexpr int kRowKernelDeclined = 1;
 int launch_sweep_f32(const SweepLaunch& a);
 int launch_sweep_f16(const SweepLaunch& a);
 int launch_sweep_bf16(const SweepLaunch& a);

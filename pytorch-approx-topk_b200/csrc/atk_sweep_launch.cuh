@@ -1,4 +1,4 @@
-// Host-side launch logic of the column sweep and the fused row kernel, included
+// Host-side launch logic of the column sweep, included
 // by one translation unit per element type so the template instantiations
 // compile in parallel.
 #pragma once
@@ -35,7 +35,6 @@ inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
   p.stripe_stride = a.stripe_stride;
   p.idx_stride = a.idx_stride;
   p.idx_offset = a.idx_offset;
-  p.k = a.k;
   const uintptr_t ov = reinterpret_cast<uintptr_t>(a.out_vals);
   const uintptr_t oi = reinterpret_cast<uintptr_t>(a.out_idx);
   p.vec_out = (ov % 16 == 0) && (oi % 16 == 0) && ((a.out_row_stride * elem_size) % 16 == 0) &&
@@ -43,7 +42,7 @@ inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
 }
 
 // ---- stage 1 only ---------------------------------------------------------
-template <typename T, typename Q, int J, int V>
+template <typename T, typename Q, int J, int V, bool SIMD>
 int launch_stage1(const SweepLaunch& a) {
   SweepParams p;
   fill_common(p, a, static_cast<int>(sizeof(T)));
@@ -81,73 +80,28 @@ int launch_stage1(const SweepLaunch& a) {
   skip = false;
 #endif
   if (skip)
-    sweep_kernel<T, Q, J, V, true><<<grid, block, smem, a.stream>>>(p);
+    sweep_kernel<T, Q, J, V, true, SIMD><<<grid, block, smem, a.stream>>>(p);
   else
-    sweep_kernel<T, Q, J, V, false><<<grid, block, smem, a.stream>>>(p);
+    sweep_kernel<T, Q, J, V, false, SIMD><<<grid, block, smem, a.stream>>>(p);
   note_launch();
   return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
-}
-
-// ---- fused stage 1 + select -----------------------------------------------
-template <typename T, typename Q, int J, int V>
-int launch_row(const SweepLaunch& a) {
-  SweepParams p;
-  fill_common(p, a, static_cast<int>(sizeof(T)));
-  const long long col_threads = (a.b + V - 1) / V;
-  const long long k0 = a.b * J;
-  // One block must own every column of the row, its candidates must fit in
-  // shared memory, and there must be enough rows to occupy the GPU.
-  if (col_threads > kRowMaxThreads || k0 > 16384 || a.rows < a.sm_count / 2 || a.rows >= (1ll << 31) ||
-      p.l_full + 1 >= (1ll << 31))
-    return kRowKernelDeclined;
-  long long S = floor_pow2(kRowMaxThreads / col_threads);
-  const long long by_work = floor_pow2(p.l_full >= 4 ? p.l_full / 4 : 1);
-  if (by_work < S) S = by_work;
-  // keep whole warps so that the block-wide ranking sees full ballots
-  long long cw = col_threads;
-  while ((cw * S) % 32 != 0) ++cw;
-  if (cw * S > kRowMaxThreads) return kRowKernelDeclined;
-  p.tiles = 1;
-  p.cw = static_cast<int>(cw);
-  p.s = static_cast<int>(S);
-  const size_t merge_words = S > 1 ? static_cast<size_t>(S / 2) * (V * Q::kWords) * cw : 0;
-  const size_t cand_words = static_cast<size_t>(k0) * (Q::kPacked ? 1 : 2);
-  const size_t smem = ((merge_words > cand_words ? merge_words : cand_words) + 256 + 2 + 32) * 4;
-  if (smem > 200 * 1024) return kRowKernelDeclined;
-  bool skip = (p.l_full / S) >= 256;
-  const dim3 grid(static_cast<unsigned>(a.rows));
-  const dim3 block(static_cast<unsigned>(cw), static_cast<unsigned>(S));
-  cudaError_t e = cudaSuccess;
-  if (skip) {
-    if (smem > 48 * 1024)
-      e = cudaFuncSetAttribute(row_kernel<T, Q, J, V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem));
-    if (e != cudaSuccess) return ATK_ERR_CUDA;
-    row_kernel<T, Q, J, V, true><<<grid, block, smem, a.stream>>>(p);
-  } else {
-    if (smem > 48 * 1024)
-      e = cudaFuncSetAttribute(row_kernel<T, Q, J, V, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem));
-    if (e != cudaSuccess) return ATK_ERR_CUDA;
-    row_kernel<T, Q, J, V, false><<<grid, block, smem, a.stream>>>(p);
-  }
-  note_launch();
-  return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
-}
-
-template <typename T, typename Q, int J, int V>
-int launch_either(const SweepLaunch& a) {
-  return a.k > 0 ? launch_row<T, Q, J, V>(a) : launch_stage1<T, Q, J, V>(a);
 }
 
 // Queue layout: 16-bit inputs use packed 32-bit entries whenever the stripe
-// number fits in 16 bits; everything else uses (float, int) pairs.
+// number fits in 16 bits (scanned with the two-column SIMD queues on the
+// vector path); everything else uses (float, int) pairs.
 template <typename T, int J, int V, bool FIRST>
 int launch_by_queue(const SweepLaunch& a) {
   if constexpr (sizeof(T) == 2) {
-    if (a.n / a.b + 1 <= 65536) return launch_either<T, PackedQueue<T, J, FIRST>, J, V>(a);
+    if (a.n / a.b + 1 <= 65536) {
+#ifdef ATK_NO_SIMD16
+      return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, false>(a);
+#else
+      return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4)>(a);
+#endif
+    }
   }
-  return launch_either<T, FloatQueue<T, J, FIRST>, J, V>(a);
+  return launch_stage1<T, FloatQueue<T, J, FIRST>, J, V, false>(a);
 }
 
 template <typename T, int V>
@@ -165,15 +119,31 @@ int launch_by_j(const SweepLaunch& a) {
   }
 }
 
-// Vector path: every 16-byte load must be aligned and lie inside one stripe.
+// Columns per thread.  A vector of V elements is loaded per stripe, so it must
+// be aligned and lie inside one stripe.  16-byte vectors by default; queues of
+// three or four entries take half as many columns per thread (8-byte loads for
+// the 16-bit types), which halves their register footprint and doubles the
+// number of threads that hide each other's latency.
 template <typename T>
 int launch_sweep(const SweepLaunch& a) {
   constexpr int s = static_cast<int>(sizeof(T));
   constexpr int kVec = ElemTraits<T>::kVec;
   if (a.rows <= 0 || a.b <= 0) return ATK_OK;
-  const bool vec = (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) && ((a.row_stride * s) % 16 == 0) &&
-                   ((a.stripe_stride * s) % 16 == 0) && (a.b % kVec == 0);
-  return vec ? launch_by_j<T, kVec>(a) : launch_by_j<T, 1>(a);
+  auto fits = [&](int v) {
+    const int bytes = v * s;
+    return (reinterpret_cast<uintptr_t>(a.x) % bytes == 0) && ((a.row_stride * s) % bytes == 0) &&
+           ((a.stripe_stride * s) % bytes == 0) && (a.b % v == 0);
+  };
+  if constexpr (sizeof(T) == 2) {
+#ifndef ATK_NO_HALF_VECTOR
+    if (a.j >= 3 && fits(4)) return launch_by_j<T, 4>(a);
+#endif
+    if (fits(kVec)) return launch_by_j<T, kVec>(a);
+    if (fits(4)) return launch_by_j<T, 4>(a);
+    return launch_by_j<T, 1>(a);
+  } else {
+    return fits(kVec) ? launch_by_j<T, kVec>(a) : launch_by_j<T, 1>(a);
+  }
 }
 
 }  // namespace sweep_detail
