@@ -1,19 +1,20 @@
 """Benchmark of the bucketed approximate top-k hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4j1|c4j2|c5b]
 
-Workload (synthetic, seeded): the configuration the headline metric is quoted
-on — fp32 rows of 2^20 elements ~N(0,1), k = 2^16, j = 2, k_mult = 1 (2^15
-interleaved buckets, no second stage), 128 rows per GPU.  A step is one pass of
-the operator over one such batch.  With N > 1 (launched by torchrun, one rank
-per GPU) every rank owns its own 128 rows: rows are independent, so there is no
-data-path collective and scaling is weak; at N = 8 the job is the 1024-row
-row-sharded configuration.
+Default workload "c2" (synthetic, seeded) is the configuration the headline
+metric is quoted on — fp32 rows of 2^20 elements ~N(0,1), k = 2^16, j = 2,
+k_mult = 1 (2^15 interleaved buckets, no second stage), 128 rows per GPU.  A
+step is one pass of the operator over one such batch.  With N > 1 (launched by
+torchrun, one rank per GPU) every rank owns its own rows: rows are independent,
+so there is no data-path collective and scaling is weak; at N = 8 the job is the
+1024-row row-sharded configuration.  "c5b" is one long row whose bucket groups
+are sharded over the GPUs (strong scaling; one all-gather of candidates).
 
 One JSON line is printed by rank 0:
   value      rows/s of the whole job, inputs resident in HBM, timed with CUDA
              events on the launching stream, max over ranks
-  roofline   the stage-1 kernel against the measured HBM copy bandwidth
+  roofline   the step against the measured HBM copy bandwidth
   e2e        the same metric through the host-buffer API: pinned host rows in,
              pinned host results out, copies inside the timed region
   cpu_baseline  the reference's CPU path (torch ops on the host's cores) on a
@@ -41,23 +42,40 @@ for _p in (str(ROOT), str(ROOT / "pytorch-approx-topk_b200")):
 
 import torch  # noqa: E402
 
-ROWS_PER_GPU = 128
-N = 1 << 20
-K = 1 << 16
-J = 2
-K_MULT = 1
-ELEM = 4
 METRIC = "approx top-k rows/s"
-CONFIG = {"workload": "fp32 128x2^20 rows per GPU ~N(0,1) seeded, k=2^16, j=2, k_mult=1, interleaved "
-                      "(2^15 buckets, no second stage), int64 indices",
-          "rows_per_gpu": ROWS_PER_GPU, "n": N, "k": K, "j": J, "k_mult": K_MULT,
-          "sharding": "rows, no collective"}
-# Algorithmic bytes of one launch: read every input element once, write the k
-# (value, int64 index) pairs once.
-ALG_BYTES_PER_ROW = N * ELEM + K * (ELEM + 8)
-# dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch on this
-# workload, from the ncu capture summarised under profiles/ (None until taken).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+# Workloads (all dim=-1, interleaved, int64 indices).  "c2" is the headline
+# configuration; the others are the remaining reference configurations and are
+# selected with --workload.  rows are PER GPU (weak scaling, rows are sharded
+# with no collective) except for "c5b", one long row whose bucket groups are
+# sharded over the GPUs (strong scaling, one all-gather of candidates).
+WORKLOADS = {
+    "c2": dict(dtype="float32", rows=128, n=1 << 20, k=1 << 16, j=2, k_mult=1, data="randn",
+               text="fp32 128x2^20 rows per GPU ~N(0,1) seeded, k=2^16, j=2, k_mult=1, interleaved "
+                    "(2^15 buckets, no second stage), int64 indices"),
+    "c3": dict(dtype="bfloat16", rows=1024, n=65536, k=2048, j=4, k_mult=2, data="attention",
+               text="bf16 1024x65536 rows per GPU, values q.K^T/sqrt(128) with q,K ~N(0,1) head_dim 128, "
+                    "k=2048, j=4, k_mult=2 (exact select over 4096 candidates)"),
+    "c4j1": dict(dtype="float16", rows=4096, n=128256, k=64, j=1, k_mult=4, data="spikes",
+                 text="fp16 4096x128256 logits per GPU ~N(0,2) + 16 spikes of +8 per row, k=64, j=1, k_mult=4"),
+    "c4j2": dict(dtype="float16", rows=4096, n=128256, k=64, j=2, k_mult=4, data="spikes",
+                 text="fp16 4096x128256 logits per GPU ~N(0,2) + 16 spikes of +8 per row, k=64, j=2, k_mult=4"),
+    "c5b": dict(dtype="float32", rows=1, n=1 << 32, k=1 << 20, j=4, k_mult=2, data="randn", long_row=True,
+                text="one fp32 row of 2^32 ~N(0,1), k=2^20, j=4, k_mult=2; bucket groups sharded over the "
+                     "GPUs, all-gather of candidates, exact select over 2^21 candidates"),
+}
+DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+DTYPE_TAG = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
+# dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch on the
+# headline workload, from the ncu capture summarised under profiles/.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c2": None}
+
+
+def alg_bytes(w: dict, rows: int) -> int:
+    """Algorithmic bytes of one step: read every input element once, write the
+    k (value, int64 index) pairs once."""
+    s = torch.empty(0, dtype=DTYPES[w["dtype"]]).element_size()
+    return rows * (w["n"] * s + w["k"] * (s + 8))
 
 
 def measured_hbm_peak() -> tuple[float, str]:
@@ -117,55 +135,103 @@ class ClockSampler:
                 "window": "timed region plus an untimed continuation of the same step loop"}
 
 
-def make_rows(rows: int, seed: int, device) -> torch.Tensor:
+def make_input(w: dict, rows: int, seed: int, device) -> torch.Tensor:
+    """Seeded synthetic rows with the shape and value distribution of the workload."""
     g = torch.Generator(device=device).manual_seed(seed)
-    return torch.randn(rows, N, device=device, generator=g, dtype=torch.float32)
+    n, dtype = w["n"], DTYPES[w["dtype"]]
+    if w["data"] == "randn":
+        if rows * n <= (1 << 30):
+            return torch.randn(rows, n, device=device, generator=g).to(dtype)
+        x = torch.empty(rows, n, device=device, dtype=dtype)
+        flat = x.view(-1)
+        for off in range(0, flat.numel(), 1 << 28):     # 2^28-element chunks
+            end = min(off + (1 << 28), flat.numel())
+            flat[off:end] = torch.randn(end - off, device=device, generator=g).to(dtype)
+        return x
+    if w["data"] == "attention":
+        # scores of one query against n keys, head_dim 128, built 32 rows at a time
+        x = torch.empty(rows, n, device=device, dtype=dtype)
+        for r0 in range(0, rows, 32):
+            nr = min(32, rows - r0)
+            keys = torch.randn(nr, n, 128, device=device, generator=g)
+            q = torch.randn(nr, 1, 128, device=device, generator=g)
+            x[r0:r0 + nr] = (q @ keys.transpose(-1, -2) / 128 ** 0.5).squeeze(1).to(dtype)
+        return x
+    if w["data"] == "spikes":
+        x = torch.empty(rows, n, device=device, dtype=dtype)
+        for r0 in range(0, rows, 512):
+            nr = min(512, rows - r0)
+            blk = 2.0 * torch.randn(nr, n, device=device, generator=g)
+            pos = torch.rand(nr, n, device=device, generator=g).topk(16, dim=-1).indices
+            blk.scatter_add_(1, pos, torch.full_like(pos, 8.0, dtype=blk.dtype))
+            x[r0:r0 + nr] = blk.to(dtype)
+        return x
+    raise ValueError(w["data"])
 
 
-def cpu_path_rate(target_seconds: float, threads: int) -> dict:
-    """Reference CPU path (oracle/torch_cpu_path.py) on whole 128-row batches."""
+def cpu_path_rate(w: dict, target_seconds: float, threads: int) -> dict:
+    """The reference's CPU path (oracle/torch_cpu_path.py) on a bounded sample."""
     from oracle.torch_cpu_path import bucketed_topk_cpu
 
     torch.set_num_threads(threads)
-    x = torch.randn(ROWS_PER_GPU, N, generator=torch.Generator().manual_seed(0))
-    bucketed_topk_cpu(x[:8], K, J, K_MULT, True)  # warm the thread pool
+    rows = min(w["rows"], 128)
+    n = min(w["n"], 1 << 26)            # the long row is sampled by a 2^26-element slice
+    scale = w["n"] // n
+    k = max(w["k"] // scale, w["j"])
+    x = make_input(dict(w, n=n, data="randn" if w["data"] != "spikes" else "randn"), rows, 0, "cpu")
+    bucketed_topk_cpu(x[: max(1, rows // 16)], k, w["j"], w["k_mult"], True)  # warm the thread pool
     reps, t0 = 0, time.perf_counter()
     while True:
-        bucketed_topk_cpu(x, K, J, K_MULT, True)
+        bucketed_topk_cpu(x, k, w["j"], w["k_mult"], True)
         reps += 1
         dt = time.perf_counter() - t0
-        if dt >= target_seconds or reps >= 200:
+        if dt >= target_seconds or reps >= 500:
             break
-    return {"value": reps * ROWS_PER_GPU / dt, "unit": "rows/s", "cores": threads, "kind": "port",
-            "sample": f"{reps} passes over the full {ROWS_PER_GPU}x2^20 fp32 batch in {dt:.1f} s "
-                      f"(torch CPU ops restating the reference's autobucket path, {threads} threads)"}
+    sample = (f"{reps} passes over {rows}x{n} {w['dtype']} rows (k={k}) in {dt:.1f} s, torch CPU ops restating "
+              f"the reference's autobucket path, {threads} threads")
+    if scale > 1:
+        sample += f"; a 1/{scale} slice of the row with the same bucket length, rate scaled to full rows"
+    return {"value": reps * rows / dt / scale, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample}
+
+
+def config_of(w: dict, name: str) -> dict:
+    return {"workload": w["text"], "name": name, "rows_per_gpu": w["rows"], "n": w["n"], "k": w["k"],
+            "j": w["j"], "k_mult": w["k_mult"],
+            "sharding": "bucket groups of the row + all-gather of candidates" if w.get("long_row")
+            else "rows, no collective"}
 
 
 def run_reference(args, rank: int) -> int:
+    """Reference arm: the reference's own CPU path on the host cores (rank 0 only)."""
     if rank != 0:
         return 0
+    w = WORKLOADS[args.workload]
     threads = os.cpu_count() or 1
     from oracle.torch_cpu_path import bucketed_topk_cpu
 
     torch.set_num_threads(threads)
-    sample_rows = 32  # one step = a bounded sample of the batch
-    x = torch.randn(sample_rows, N, generator=torch.Generator().manual_seed(0))
+    sample_rows = min(w["rows"], 32)     # one step = a bounded sample of the batch
+    n = min(w["n"], 1 << 26)
+    scale = w["n"] // n
+    k = max(w["k"] // scale, w["j"])
+    x = make_input(dict(w, n=n, data="randn"), sample_rows, 0, "cpu")
     for _ in range(args.warmup):
-        bucketed_topk_cpu(x, K, J, K_MULT, True)
+        bucketed_topk_cpu(x, k, w["j"], w["k_mult"], True)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        bucketed_topk_cpu(x, K, J, K_MULT, True)
+        bucketed_topk_cpu(x, k, w["j"], w["k_mult"], True)
     dt = time.perf_counter() - t0
-    value = args.steps * sample_rows / dt
+    value = args.steps * sample_rows / dt / scale
+    sample = (f"{sample_rows}x{n} {w['dtype']} rows per step (k={k}), torch CPU ops restating the reference's "
+              f"autobucket path, {threads} threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": dict(CONFIG, rows_per_step=sample_rows,
-                       note="reference CPU path on host cores, each step a 32-row sample of the batch; GPUs unused"),
-        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
-                         "sample": f"{sample_rows} rows of the 128-row batch per step, torch CPU ops "
-                                   f"restating the reference's autobucket path, {threads} threads"},
+        "higher_is_better": True, "scaling": "strong" if w.get("long_row") else "weak", "vs_baseline": None,
+        "dtype": DTYPE_TAG[w["dtype"]], "data": "synthetic",
+        "config": dict(config_of(w, args.workload), rows_per_step=sample_rows,
+                       note="reference CPU path on host cores, each step a bounded sample; GPUs unused"),
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -178,10 +244,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
 
     import approx_topk
     from approx_topk import _native
-    from approx_topk.host_buffers import topk_host
+    from approx_topk import distributed as atd
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path)")
+    w = WORKLOADS[args.workload]
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -193,33 +260,58 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
         torch.cuda.synchronize(dev)
 
     lib = _native.lib()
-    # two distinct 512 MiB inputs, alternated: every step reads data that is
-    # not in the 126 MB L2
-    xs = [make_rows(ROWS_PER_GPU, 1000 * rank + i, dev) for i in range(2)]
+    dtype = DTYPES[w["dtype"]]
+    code = _native.dtype_code(dtype)
+    rows, n, k, j, k_mult = w["rows"], w["n"], w["k"], w["j"], w["k_mult"]
     stream = torch.cuda.current_stream(dev)
-
-    # The timed step calls the C-ABI entry point the Python operator itself
-    # calls (atk_topk), with preallocated outputs: Python's custom-op dispatch
-    # costs about as much host time as the 100 us kernel takes, and a CUDA-graph
-    # replay per step adds ~10 us of launch latency, so either would measure the
-    # host, not the path.  Two (input, output) buffer sets are alternated so
-    # that neither the 512 MiB input nor the 96 MiB output of a step is in L2.
-    code = _native.dtype_code(torch.float32)
-    outs = [(torch.empty(ROWS_PER_GPU, K, device=dev, dtype=torch.float32),
-             torch.empty(ROWS_PER_GPU, K, device=dev, dtype=torch.int64)) for _ in range(2)]
     stream_ptr = stream.cuda_stream
+    long_row = bool(w.get("long_row"))
 
-    def step(i):
-        x, (v, ix) = xs[i & 1], outs[i & 1]
-        rc = lib.atk_topk(x.data_ptr(), code, ROWS_PER_GPU, N, N, K, J, K_MULT, 1, -1,
-                          v.data_ptr(), ix.data_ptr(), K, None, 0, stream_ptr)
-        if rc != 0:
-            raise RuntimeError(_native.strerror(rc))
+    if long_row:
+        # One row for the whole job; this rank holds its bucket group as a dense
+        # stripes x cols slab, generated directly in that layout (the values are
+        # i.i.d., so the slab of a random row is a random slab).
+        b = k * k_mult // j
+        c0, c1 = atd.bucket_group(b, rank, world)
+        slab = make_input(dict(w, n=(n // b) * (c1 - c0)), 1, 77 + rank, dev).view(n // b, c1 - c0)
+        result = {}
 
-    # the public operator gives the same bits as the direct call
-    pv, pi = approx_topk.topk(xs[0], K, -1, j=J, k_mult=K_MULT)
-    step(0)
-    assert torch.equal(pv, outs[0][0]) and torch.equal(pi, outs[0][1])
+        def step(i):
+            result["out"] = atd.topk_long_row(slab, k, j, k_mult)
+
+        check = None
+        n_sets = 1
+        rows_per_rank_step = 1.0 / world
+    else:
+        # Two (input, output, workspace) buffer sets are alternated so that
+        # neither the input nor the output of a step is still in the 126 MB L2.
+        # The timed step calls the C-ABI entry point the Python operator itself
+        # calls (atk_topk) with preallocated buffers: Python's custom-op dispatch
+        # costs about as much host time as a 100 us kernel takes, and a CUDA-graph
+        # replay per step adds ~10 us of launch latency, so either would measure
+        # the host, not the path.
+        n_sets = 2
+        xs = [make_input(w, rows, 1000 * rank + i, dev) for i in range(n_sets)]
+        outs = [(torch.empty(rows, k, device=dev, dtype=dtype), torch.empty(rows, k, device=dev, dtype=torch.int64))
+                for _ in range(n_sets)]
+        ws_bytes = lib.atk_topk_workspace_bytes(code, rows, n, k, j, k_mult)
+        wss = [torch.empty(max(ws_bytes, 1), device=dev, dtype=torch.uint8) for _ in range(n_sets)]
+
+        def step(i):
+            x, (v, ix), ws = xs[i % n_sets], outs[i % n_sets], wss[i % n_sets]
+            rc = lib.atk_topk(x.data_ptr(), code, rows, n, n, k, j, k_mult, 1, -1, v.data_ptr(), ix.data_ptr(), k,
+                              ws.data_ptr() if ws_bytes else None, ws_bytes, stream_ptr)
+            if rc != 0:
+                raise RuntimeError(_native.strerror(rc))
+
+        # the public operator gives the same bits as the direct call
+        pv, pi = approx_topk.topk(xs[0], k, -1, j=j, k_mult=k_mult)
+        step(0)
+        torch.cuda.synchronize(dev)
+        assert torch.equal(pv, outs[0][0]) and torch.equal(pi, outs[0][1])
+        del pv, pi
+        rows_per_rank_step = float(rows)
+
     lib.atk_reset_launch_count()
     step(0)
     launches_per_step = int(lib.atk_launch_count())
@@ -247,7 +339,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
         t_probe = time.perf_counter()
         i = 0
         while time.perf_counter() - t_probe < args.clock_probe_seconds:
-            for _ in range(64):
+            for _ in range(16):
                 step(i)
                 i += 1
             torch.cuda.synchronize(dev)
@@ -257,69 +349,73 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
 
     e2e_ms_local = float("nan")
     e2e_steps = max(3, min(args.steps, 10))
-    if not args.no_e2e:
-        e2e_ms_local = run_e2e(args, dev, xs[0], e2e_steps, barrier)
+    do_e2e = not args.no_e2e and not long_row
+    if do_e2e:
+        e2e_ms_local = run_e2e(w, dev, xs[0], e2e_steps, barrier)
 
     times = torch.tensor([total_ms, kernel_ms, e2e_ms_local], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms, kernel_ms, e2e_ms = times.tolist()
-    return finish(args, rank, world, total_ms, kernel_ms, e2e_ms, e2e_steps, launches, clocks)
-
-
-def run_e2e(args, dev, x_dev, e2e_steps, barrier) -> float:
-    """End to end through the host-buffer API: pinned host rows -> pinned host results."""
-    from approx_topk.host_buffers import topk_host
-
-    xh = torch.empty(ROWS_PER_GPU, N, dtype=torch.float32).pin_memory()
-    xh.copy_(x_dev)
-    out = (torch.empty(ROWS_PER_GPU, K, dtype=torch.float32).pin_memory(),
-           torch.empty(ROWS_PER_GPU, K, dtype=torch.int64).pin_memory())
-    for _ in range(2):
-        topk_host(xh, K, J, K_MULT, device=dev, out=out)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        topk_host(xh, K, J, K_MULT, device=dev, out=out)
-    torch.cuda.synchronize(dev)
-    return (time.perf_counter() - t0) * 1e3
-
-
-def finish(args, rank, world, total_ms, kernel_ms, e2e_ms, e2e_steps, launches, clocks) -> int:
-    import torch.distributed as dist
 
     if rank == 0:
-        rows_total = ROWS_PER_GPU * world
+        rows_total = rows_per_rank_step * world
         peak, peak_src = measured_hbm_peak()
-        alg = ALG_BYTES_PER_ROW * ROWS_PER_GPU
+        s = torch.empty(0, dtype=dtype).element_size()
+        # bytes one GPU moves per step (the roofline is per GPU)
+        alg = alg_bytes(w, rows) if not long_row else (n // world) * s + k * (s + 8)
         achieved = alg / (kernel_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": rows_total * args.steps / (total_ms * 1e-3), "unit": "rows/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": dict(CONFIG, l2="two input/output buffer sets alternated; 512 MiB in + 96 MiB out per step "
-                                      "exceed the 126 MB L2",
-                           timed_call="atk_topk (C ABI) on the current stream, outputs preallocated"),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if long_row else "weak",
+            "vs_baseline": None, "dtype": DTYPE_TAG[w["dtype"]], "data": "synthetic",
+            "config": dict(config_of(w, args.workload),
+                           l2=("input far larger than the 126 MB L2" if long_row else
+                               "two input/output buffer sets alternated; what a step reads and writes is not in L2"),
+                           timed_call=("approx_topk.distributed.topk_long_row (atk_stage1_slab, NCCL all-gather, "
+                                       "atk_select)" if long_row else
+                                       "atk_topk (C ABI) on the current stream, buffers preallocated")),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "kernel": "sweep_kernel<float,2,4>", "alg_bytes_per_launch": alg,
-                         "read_only_gbs": ROWS_PER_GPU * N * ELEM / (kernel_ms * 1e-3) / 1e9,
-                         "kernel_ms": kernel_ms, "peak_source": peak_src},
-            "e2e": None if args.no_e2e else {"value": rows_total * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s",
-                    "h2d_bytes_per_step": ROWS_PER_GPU * N * ELEM,
-                    "d2h_bytes_per_step": ROWS_PER_GPU * K * (ELEM + 8), "ms_per_step": e2e_ms / e2e_steps,
-                    "api": "approx_topk.host_buffers.topk_host (atk_topk_host), pinned host buffers"},
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload),
+                         "alg_bytes_per_step_per_gpu": alg,
+                         "read_only_gbs": ((n // world) * s if long_row else rows * n * s) / (kernel_ms * 1e-3) / 1e9,
+                         "step_ms": kernel_ms, "kernels_per_step": launches_per_step,
+                         "peak_source": peak_src},
+            "e2e": None if not do_e2e else {
+                "value": rows_total * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s",
+                "h2d_bytes_per_step": rows * n * s, "d2h_bytes_per_step": rows * k * (s + 8),
+                "ms_per_step": e2e_ms / e2e_steps,
+                "api": "approx_topk.host_buffers.topk_host (atk_topk_host), pinned host buffers"},
             "gpu_launches": launches,
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_path_rate(args.cpu_seconds, os.cpu_count() or 1)
+            line["cpu_baseline"] = cpu_path_rate(w, args.cpu_seconds, os.cpu_count() or 1)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def run_e2e(w, dev, x_dev, e2e_steps, barrier) -> float:
+    """End to end through the host-buffer API: pinned host rows -> pinned host results."""
+    from approx_topk.host_buffers import topk_host
+
+    xh = torch.empty(x_dev.shape, dtype=x_dev.dtype).pin_memory()
+    xh.copy_(x_dev)
+    out = (torch.empty(x_dev.shape[0], w["k"], dtype=x_dev.dtype).pin_memory(),
+           torch.empty(x_dev.shape[0], w["k"], dtype=torch.int64).pin_memory())
+    for _ in range(2):
+        topk_host(xh, w["k"], w["j"], w["k_mult"], device=dev, out=out)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        topk_host(xh, w["k"], w["j"], w["k_mult"], device=dev, out=out)
+    torch.cuda.synchronize(dev)
+    return (time.perf_counter() - t0) * 1e3
 
 
 def main() -> int:
@@ -328,6 +424,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="length of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--clock-probe-seconds", type=float, default=1.0,

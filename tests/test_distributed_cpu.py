@@ -1,0 +1,95 @@
+"""CPU (gloo, world_size 2) tests of the multi-GPU host logic: row sharding and
+the bucket-group sharding of one long row with the all-gather of candidates.
+The kernels are replaced by the CPU oracle so that only the partitioning, the
+exchange and the index arithmetic are under test."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from approx_topk import distributed as atd
+from oracle import cpu_oracle as oracle
+
+
+def test_row_shard_covers_all_rows_once():
+    for rows in (0, 1, 7, 128, 1000):
+        for world in (1, 2, 3, 8):
+            spans = [atd.row_shard(rows, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            for (a, b), (c, d) in zip(spans, spans[1:]):
+                assert b == c
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        atd.row_shard(10, 2, 2)
+
+
+def test_bucket_group_requires_equal_groups():
+    assert atd.bucket_group(1024, 3, 4) == (768, 1024)
+    with pytest.raises(ValueError):
+        atd.bucket_group(10, 0, 4)
+
+
+def oracle_stage1_slab(slab, total_buckets, col_offset, j):
+    stripes, cols = slab.shape
+    v, i = oracle.stage1(slab.reshape(1, -1), cols * j, j, interleaved=True)
+    i = i.reshape(-1)
+    return v.reshape(-1), (i // cols) * total_buckets + col_offset + (i % cols)
+
+
+def oracle_select(cand_vals, cand_idx, k):
+    v, i = oracle.select(cand_vals.reshape(1, -1), cand_idx.reshape(1, -1), k)
+    return v.reshape(-1), i.reshape(-1)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, k, j, k_mult, n, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        row = torch.randn(n, generator=torch.Generator().manual_seed(1234))
+        b = k * k_mult // j
+        slab = atd.slab_of_row(row, b, rank, world)
+        v, i = atd.topk_long_row(slab, k, j, k_mult, stage1=oracle_stage1_slab, select=oracle_select)
+        torch.save((v, i), os.path.join(out, f"r{rank}.pt"))
+        # rows: every rank handles its own span, nothing is exchanged
+        start, stop = atd.row_shard(10, rank, world)
+        torch.save((start, stop), os.path.join(out, f"span{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("k,j,k_mult", [(64, 2, 1), (64, 4, 2), (32, 1, 4)])
+def test_long_row_two_ranks_equals_single_process(tmp_path, k, j, k_mult):
+    world, n = 2, 1 << 14
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, k, j, k_mult, n, str(tmp_path)), nprocs=world, join=True)
+    row = torch.randn(n, generator=torch.Generator().manual_seed(1234))
+    ev, ei = oracle.topk(row.reshape(1, -1), k, j=j, k_mult=k_mult, interleaved=True)
+    results = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    for v, i in results:
+        assert torch.equal(v.sort().values, ev.reshape(-1).sort().values)
+        assert torch.equal(i.sort().values, ei.reshape(-1).sort().values)
+        assert torch.equal(row[i], v)
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    spans = [torch.load(tmp_path / f"span{r}.pt") for r in range(world)]
+    assert spans == [(0, 5), (5, 10)]
+
+
+def test_long_row_single_process_matches_oracle():
+    n, k, j, k_mult = 1 << 13, 32, 2, 2
+    row = torch.randn(n, generator=torch.Generator().manual_seed(7))
+    slab = atd.slab_of_row(row, k * k_mult // j, 0, 1)
+    v, i = atd.topk_long_row(slab, k, j, k_mult, stage1=oracle_stage1_slab, select=oracle_select)
+    ev, ei = oracle.topk(row.reshape(1, -1), k, j=j, k_mult=k_mult)
+    assert torch.equal(i.sort().values, ei.reshape(-1).sort().values)

@@ -238,3 +238,15 @@ def test_host_buffer_entry_point_equals_device_path(dtype, j, k_mult):
     assert torch.equal(bits(hv), bits(v)) and torch.equal(hi, i.cpu())
     hv, hi = api.topk_host(x.cpu(), 128, j, k_mult, True)      # pageable memory, default chunking
     assert torch.equal(bits(hv), bits(v)) and torch.equal(hi, i.cpu())
+
+
+def test_long_row_entry_point_single_rank_equals_operator():
+    # world size 1: the bucket-group path (slab stage 1 + select) must equal the plain operator
+    from approx_topk import distributed as atd
+
+    n, k, j, k_mult = 1 << 20, 1 << 12, 4, 2
+    row = make(1, n, torch.float32, 900)
+    slab = atd.slab_of_row(row.view(-1), k * k_mult // j, 0, 1)
+    v, i = atd.topk_long_row(slab, k, j, k_mult)
+    ev, ei = api.topk(row, k, j, k_mult, True)
+    assert_pairs_identical(v.view(1, -1), i.view(1, -1), ev, ei)
