@@ -41,7 +41,8 @@ enum {
   ATK_ERR_BAD_ARG = -5,      /* null pointer, negative size, k_mult < 1, k > k0 ... */
   ATK_ERR_WORKSPACE = -6,    /* workspace missing or smaller than *_workspace_bytes */
   ATK_ERR_TOO_LARGE = -7,    /* a size exceeds what the kernels index (see each function) */
-  ATK_ERR_CUDA = -8          /* a CUDA runtime call failed; see cudaGetLastError */
+  ATK_ERR_CUDA = -8,         /* a CUDA runtime call failed; see cudaGetLastError */
+  ATK_ERR_SCRATCH_LIMIT = -9 /* atk_select_static: the problem needs more than the built-in scratch */
 };
 
 /* Library version, major*10000 + minor*100 + patch. */
@@ -104,6 +105,45 @@ int atk_select(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_
                int64_t k0, int64_t cand_row_stride, int64_t k,
                void* out_vals, int64_t* out_idx, int64_t out_row_stride,
                void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * atk_select without a workspace argument, for callers that cannot allocate
+ * device memory.  It has no counterpart in the reference.
+ *
+ * Who needs it: a plugin loaded into a host process that owns the whole GPU
+ * memory budget (an inference server or a database engine that carves up device
+ * memory at start-up and gives extensions no allocator), a latency-critical
+ * loop in which a cudaMalloc may stall the device, or a caller that only holds
+ * raw pointers and a stream from another runtime.  Such callers can still pass
+ * their candidate and output buffers, but have nowhere to get the select's
+ * scratch (digit histograms, running state, per-block counts) from.
+ *
+ * Here that scratch is a fixed array of ATK_SELECT_STATIC_SCRATCH_BYTES (1 MiB)
+ * of device memory that is part of the library image: every GPU that loads the
+ * library holds it until the process exits.  The call is otherwise identical
+ * to atk_select and returns the same bits.  It calls no cudaMalloc, cudaFree
+ * or any other allocating routine.
+ *
+ * Limit: when atk_select_workspace_bytes(dtype, rows, k0, k) exceeds the
+ * built-in 1 MiB the call is refused with ATK_ERR_SCRATCH_LIMIT and launches
+ * nothing (rows of up to 32768 candidates need no scratch at all; one row of
+ * 2^21 fp32 candidates needs about 6 KiB; 64 rows of 2^24 about 0.8 MiB).
+ *
+ * First call on a device: looks up the device address of the array
+ * (cudaGetSymbolAddress, with that device current) and caches it per device.
+ * Make this first call before starting any stream capture.
+ *
+ * Sharing: all calls on a device use the same array.  It keeps what the
+ * previous call left in it; the parts that must start at zero are cleared on
+ * the stream at the start of every call, so back-to-back calls on one stream
+ * are safe.  Two calls whose GPU work overlaps in time (different streams or
+ * host threads without ordering between them) race on the array and give
+ * undefined results: order them, or use atk_select with separate workspaces.
+ */
+#define ATK_SELECT_STATIC_SCRATCH_BYTES (1u << 20)
+int atk_select_static(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_t rows,
+                      int64_t k0, int64_t cand_row_stride, int64_t k,
+                      void* out_vals, int64_t* out_idx, int64_t out_row_stride, void* stream);
 
 /*
  * The whole operator approx_topk.topk(x, k, dim=-1, j, k_mult, interleaved)

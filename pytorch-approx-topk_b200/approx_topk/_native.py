@@ -26,6 +26,7 @@ ATK_ERR_BAD_ARG = -5
 ATK_ERR_WORKSPACE = -6
 ATK_ERR_TOO_LARGE = -7
 ATK_ERR_CUDA = -8
+ATK_ERR_SCRATCH_LIMIT = -9
 
 DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
@@ -43,6 +44,7 @@ SIGNATURES = {
     "atk_stage1_slab": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp]),
     "atk_select_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "atk_select": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _sz, _vp]),
+    "atk_select_static": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
     "atk_topk_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64]),
     "atk_topk": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_bucketed_argmax": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _i64, _vp]),

@@ -77,6 +77,8 @@ const char* atk_strerror(int status) {
     case ATK_ERR_WORKSPACE: return "topk: workspace missing or too small";
     case ATK_ERR_TOO_LARGE: return "topk: problem size exceeds the kernel's index range";
     case ATK_ERR_CUDA: return "topk: CUDA runtime error";
+    case ATK_ERR_SCRATCH_LIMIT:
+      return "topk: atk_select_static needs more scratch than its built-in 1 MiB; use atk_select with a workspace";
     default: return "topk: unknown status";
   }
 }
@@ -189,6 +191,29 @@ int atk_select(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_
   a.workspace_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
   return launch_select(a, dtype);
+}
+
+int atk_select_static(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_t rows, int64_t k0,
+                      int64_t cand_row_stride, int64_t k, void* out_vals, int64_t* out_idx,
+                      int64_t out_row_stride, void* stream) {
+  if (elem_size(dtype) == 0) return ATK_ERR_BAD_DTYPE;
+  if (rows < 0 || k0 < 0 || k < 0 || k > k0 || cand_row_stride < 0 || out_row_stride < 0) return ATK_ERR_BAD_ARG;
+  if (rows == 0 || k == 0) return ATK_OK;
+  if (cand_vals == nullptr || cand_idx == nullptr || out_vals == nullptr || out_idx == nullptr) return ATK_ERR_BAD_ARG;
+  SelectLaunch a;
+  a.cand_vals = cand_vals;
+  a.cand_idx = reinterpret_cast<const long long*>(cand_idx);
+  a.rows = rows;
+  a.k0 = k0;
+  a.cand_row_stride = cand_row_stride;
+  a.k = k;
+  a.out_vals = out_vals;
+  a.out_idx = reinterpret_cast<long long*>(out_idx);
+  a.out_row_stride = out_row_stride;
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_select_static(a, dtype);
 }
 
 size_t atk_topk_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j, int64_t k_mult) {

@@ -12,6 +12,8 @@
 //    registers, a single launch;
 //  * large rows: several blocks per row; digit histograms, block counts and
 //    the running (prefix, need) state live in a caller-provided workspace.
+#include <atomic>
+
 #include "atk_select.cuh"
 #include "atk_block_select.cuh"
 
@@ -407,6 +409,52 @@ size_t select_workspace_bytes(int dtype, long long rows, long long k0) {
     case ATK_BF16: return workspace_typed<__nv_bfloat16>(rows, k0);
     default: return 0;
   }
+}
+
+// ---- built-in scratch for callers that cannot allocate -----------------------
+// Part of the library image: every device that loads the library holds these
+// bytes until the process exits.  In host code the name below is only a
+// host-side stand-in for the symbol, not a device address; the address that
+// kernels may use comes from cudaGetSymbolAddress, looked up once per device.
+static __device__ __align__(256) unsigned char g_select_static_scratch[ATK_SELECT_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_select_static_scratch on the current device, or nullptr
+// if the runtime cannot provide it.  The first call on a device does the
+// look-up (with that device current) and caches it; later calls only read the
+// cache.  Two threads racing on the first call store the same value.
+void* static_scratch_of_current_device() {
+  static std::atomic<void*> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (dev >= 0 && dev < 64) {
+    void* known = cache[dev].load(std::memory_order_acquire);
+    if (known != nullptr) return known;
+  }
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_select_static_scratch) != cudaSuccess || ptr == nullptr) return nullptr;
+  if (dev >= 0 && dev < 64) cache[dev].store(ptr, std::memory_order_release);
+  return ptr;
+}
+}  // namespace
+
+int launch_select_static(const SelectLaunch& a, int dtype) {
+  if (a.rows <= 0 || a.k <= 0) return ATK_OK;
+  const size_t need = select_workspace_bytes(dtype, a.rows, a.k0);
+  if (need > sizeof(g_select_static_scratch)) return ATK_ERR_SCRATCH_LIMIT;
+  SelectLaunch b = a;
+  b.workspace = nullptr;
+  b.workspace_bytes = 0;
+  if (need > 0) {
+    void* scratch = static_scratch_of_current_device();
+    if (scratch == nullptr) return ATK_ERR_CUDA;
+    b.workspace = scratch;
+    b.workspace_bytes = sizeof(g_select_static_scratch);
+  }
+  // The select clears the histograms it accumulates into at the start of every
+  // call (on the stream); everything else in the scratch is written before it
+  // is read, so stale contents of an earlier call are harmless.
+  return launch_select(b, dtype);
 }
 
 int launch_select(const SelectLaunch& a, int dtype) {

@@ -20,4 +20,9 @@ struct SelectLaunch {
 size_t select_workspace_bytes(int dtype, long long rows, long long k0);
 int launch_select(const SelectLaunch& a, int dtype);
 
+// launch_select with the library's built-in static device scratch in place of
+// a.workspace (which is ignored).  Returns ATK_ERR_SCRATCH_LIMIT, launching
+// nothing, when the problem needs more than that array holds.
+int launch_select_static(const SelectLaunch& a, int dtype);
+
 }  // namespace atk
