@@ -80,6 +80,21 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) raw[i] = slot0 + i < k0 ? vrow[slot0 + i] : Bits(0);
   }
+  // The positions travel with their candidates.  For short per-thread runs
+  // they are fetched up front with the values (contiguous, 16-byte loads), so
+  // the write-out at the end does not wait on a chain of dependent gathers.
+  constexpr bool kPrefetchIdx = ITEMS <= 8;
+  __align__(16) long long pidx[kPrefetchIdx ? ITEMS : 1];
+  if (kPrefetchIdx) {
+    if (vec_ok && ITEMS % 2 == 0 && slot0 + ITEMS <= k0) {
+#pragma unroll
+      for (int i = 0; i < ITEMS / 2; ++i)
+        reinterpret_cast<uint4*>(pidx)[i] = reinterpret_cast<const uint4*>(irow + slot0)[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) pidx[i] = slot0 + i < k0 ? irow[slot0 + i] : 0;
+    }
+  }
   // Slots past the end get key 0; every use below is guarded by the slot bound.
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) key[i] = slot0 + i < k0 ? K::key(raw[i]) : 0u;
@@ -147,7 +162,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
     }
     if (pos >= 0) {
       ovrow[pos] = raw[i];
-      oirow[pos] = irow[slot0 + i];
+      oirow[pos] = kPrefetchIdx ? pidx[kPrefetchIdx ? i : 0] : irow[slot0 + i];
     }
   }
 }
@@ -345,7 +360,8 @@ int select_typed(const SelectLaunch& a) {
     const int k0 = static_cast<int>(a.k0);
     const int k = static_cast<int>(a.k);
     const int s = static_cast<int>(sizeof(Bits));
-    const int vec_ok = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * s) % 16 == 0);
+    const int vec_ok = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * s) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(a.cand_idx) % 16 == 0) && ((a.cand_row_stride * 8) % 16 == 0);
     const unsigned rows = static_cast<unsigned>(a.rows);
     auto threads_for = [&](int items) {
       int t = (k0 + items - 1) / items;

@@ -1,0 +1,66 @@
+"""Worker of tests/test_multi_gpu.py: one rank per GPU under torchrun (NCCL).
+
+Checks on real GPUs that (1) the bucket-group sharding of one long row with the
+all-gather of candidates gives bit-identical results to the single-GPU
+operator on the same row, on every rank, and (2) row sharding reproduces the
+unsharded result row for row.
+"""
+
+import os
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+for p in (str(ROOT), str(ROOT / "pytorch-approx-topk_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch
+import torch.distributed as dist
+
+import approx_topk
+from approx_topk import distributed as atd
+
+
+def canonical(v, i):
+    o = torch.argsort(i)
+    return v[o], i[o]
+
+
+def main() -> int:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    try:
+        for dtype, n, k, j, k_mult in [(torch.float32, 1 << 22, 1 << 12, 4, 2), (torch.bfloat16, 1 << 20, 1 << 10, 2, 1),
+                                       (torch.float16, 1 << 21, 1 << 16, 1, 2)]:
+            g = torch.Generator(device=dev).manual_seed(4321)        # same row on every rank
+            row = torch.randn(n, device=dev, generator=g).to(dtype)
+            b = k * k_mult // j
+            slab = atd.slab_of_row(row, b, rank, world)
+            v, i = atd.topk_long_row(slab, k, j, k_mult)
+            ev, ei = approx_topk.topk(row.view(1, -1), k, -1, j=j, k_mult=k_mult)
+            (v, i), (ev, ei) = canonical(v, i), canonical(ev.view(-1), ei.view(-1))
+            assert torch.equal(i, ei), f"rank {rank}: indices differ ({dtype}, n={n})"
+            assert torch.equal(v.view(torch.int16 if v.element_size() == 2 else torch.int32),
+                               ev.view(torch.int16 if ev.element_size() == 2 else torch.int32)), \
+                f"rank {rank}: values differ ({dtype}, n={n})"
+        # rows: each rank computes its span; together they equal the full batch
+        g = torch.Generator(device=dev).manual_seed(99)
+        x = torch.randn(37, 1 << 14, device=dev, generator=g)
+        full_v, full_i = approx_topk.topk(x, 256, -1, j=2)
+        lo, hi = atd.row_shard(x.shape[0], rank, world)
+        v, i = atd.topk_row_sharded(x[lo:hi], 256, j=2)
+        assert torch.equal(v, full_v[lo:hi]) and torch.equal(i, full_i[lo:hi])
+        dist.barrier()
+        if rank == 0:
+            print("MULTI_GPU_OK", world)
+    finally:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
