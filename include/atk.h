@@ -74,10 +74,20 @@ int atk_device_supported(void);
  * reference the queue starts at -inf, so -inf inputs are selectable and every
  * output slot is a real element.
  * k0 == 0 is a no-op.  Limits: n / buckets < 2^31.
+ *
+ * workspace (optional, may be NULL / 0): atk_stage1_workspace_bytes() bytes of
+ * device scratch, 256-byte aligned.  Shapes with few rows and few buckets
+ * cannot occupy the GPU with one block per group of columns (the weakness of
+ * the reference's thread-per-bucket kernel); given scratch, the kernel also
+ * splits the stripes of a column over several blocks and merges their partial
+ * candidates in a second small launch.  The result does not depend on whether
+ * (or how much) scratch is given, only the speed on such shapes does.
  */
+size_t atk_stage1_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k0, int j, int interleaved);
 int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
                int64_t k0, int j, int interleaved, int mode,
-               void* out_vals, int64_t* out_idx, int64_t out_row_stride, void* stream);
+               void* out_vals, int64_t* out_idx, int64_t out_row_stride,
+               void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Stage 1 over a column slab of one long interleaved row that is sharded over
@@ -148,8 +158,9 @@ int atk_select_static(const void* cand_vals, const int64_t* cand_idx, int dtype,
 /*
  * The whole operator approx_topk.topk(x, k, dim=-1, j, k_mult, interleaved)
  * (priority_queue.py:14-88): stage 1 with k0 = k*k_mult and, when k_mult > 1,
- * the exact select.  Candidates stay on chip when one thread block can own a
- * row's candidates; otherwise they pass through the workspace.
+ * the exact select over the candidates, which pass through the workspace
+ * (they are re-read from L2 for the shapes of the reference's configurations).
+ * With k_mult == 1 the workspace is optional (see atk_stage1).
  */
 size_t atk_topk_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j,
                                 int64_t k_mult);
@@ -165,10 +176,13 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
  * contiguous buckets are fixed chunks of ceil(n/k), the FIRST maximum wins a
  * tie, outputs in bucket order.  k may exceed n (all-padding buckets return
  * the lowest value and the first padded position).
+ * workspace: optional, atk_stage1_workspace_bytes(dtype, rows, n, k, 1, interleaved)
+ * bytes, same role as in atk_stage1.
  */
 int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
                         int64_t k, int interleaved,
-                        void* out_vals, int64_t* out_idx, int64_t out_row_stride, void* stream);
+                        void* out_vals, int64_t* out_idx, int64_t out_row_stride,
+                        void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Host-buffer form of atk_topk: x_host / out_*_host are HOST pointers (pinned

@@ -40,14 +40,15 @@ SIGNATURES = {
     "atk_version": (_int, []),
     "atk_strerror": (ctypes.c_char_p, [_int]),
     "atk_device_supported": (_int, []),
-    "atk_stage1": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _vp, _i64, _vp]),
+    "atk_stage1_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _int]),
+    "atk_stage1": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_stage1_slab": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp]),
     "atk_select_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "atk_select": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_select_static": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
     "atk_topk_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64]),
     "atk_topk": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
-    "atk_bucketed_argmax": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _i64, _vp]),
+    "atk_bucketed_argmax": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_topk_host_scratch_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64, _i64]),
     "atk_topk_host": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _vp, _vp, _vp, _sz, _i64]),
     "atk_launch_count": (_i64, []),

@@ -67,10 +67,14 @@ def _argmax_cuda(xs: Tensor, k: int, dim: int, interleaved: bool) -> tuple[Tenso
     indices = torch.empty(lead + [k], device=xs.device, dtype=torch.int64)
     if k > 0 and rows > 0:
         _native.require_device(xs.device)
+        lib = _native.lib()
         with torch.cuda.device(xs.device):
-            status = _native.lib().atk_bucketed_argmax(
+            ws_bytes = lib.atk_stage1_workspace_bytes(code, rows, n, k, 1, int(interleaved)) if k <= n else 0
+            ws = torch.empty(ws_bytes, device=xs.device, dtype=torch.uint8) if ws_bytes else None
+            status = lib.atk_bucketed_argmax(
                 x_last.data_ptr(), code, rows, n, row_stride, k, int(interleaved),
                 values.data_ptr(), indices.data_ptr(), k,
+                ws.data_ptr() if ws is not None else None, ws_bytes,
                 _native.current_stream_ptr(xs.device),
             )
         _native.check(status)

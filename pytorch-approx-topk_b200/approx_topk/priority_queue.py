@@ -70,7 +70,7 @@ def topk(
     indices = torch.empty(lead_shape + [k], device=xs.device, dtype=torch.int64)
 
     with torch.cuda.device(xs.device):
-        ws_bytes = lib.atk_topk_workspace_bytes(code, rows, n, k, j, k_mult) if k0 != k else 0
+        ws_bytes = lib.atk_topk_workspace_bytes(code, rows, n, k, j, k_mult)
         workspace = torch.empty(ws_bytes, device=xs.device, dtype=torch.uint8) if ws_bytes else None
         mode = -1 if multithread_buckets is None else int(bool(multithread_buckets))
         status = lib.atk_topk(

@@ -90,9 +90,15 @@ int atk_device_supported(void) {
   return major == 10 ? ATK_OK : ATK_ERR_CUDA;
 }
 
+size_t atk_stage1_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k0, int j, int interleaved) {
+  const int s = elem_size(dtype);
+  if (s == 0 || !interleaved || rows <= 0 || k0 <= 0 || j < 1 || j > 4 || k0 % j != 0 || k0 > n) return 0;
+  return sweep_workspace_bytes(s, rows, n, k0 / j, j, sm_count_of_current_device());
+}
+
 int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k0,
                int j, int interleaved, int mode, void* out_vals, int64_t* out_idx,
-               int64_t out_row_stride, void* stream) {
+               int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
   (void)mode;
   int rc = check_common(x, dtype, rows, n, row_stride, out_vals, out_idx, out_row_stride);
   if (rc != ATK_OK) return rc;
@@ -118,6 +124,8 @@ int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_st
     a.j = j;
     a.first_wins = false;
     a.sm_count = sm_count_of_current_device();
+    a.workspace = workspace;
+    a.workspace_bytes = workspace_bytes;
     a.stream = static_cast<cudaStream_t>(stream);
     return sweep_dispatch(a, dtype);
   }
@@ -160,6 +168,8 @@ int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols, 
   a.j = j;
   a.first_wins = false;
   a.sm_count = sm_count_of_current_device();
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
   a.stream = static_cast<cudaStream_t>(stream);
   return sweep_dispatch(a, dtype);
 }
@@ -217,35 +227,48 @@ int atk_select_static(const void* cand_vals, const int64_t* cand_idx, int dtype,
 }
 
 size_t atk_topk_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j, int64_t k_mult) {
-  (void)n;
-  (void)j;
   const int s = elem_size(dtype);
-  if (s == 0 || rows <= 0 || k <= 0 || k_mult <= 1) return 0;
+  if (s == 0 || rows <= 0 || k <= 0 || k_mult < 1) return 0;
   const int64_t k0 = k * k_mult;
-  return align256(static_cast<size_t>(rows) * k0 * s) + align256(static_cast<size_t>(rows) * k0 * 8) +
-         select_workspace_bytes(dtype, rows, k0);
+  // stage 1 may split stripes over blocks (interleaved buckets; harmless upper bound otherwise)
+  size_t total = align256(atk_stage1_workspace_bytes(dtype, rows, n, k0, j, 1));
+  if (k_mult > 1)
+    total += align256(static_cast<size_t>(rows) * k0 * s) + align256(static_cast<size_t>(rows) * k0 * 8) +
+             select_workspace_bytes(dtype, rows, k0);
+  return total;
 }
 
 int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k, int j,
              int64_t k_mult, int interleaved, int mode, void* out_vals, int64_t* out_idx,
              int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
   if (k_mult < 1 || k < 0) return ATK_ERR_BAD_ARG;
-  if (k_mult == 1)
-    return atk_stage1(x, dtype, rows, n, row_stride, k, j, interleaved, mode, out_vals, out_idx,
-                      out_row_stride, stream);
   const int s = elem_size(dtype);
   if (s == 0) return ATK_ERR_BAD_DTYPE;
   if (k == 0 || rows == 0) return ATK_OK;
   const int64_t k0 = k * k_mult;
-  const size_t need = atk_topk_workspace_bytes(dtype, rows, n, k, j, k_mult);
-  if (workspace == nullptr || workspace_bytes < need) return ATK_ERR_WORKSPACE;
+  // Workspace layout: [stage-1 stripe-split planes][candidate values][candidate positions][select state].
+  // The stage-1 part is optional (a smaller or missing workspace only disables the split over blocks);
+  // the rest is required when k_mult > 1.
   unsigned char* ws = static_cast<unsigned char*>(workspace);
-  void* cand_vals = ws;
-  ws += align256(static_cast<size_t>(rows) * k0 * s);
-  int64_t* cand_idx = reinterpret_cast<int64_t*>(ws);
-  ws += align256(static_cast<size_t>(rows) * k0 * 8);
+  size_t split_bytes = align256(atk_stage1_workspace_bytes(dtype, rows, n, k0, j, interleaved));
+  if (k_mult == 1) {
+    if (ws == nullptr || workspace_bytes < split_bytes) split_bytes = ws == nullptr ? 0 : workspace_bytes;
+    return atk_stage1(x, dtype, rows, n, row_stride, k, j, interleaved, mode, out_vals, out_idx, out_row_stride,
+                      ws, split_bytes, stream);
+  }
+  const size_t cand_v = align256(static_cast<size_t>(rows) * k0 * s);
+  const size_t cand_i = align256(static_cast<size_t>(rows) * k0 * 8);
   const size_t sel_ws = select_workspace_bytes(dtype, rows, k0);
-  int rc = atk_stage1(x, dtype, rows, n, row_stride, k0, j, interleaved, mode, cand_vals, cand_idx, k0, stream);
+  if (ws == nullptr || workspace_bytes < cand_v + cand_i + sel_ws) return ATK_ERR_WORKSPACE;
+  if (workspace_bytes < split_bytes + cand_v + cand_i + sel_ws) split_bytes = 0;
+  void* split_ws = split_bytes ? ws : nullptr;
+  ws += split_bytes;
+  void* cand_vals = ws;
+  ws += cand_v;
+  int64_t* cand_idx = reinterpret_cast<int64_t*>(ws);
+  ws += cand_i;
+  int rc = atk_stage1(x, dtype, rows, n, row_stride, k0, j, interleaved, mode, cand_vals, cand_idx, k0,
+                      split_ws, split_bytes, stream);
   if (rc != ATK_OK) return rc;
   return atk_select(cand_vals, cand_idx, dtype, rows, k0, k0, k, out_vals, out_idx, out_row_stride,
                     sel_ws ? ws : nullptr, sel_ws, stream);
@@ -253,7 +276,7 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
 
 int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k,
                         int interleaved, void* out_vals, int64_t* out_idx, int64_t out_row_stride,
-                        void* stream) {
+                        void* workspace, size_t workspace_bytes, void* stream) {
   int rc = check_common(x, dtype, rows, n, row_stride, out_vals, out_idx, out_row_stride);
   if (rc != ATK_OK) return rc;
   if (k < 0) return ATK_ERR_BAD_ARG;
@@ -275,6 +298,8 @@ int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64
     a.j = 1;
     a.first_wins = true;
     a.sm_count = sm_count_of_current_device();
+    a.workspace = workspace;
+    a.workspace_bytes = workspace_bytes;
     a.stream = static_cast<cudaStream_t>(stream);
     return sweep_dispatch(a, dtype);
   }

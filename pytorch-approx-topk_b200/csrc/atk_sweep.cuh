@@ -37,6 +37,14 @@ struct SweepParams {
   int cw;                    // blockDim.x: threads across columns
   int s;                     // blockDim.y: stripe splits inside the block (power of two)
   int vec_out;               // 16-byte stores are legal for both outputs
+  // Cross-block stripe split: z blocks share one (row, tile); block z walks
+  // stripes [z*z_chunk, (z+1)*z_chunk) and writes its partial candidates to
+  // plane z of the scratch buffers (dense [z][rows][k0]); a merge kernel
+  // combines the planes.  z == 1: blocks write the outputs directly.
+  int z;
+  long long z_chunk;
+  void* part_vals;
+  long long* part_idx;
 };
 
 #ifndef ATK_SWEEP_THREADS
@@ -57,19 +65,18 @@ template <int V, int WORDS> struct SweepUnroll {
 #endif
 };
 
-// Walk this thread's complete stripes (ty, ty+S, ...) of its V columns starting
-// at c0, feeding every 16-byte (or scalar) load to QS::consume.  Returns the
-// first stripe number not visited (== l_full for the thread that owns the
-// ragged last stripe).
+// Walk this thread's complete stripes (l_begin+ty, l_begin+ty+S, ... < lf) of its
+// V columns starting at c0, feeding every 16-byte (or scalar) load to
+// QS::consume.  Returns the first stripe number not visited (== lf for the
+// thread that would own stripe lf).
 template <typename T, typename QS, int V, bool SKIP>
 __device__ __forceinline__ long long sweep_walk(QS (&qs)[V / QS::kCols], const SweepParams& p, const T* xrow,
-                                                long long c0, int ty, int S) {
+                                                long long c0, int ty, int S, long long l_begin, long long lf) {
   using VL = VecLoad<T, V>;
   constexpr int U = SweepUnroll<V / QS::kCols, QS::kWords>::kU;
-  const long long lf = p.l_full;
   const long long step = static_cast<long long>(S) * p.stripe_stride;
-  const T* ptr = xrow + c0 + static_cast<long long>(ty) * p.stripe_stride;
-  long long l = ty;
+  long long l = l_begin + ty;
+  const T* ptr = xrow + c0 + l * p.stripe_stride;
   // Main loop: U independent loads in flight, then U insertions, stripes in
   // increasing order so the scan rule resolves ties like the reference.
   for (; l + static_cast<long long>(U - 1) * S < lf; l += static_cast<long long>(U) * S) {
@@ -92,25 +99,29 @@ __device__ __forceinline__ long long sweep_walk(QS (&qs)[V / QS::kCols], const S
 // on two-column SIMD queues that are then converted to packed entries.
 template <typename T, typename Q, int V, bool SKIP, bool SIMD>
 __device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, const T* xrow, long long c0,
-                                           int ty, int S) {
+                                           int ty, int S, int z) {
+  // stripe range of this block (the whole column unless stripes are split over blocks)
+  const long long l_begin = static_cast<long long>(z) * p.z_chunk;
+  long long l_end = l_begin + p.z_chunk;
+  if (l_end > p.l_full || z == p.z - 1) l_end = p.l_full;
   long long l;
   if constexpr (SIMD) {
     using QS = Simd16Queue<T, Q::kJ, Q::kFirst>;
     QS qs[V / 2];
 #pragma unroll
     for (int i = 0; i < V / 2; ++i) qs[i].init();
-    l = sweep_walk<T, QS, V, SKIP>(qs, p, xrow, c0, ty, S);
+    l = sweep_walk<T, QS, V, SKIP>(qs, p, xrow, c0, ty, S, l_begin, l_end);
 #pragma unroll
     for (int e = 0; e < V; ++e)
 #pragma unroll
       for (int j = 0; j < Q::kJ; ++j) q[e].k[j] = qs[e / 2].packed_key(j, e & 1);
   } else {
-    l = sweep_walk<T, Q, V, SKIP>(q, p, xrow, c0, ty, S);
+    l = sweep_walk<T, Q, V, SKIP>(q, p, xrow, c0, ty, S, l_begin, l_end);
   }
   // Ragged last stripe (b does not divide n): only columns < rem exist.  It
   // belongs to the split that would visit stripe l_full, and is that thread's
   // highest stripe, so scan order is preserved.
-  if (p.rem > 0 && l == p.l_full) {
+  if (p.rem > 0 && l == p.l_full && z == p.z - 1) {
     const T* last = xrow + p.l_full * p.stripe_stride + c0;
 #pragma unroll
     for (int e = 0; e < V; ++e) {
@@ -152,8 +163,10 @@ sweep_kernel(const SweepParams p) {
   const int tx = threadIdx.x;
   const int ty = threadIdx.y;
   const int S = p.s;
-  const long long row = static_cast<long long>(blockIdx.x) / p.tiles;
-  const long long tile = static_cast<long long>(blockIdx.x) - row * p.tiles;
+  const long long unit = static_cast<long long>(blockIdx.x) / p.z;        // (row, tile)
+  const int z = static_cast<int>(static_cast<long long>(blockIdx.x) - unit * p.z);
+  const long long row = unit / p.tiles;
+  const long long tile = unit - row * p.tiles;
   const long long c0 = (tile * p.cw + tx) * V;
   const bool active = c0 < p.b;
   const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
@@ -162,7 +175,7 @@ sweep_kernel(const SweepParams p) {
 #pragma unroll
   for (int e = 0; e < V; ++e) q[e].init();
 
-  if (active) sweep_scan<T, Q, V, SKIP, SIMD>(q, p, xrow, c0, ty, S);
+  if (active) sweep_scan<T, Q, V, SKIP, SIMD>(q, p, xrow, c0, ty, S, z);
   if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
   if (!active || ty != 0) return;
 
@@ -183,11 +196,14 @@ sweep_kernel(const SweepParams p) {
         oi[e * J + j] = stripe * p.idx_stride + p.idx_offset + c0 + e;
       }
     }
-  const long long out_base = row * p.out_row_stride + c0 * J;
-  Bits* vdst = static_cast<Bits*>(p.out_vals) + out_base;
-  long long* idst = p.out_idx + out_base;
+  // direct to the outputs, or to plane z of the scratch when stripes are split over blocks
+  const long long k0 = p.b * J;
+  const long long out_base = p.z > 1 ? (static_cast<long long>(z) * p.rows + row) * k0 + c0 * J
+                                     : row * p.out_row_stride + c0 * J;
+  Bits* vdst = static_cast<Bits*>(p.z > 1 ? p.part_vals : p.out_vals) + out_base;
+  long long* idst = (p.z > 1 ? p.part_idx : p.out_idx) + out_base;
   constexpr int kValBytes = V * J * static_cast<int>(sizeof(Bits));
-  if (kValBytes % 16 == 0 && p.vec_out) {
+  if (kValBytes % 16 == 0 && p.vec_out && p.z == 1) {
     const uint4* src = reinterpret_cast<const uint4*>(ov);
 #pragma unroll
     for (int i = 0; i < kValBytes / 16; ++i) st_out_16(reinterpret_cast<uint4*>(vdst) + i, src[i]);
@@ -203,6 +219,159 @@ sweep_kernel(const SweepParams p) {
   }
 }
 
+// Combine the z partial candidate planes written by a stripe-split sweep: one
+// warp per (row, bucket); lane l ranks the entries of planes l, l+32, ... by
+// value, then by position (later wins; earlier with FIRST), the 32 lanes merge
+// by xor-shuffles, and lane 0 writes the best J in ascending order — exactly
+// what one block walking the whole column would have produced.
+template <typename T, int J, bool FIRST>
+struct PlaneEntryQueue {
+  using Bits = typename ElemTraits<T>::Bits;
+  float v[J];
+  long long i[J];
+  Bits b[J];   // raw bits travel with the entries so signed zeros survive
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int q = 0; q < J; ++q) {
+      v[q] = -INFINITY;
+      i[q] = FIRST ? 0x7fffffffffffffffll : -1ll;
+      b[q] = ElemTraits<T>::narrow(-INFINITY);
+    }
+  }
+  __device__ __forceinline__ void push(float nv, long long ni, Bits nb) {
+    bool p[J + 1];
+#pragma unroll
+    for (int q = 0; q < J; ++q) p[q] = (nv > v[q]) || (nv == v[q] && (FIRST ? ni < i[q] : ni > i[q]));
+    p[J] = false;
+#pragma unroll
+    for (int q = 0; q < J; ++q) {
+      const int up = q + 1 < J ? q + 1 : q;
+      const float tv = p[q + 1] ? v[up] : (p[q] ? nv : v[q]);
+      const long long ti = p[q + 1] ? i[up] : (p[q] ? ni : i[q]);
+      const Bits tb = p[q + 1] ? b[up] : (p[q] ? nb : b[q]);
+      v[q] = tv;
+      i[q] = ti;
+      b[q] = tb;
+    }
+  }
+};
+
+template <typename T, int J, bool FIRST>
+__global__ void __launch_bounds__(256)
+sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_vals,
+                          const long long* __restrict__ part_idx, int z, long long rows, long long b,
+                          typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
+                          long long out_row_stride) {
+  using Tr = ElemTraits<T>;
+  using Bits = typename Tr::Bits;
+  const int lane = threadIdx.x & 31;
+  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const bool valid = unit < rows * b;          // whole warps stay for the shuffles
+  const long long row = valid ? unit / b : 0;
+  const long long c = valid ? unit - row * b : 0;
+  const long long k0 = b * J;
+  PlaneEntryQueue<T, J, FIRST> q;
+  q.init();
+  if (valid) {
+    for (int zz = lane; zz < z; zz += 32) {
+      const long long base = (static_cast<long long>(zz) * rows + row) * k0 + c * J;
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const Bits bits = part_vals[base + j];
+        q.push(Tr::widen(bits), part_idx[base + j], bits);
+      }
+    }
+  }
+  for (int off = 16; off >= 1; off >>= 1) {
+    float ov[J];
+    long long oi[J];
+    uint32_t ob[J];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      ov[j] = __shfl_xor_sync(0xffffffffu, q.v[j], off);
+      oi[j] = __shfl_xor_sync(0xffffffffu, q.i[j], off);
+      ob[j] = __shfl_xor_sync(0xffffffffu, static_cast<uint32_t>(q.b[j]), off);
+    }
+#pragma unroll
+    for (int j = 0; j < J; ++j) q.push(ov[j], oi[j], static_cast<Bits>(ob[j]));
+  }
+  if (!valid || lane != 0) return;
+  Bits* vdst = out_vals + row * out_row_stride + c * J;
+  long long* idst = out_idx + row * out_row_stride + c * J;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    vdst[j] = q.b[j];
+    idst[j] = q.i[j];
+  }
+}
+
+// ---- launch shape (host) -------------------------------------------------------
+namespace sweep_detail {
+inline long long floor_pow2(long long v) {
+  long long r = 1;
+  while (r * 2 <= v) r *= 2;
+  return r;
+}
+inline long long ceil_pow2(long long v) {
+  long long r = 1;
+  while (r < v) r *= 2;
+  return r;
+}
+
+inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct SweepPlan {
+  long long cw, tiles, S, Z, z_chunk;
+};
+
+// Equal stripe ranges for Z blocks, with Z lowered so that no range is empty
+// (the last block must own the ragged last stripe).
+inline void set_chunks(SweepPlan& pl, long long l_full) {
+  if (pl.Z < 1) pl.Z = 1;
+  pl.z_chunk = (l_full + pl.Z - 1) / pl.Z;
+  if (pl.z_chunk < 1) pl.z_chunk = 1;
+  const long long used = (l_full + pl.z_chunk - 1) / pl.z_chunk;
+  pl.Z = used >= 1 ? used : 1;
+}
+
+// Threads across columns, stripe splits inside a block (S) and over blocks (Z).
+// Splitting happens only when the columns alone cannot fill the machine, and
+// never beyond what the block size or the stripe count allow.
+inline SweepPlan plan_sweep(long long rows, long long b, long long l_full, int V, int sm_count) {
+  SweepPlan pl;
+  const long long col_threads = (b + V - 1) / V;
+  pl.cw = col_threads < kSweepMaxThreads ? col_threads : kSweepMaxThreads;
+  pl.tiles = (col_threads + pl.cw - 1) / pl.cw;
+  pl.S = 1;
+  pl.Z = 1;
+  const long long want_threads = static_cast<long long>(sm_count) * 1024;
+  long long have_threads = rows * pl.tiles * pl.cw;
+  if (have_threads < want_threads && l_full >= 8) {
+    const long long by_block = floor_pow2(kSweepMaxThreads / pl.cw);
+    const long long by_work = floor_pow2(l_full / 4);
+    const long long by_need = ceil_pow2((want_threads + have_threads - 1) / have_threads);
+    pl.S = by_block;
+    if (by_work < pl.S) pl.S = by_work;
+    if (by_need < pl.S) pl.S = by_need;
+    if (pl.S < 1) pl.S = 1;
+  }
+  have_threads *= pl.S;
+  // Over blocks: only when a thread would otherwise walk a long column (a
+  // second launch merges the planes, which costs more than it saves on short
+  // ones); every block keeps at least 32 stripes per in-block split.
+  if (have_threads * 2 <= want_threads && l_full / pl.S >= 256) {
+    long long z = want_threads / have_threads;
+    const long long by_work = l_full / (pl.S * 32);
+    if (by_work < z) z = by_work;
+    if (z > 1024) z = 1024;
+    if (z >= 2) pl.Z = z;
+  }
+  set_chunks(pl, l_full);
+  return pl;
+}
+
+}  // namespace sweep_detail
+
 // Arguments of the typed launchers (one translation unit per element type).
 struct SweepLaunch {
   const void* x;
@@ -216,8 +385,23 @@ struct SweepLaunch {
   int j;
   bool first_wins;          // k_b = 1 arg-max conventions (J must be 1)
   int sm_count;
+  void* workspace;          // optional scratch for splitting stripes over blocks (may be null)
+  size_t workspace_bytes;
   cudaStream_t stream;
 };
+
+// Scratch the stripe split over blocks would like for this shape, assuming the
+// widest vector path (0 when the shape fills the GPU without it).  The launch
+// uses as many planes as the scratch it is given holds.
+inline size_t sweep_workspace_bytes(int elem_size, long long rows, long long n, long long b, int j, int sm_count) {
+  if (rows <= 0 || b <= 0 || n < b) return 0;
+  const int vec = 16 / elem_size;
+  const sweep_detail::SweepPlan pl = sweep_detail::plan_sweep(rows, b, n / b, (j >= 3 && elem_size == 2) ? 4 : vec, sm_count);
+  if (pl.Z <= 1) return 0;
+  const size_t k0 = static_cast<size_t>(b) * j;
+  return sweep_detail::align256(static_cast<size_t>(pl.Z) * rows * k0 * elem_size) +
+         static_cast<size_t>(pl.Z) * rows * k0 * 8 + 256;
+}
 
 int launch_sweep_f32(const SweepLaunch& a);
 int launch_sweep_f16(const SweepLaunch& a);

@@ -11,17 +11,6 @@ namespace atk {
 
 namespace sweep_detail {
 
-inline long long floor_pow2(long long v) {
-  long long r = 1;
-  while (r * 2 <= v) r *= 2;
-  return r;
-}
-inline long long ceil_pow2(long long v) {
-  long long r = 1;
-  while (r < v) r *= 2;
-  return r;
-}
-
 inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
   p.x = a.x;
   p.out_vals = a.out_vals;
@@ -41,41 +30,44 @@ inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
               ((a.out_row_stride * 8) % 16 == 0);
 }
 
-// ---- stage 1 only ---------------------------------------------------------
+// ---- stage 1 -----------------------------------------------------------------
 template <typename T, typename Q, int J, int V, bool SIMD>
 int launch_stage1(const SweepLaunch& a) {
+  using Bits = typename ElemTraits<T>::Bits;
   SweepParams p;
   fill_common(p, a, static_cast<int>(sizeof(T)));
   if (p.l_full + 1 >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
 
-  const long long col_threads = (a.b + V - 1) / V;
-  long long cw = col_threads < kSweepMaxThreads ? col_threads : kSweepMaxThreads;
-  const long long tiles = (col_threads + cw - 1) / cw;
-  p.tiles = tiles;
-  p.cw = static_cast<int>(cw);
-  if (a.rows * tiles >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
-
-  // Stripe splits inside the block: only when the columns alone cannot fill
-  // the machine, never more than the block size or the stripe count allow.
-  long long S = 1;
-  const long long want_threads = static_cast<long long>(a.sm_count) * 1024;
-  const long long have_threads = a.rows * tiles * cw;
-  if (have_threads < want_threads && p.l_full >= 8) {
-    const long long by_block = floor_pow2(kSweepMaxThreads / cw);
-    const long long by_work = floor_pow2(p.l_full / 4);
-    const long long by_need = ceil_pow2((want_threads + have_threads - 1) / have_threads);
-    S = by_block;
-    if (by_work < S) S = by_work;
-    if (by_need < S) S = by_need;
-    if (S < 1) S = 1;
+  SweepPlan pl = plan_sweep(a.rows, a.b, p.l_full, V, a.sm_count);
+  const long long k0 = a.b * J;
+  if (pl.Z > 1) {
+    // use as many planes as the caller's scratch holds (none: no split over blocks)
+    const size_t per_z = static_cast<size_t>(a.rows) * k0 * (sizeof(Bits) + 8);
+    long long fit = 0;
+    if (a.workspace != nullptr && a.workspace_bytes > 256) fit = static_cast<long long>((a.workspace_bytes - 256) / per_z);
+    if (fit < pl.Z) pl.Z = fit >= 2 ? fit : 1;
+    set_chunks(pl, p.l_full);
   }
-  p.s = static_cast<int>(S);
+  p.tiles = pl.tiles;
+  p.cw = static_cast<int>(pl.cw);
+  p.s = static_cast<int>(pl.S);
+  p.z = static_cast<int>(pl.Z);
+  p.z_chunk = pl.z_chunk;
+  p.part_vals = nullptr;
+  p.part_idx = nullptr;
+  if (pl.Z > 1) {
+    // dense planes [z][rows][k0]: all value planes first, then all position planes
+    unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+    p.part_vals = ws;
+    p.part_idx = reinterpret_cast<long long*>(ws + align256(static_cast<size_t>(pl.Z) * a.rows * k0 * sizeof(Bits)));
+  }
+  if (a.rows * pl.tiles * pl.Z >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
 
-  const size_t smem = S > 1 ? static_cast<size_t>(S / 2) * (V * Q::kWords) * cw * 4 : 0;
-  const dim3 grid(static_cast<unsigned>(a.rows * tiles));
-  const dim3 block(static_cast<unsigned>(cw), static_cast<unsigned>(S));
+  const size_t smem = pl.S > 1 ? static_cast<size_t>(pl.S / 2) * (V * Q::kWords) * pl.cw * 4 : 0;
+  const dim3 grid(static_cast<unsigned>(a.rows * pl.tiles * pl.Z));
+  const dim3 block(static_cast<unsigned>(pl.cw), static_cast<unsigned>(pl.S));
   // The head test pays off once a thread walks a long column.
-  bool skip = (p.l_full / S) >= 256;
+  bool skip = (pl.z_chunk / pl.S) >= 256;
 #ifdef ATK_DEBUG_NO_SKIP
   skip = false;
 #endif
@@ -84,7 +76,17 @@ int launch_stage1(const SweepLaunch& a) {
   else
     sweep_kernel<T, Q, J, V, false, SIMD><<<grid, block, smem, a.stream>>>(p);
   note_launch();
-  return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
+  if (pl.Z > 1) {
+    const long long blocks = (a.rows * a.b + 7) / 8;   // one warp per (row, bucket), 8 warps per block
+    if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+    sweep_merge_planes_kernel<T, J, Q::kFirst><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, a.rows, a.b, static_cast<Bits*>(a.out_vals),
+        a.out_idx, a.out_row_stride);
+    note_launch();
+    if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
+  }
+  return ATK_OK;
 }
 
 // Queue layout: 16-bit inputs use packed 32-bit entries whenever the stripe

@@ -15,13 +15,17 @@ def _stream(x):
     return torch.cuda.current_stream(x.device).cuda_stream
 
 
-def stage1(x: torch.Tensor, k0: int, j: int, interleaved: bool = True, mode: int = -1):
+def stage1(x: torch.Tensor, k0: int, j: int, interleaved: bool = True, mode: int = -1, use_workspace: bool = True):
     assert x.is_cuda and x.ndim == 2 and x.stride(1) == 1
     rows, n = x.shape
     vals = torch.empty((rows, k0), device=x.device, dtype=x.dtype)
     idx = torch.empty((rows, k0), device=x.device, dtype=torch.int64)
-    rc = _native.lib().atk_stage1(x.data_ptr(), _native.dtype_code(x.dtype), rows, n, x.stride(0), k0, j,
-                                  int(interleaved), mode, vals.data_ptr(), idx.data_ptr(), k0, _stream(x))
+    lib = _native.lib()
+    code = _native.dtype_code(x.dtype)
+    ws_bytes = lib.atk_stage1_workspace_bytes(code, rows, n, k0, j, int(interleaved)) if use_workspace else 0
+    ws = torch.empty(max(ws_bytes, 1), device=x.device, dtype=torch.uint8)
+    rc = lib.atk_stage1(x.data_ptr(), code, rows, n, x.stride(0), k0, j, int(interleaved), mode,
+                        vals.data_ptr(), idx.data_ptr(), k0, ws.data_ptr() if ws_bytes else None, ws_bytes, _stream(x))
     _native.check(rc)
     return vals, idx
 
@@ -75,8 +79,12 @@ def bucketed_argmax(x: torch.Tensor, k: int, interleaved: bool):
     rows, n = x.shape
     vals = torch.empty((rows, k), device=x.device, dtype=x.dtype)
     idx = torch.empty((rows, k), device=x.device, dtype=torch.int64)
-    rc = _native.lib().atk_bucketed_argmax(x.data_ptr(), _native.dtype_code(x.dtype), rows, n, x.stride(0), k,
-                                           int(interleaved), vals.data_ptr(), idx.data_ptr(), k, _stream(x))
+    lib = _native.lib()
+    code = _native.dtype_code(x.dtype)
+    ws_bytes = lib.atk_stage1_workspace_bytes(code, rows, n, k, 1, int(interleaved)) if k <= n else 0
+    ws = torch.empty(max(ws_bytes, 1), device=x.device, dtype=torch.uint8)
+    rc = lib.atk_bucketed_argmax(x.data_ptr(), code, rows, n, x.stride(0), k, int(interleaved), vals.data_ptr(),
+                                 idx.data_ptr(), k, ws.data_ptr() if ws_bytes else None, ws_bytes, _stream(x))
     _native.check(rc)
     return vals, idx
 

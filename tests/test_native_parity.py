@@ -94,6 +94,39 @@ def test_stage1_long_columns_head_test_path(dtype):
     check_stage1_exact(make(1, 1 << 20, dtype, 8, "ties"), 8, 4, True)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j", [1, 2, 3, 4])
+def test_stage1_stripes_split_over_blocks(dtype, j):
+    # Few rows and few buckets: with scratch the stripes of a column are split over
+    # several blocks and merged; the result must not depend on the scratch.
+    lib = api._native.lib()
+    for seed, (rows, n, k0) in enumerate([(1, 1 << 20, 64), (1, (1 << 20) + 77, 32), (2, 300000, 96),
+                                          (3, 1 << 18, 16), (1, 1 << 22, 1024), (5, 1000003, 8)]):
+        k0 = (k0 // j) * j
+        assert lib.atk_stage1_workspace_bytes(api._native.dtype_code(dtype), rows, n, k0, j, 1) > 0
+        for dist in ("randn", "ties"):
+            x = make(rows, n, dtype, 950 + seed, dist)
+            v, i = api.stage1(x, k0, j, True, use_workspace=True)
+            v0, i0 = api.stage1(x, k0, j, True, use_workspace=False)
+            assert torch.equal(bits(v), bits(v0)) and torch.equal(i, i0), (rows, n, k0, dist)
+            ov, oi = oracle.stage1(x.cpu(), k0, j, True)
+            assert torch.equal(bits(v), bits(ov)) and torch.equal(i.cpu(), oi), (rows, n, k0, dist)
+
+
+def test_operator_single_row_small_k_uses_the_split_and_matches_oracle():
+    from approx_topk import topk
+    from approx_topk.experimental.bucketed_argmax import topk_torch
+
+    x = make(1, 128256, torch.float16, 960)
+    for j, k_mult in [(1, 1), (2, 1), (1, 4), (2, 4)]:
+        v, i = topk(x, 64, -1, j=j, k_mult=k_mult)
+        ov, oi = oracle.topk(x.cpu(), 64, j=j, k_mult=k_mult)
+        assert_valid_selection(x, v, i, ov)
+    v, i = topk_torch(x, 64, -1, True)
+    ov, oi = oracle.bucketed_argmax(x.cpu(), 64, True)
+    assert torch.equal(bits(v), bits(ov)) and torch.equal(i.cpu(), oi)
+
+
 def test_stage1_row_stride_and_unaligned_base():
     base = make(9, 1100, torch.float32, 3)
     view = base[:, 3:1027]            # base pointer only 4-byte aligned, row stride 1100
