@@ -2,18 +2,27 @@
 
 Drop-in for the operator API of graphcore-research/pytorch-approx-topk:
 ``approx_topk.topk``, ``approx_topk.priority_queue.topk`` (the
-``approx_topk::topk`` custom op) and ``approx_topk.experimental.*``.
+``approx_topk::topk`` custom op) and ``approx_topk.experimental.*``; plus
+``approx_topk.host_buffers`` and ``approx_topk.distributed``.
 """
 
-from typing import Protocol
+from __future__ import annotations
 
-from torch import Tensor
+import typing
 
-from .priority_queue import topk as topk
+import torch
+
+from . import priority_queue
+
+__all__ = ["topk", "Topk"]
+
+#: The operator, ``topk(xs, k, dim, j=1, k_mult=1, interleaved=True, multithread_buckets=False)``.
+topk = priority_queue.topk
 
 
-class Topk(Protocol):
-    """Anything callable like ``torch.topk(xs, k, dim) -> (values, indices)``."""
+class Topk(typing.Protocol):
+    """Structural type of anything callable like ``torch.topk``:
+    ``f(xs, k, dim) -> (values, indices)``."""
 
-    @staticmethod
-    def __call__(xs: Tensor, k: int, dim: int) -> tuple[Tensor, Tensor]: ...
+    def __call__(self, xs: torch.Tensor, k: int, dim: int) -> tuple[torch.Tensor, torch.Tensor]:
+        raise NotImplementedError

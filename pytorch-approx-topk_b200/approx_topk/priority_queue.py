@@ -41,17 +41,13 @@ def topk(
         input dtype, indices int64 positions along ``dim``.  Order along
         ``dim`` is unspecified.
     """
-    if dim < 0:
-        dim = xs.ndim + dim
-    if j < k and dim != xs.ndim - 1:
+    dim = _normalise_dim(xs, dim)
+    if dim != xs.ndim - 1 and j < k:
+        # several buckets along a strided axis are not supported (same rule as the reference)
         raise NotImplementedError("This topk only currently works on the last dim")
-
-    if k_mult == 1:
-        k0 = k
-    elif k_mult > 1:
-        k0 = k * k_mult
-    else:
+    if k_mult < 1:
         raise ValueError(f"k_mult must be >=1, was {k_mult}")
+    k0 = k * k_mult
 
     _native.require_cuda(xs)
     code = _native.dtype_code(xs.dtype)
@@ -86,8 +82,7 @@ def topk(
     return values, indices
 
 
-@topk.register_fake
-def _(
+def _fake_topk(
     xs: Tensor,
     k: int,
     dim: int,
@@ -96,13 +91,20 @@ def _(
     interleaved: bool = True,
     multithread_buckets: bool | None = False,
 ) -> tuple[Tensor, Tensor]:
-    output_shape = _get_output_shape(xs, k, dim)
-    values = torch.empty(output_shape, device=xs.device, dtype=xs.dtype)
-    indices = torch.empty(output_shape, dtype=torch.int64, device=xs.device)
-    return values, indices
+    """Meta implementation: shapes and dtypes only (for torch.compile / opcheck)."""
+    shape = _get_output_shape(xs, k, dim)
+    return xs.new_empty(shape), xs.new_empty(shape, dtype=torch.int64)
+
+
+topk.register_fake(_fake_topk)
+
+
+def _normalise_dim(xs: Tensor, dim: int) -> int:
+    return dim + xs.ndim if dim < 0 else dim
 
 
 def _get_output_shape(xs: Tensor, k: int, dim: int) -> list[int]:
-    output_shape = list(xs.shape)
-    output_shape[dim] = k
-    return output_shape
+    """The input's shape with ``k`` entries along ``dim``."""
+    shape = list(xs.shape)
+    shape[dim] = k
+    return shape

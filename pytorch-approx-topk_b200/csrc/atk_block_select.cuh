@@ -1,8 +1,6 @@
-// Block-level pieces of the exact select (stage 2), shared by the stand-alone
-// select kernel and by the fused row kernel.
+// Warp- and block-level pieces of the exact select (stage 2).
 //
-// Keys are order-preserving 32-bit images of the candidate values, possibly
-// with payload in low bits that `vmask` hides from every comparison.
+// Keys are order-preserving 32-bit images of the candidate values.
 #pragma once
 
 #include "atk_common.cuh"
@@ -76,36 +74,6 @@ __device__ __forceinline__ void hist_add_warp(uint32_t* hist, uint32_t digit, bo
   if (!valid) return;
   const uint32_t peers = __match_any_sync(active, digit);
   if (lane == __ffs(peers) - 1) atomicAdd(&hist[digit], static_cast<uint32_t>(__popc(peers)));
-}
-
-// MSB-first radix select over n keys in shared memory: finds the k-th largest
-// masked key `thr` and how many keys equal to it belong to the top k (`need`).
-// `passes` 8-bit digits are examined starting at bit 31.  hist: 256 words,
-// misc: 2 words of shared memory.  All threads of the block must call it; on
-// return every thread holds the same (thr, need).
-__device__ __forceinline__ void block_select_threshold(const uint32_t* keys, int n, uint32_t k, int passes,
-                                                       uint32_t* hist, uint32_t* misc, int tid, int nthreads,
-                                                       uint32_t& thr, uint32_t& need) {
-  uint32_t prefix = 0, mask = 0;
-  need = k;
-#pragma unroll 1
-  for (int pass = 0; pass < passes; ++pass) {
-    const int shift = 24 - 8 * pass;
-    for (int i = tid; i < 256; i += nthreads) hist[i] = 0;
-    __syncthreads();
-    for (int base = 0; base < n; base += nthreads) {  // warp-uniform trip count
-      const int i = base + tid;
-      const uint32_t key = i < n ? keys[i] : 0u;
-      hist_add_warp(hist, (key >> shift) & 255u, i < n && (key & mask) == prefix, tid & 31);
-    }
-    __syncthreads();
-    if (tid < 32) pick_digit(hist, need, tid, &misc[0], &misc[1]);
-    __syncthreads();
-    prefix |= misc[0] << shift;
-    mask |= 255u << shift;
-    need = misc[1];
-  }
-  thr = prefix;
 }
 
 }  // namespace atk

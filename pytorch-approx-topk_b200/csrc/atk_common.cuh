@@ -46,8 +46,11 @@ template <> struct ElemTraits<__nv_bfloat16> {
   static __device__ __forceinline__ float lowest() { return -3.3895313892515355e+38f; }
 };
 
-// ---- streaming loads: the input is read exactly once, keep it out of L1 and
-// mark it evict-first in L2 ------------------------------------------------
+// ---- loads of the input, which is read exactly once -------------------------
+// Input loads.  Plain cached loads measured 2-6 % faster than ld.global.cs /
+// ld.global.nc.L1::no_allocate on the streaming workloads, so that is the
+// default; ATK_LD_MODE=0 (evict-first) / 1 (read-only path) remain as build
+// knobs for re-measuring on other parts.
 #ifndef ATK_LD_MODE
 #define ATK_LD_MODE 3
 #endif
@@ -56,18 +59,8 @@ __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
   return __ldcs(reinterpret_cast<const uint4*>(p));
 #elif ATK_LD_MODE == 1
   return __ldg(reinterpret_cast<const uint4*>(p));
-#elif ATK_LD_MODE == 2
-  uint4 r;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
-  return r;
-#elif ATK_LD_MODE == 3
+#else
   return *reinterpret_cast<const uint4*>(p);
-#elif ATK_LD_MODE == 4
-  uint4 r;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
-  return r;
 #endif
 }
 __device__ __forceinline__ uint2 ld_stream_8(const void* p) {
@@ -79,20 +72,8 @@ __device__ __forceinline__ uint2 ld_stream_8(const void* p) {
   return *reinterpret_cast<const uint2*>(p);
 #endif
 }
-#ifndef ATK_ST_MODE
-#define ATK_ST_MODE 0
-#endif
-__device__ __forceinline__ void st_out_16(uint4* p, const uint4& v) {
-#if ATK_ST_MODE == 0
-  *p = v;
-#elif ATK_ST_MODE == 1
-  __stcs(p, v);
-#elif ATK_ST_MODE == 2
-  __stcg(p, v);
-#elif ATK_ST_MODE == 3
-  __stwt(p, v);
-#endif
-}
+// Output stores (default caching; streaming variants made no difference).
+__device__ __forceinline__ void st_out_16(uint4* p, const uint4& v) { *p = v; }
 __device__ __forceinline__ uint32_t ld_stream_4(const void* p) {
   return __ldcs(reinterpret_cast<const unsigned int*>(p));
 }
@@ -233,25 +214,6 @@ __device__ __forceinline__ void queue_push_ranked(float (&qv)[J], int (&qi)[J], 
   for (int i = 0; i < J; ++i) {
     const float nv = p[i + 1] ? qv[i + 1 < J ? i + 1 : i] : (p[i] ? v : qv[i]);
     const int   ni = p[i + 1] ? qi[i + 1 < J ? i + 1 : i] : (p[i] ? pos : qi[i]);
-    qv[i] = nv;
-    qi[i] = ni;
-  }
-}
-
-// 64-bit position flavour for the contiguous-bucket kernel.
-template <int J, bool FIRST>
-__device__ __forceinline__ void queue_push_ranked64(float (&qv)[J], long long (&qi)[J], float v, long long pos) {
-  bool p[J + 1];
-#pragma unroll
-  for (int i = 0; i < J; ++i) {
-    if (FIRST) p[i] = (v > qv[i]) || (v == qv[i] && pos < qi[i]);
-    else       p[i] = (v > qv[i]) || (v == qv[i] && pos > qi[i]);
-  }
-  p[J] = false;
-#pragma unroll
-  for (int i = 0; i < J; ++i) {
-    const float nv = p[i + 1] ? qv[i + 1 < J ? i + 1 : i] : (p[i] ? v : qv[i]);
-    const long long ni = p[i + 1] ? qi[i + 1 < J ? i + 1 : i] : (p[i] ? pos : qi[i]);
     qv[i] = nv;
     qi[i] = ni;
   }

@@ -1,4 +1,4 @@
-// Per-column queues of the J best elements, in two register layouts.
+// Per-column queues of the J best elements, in three register layouts.
 //
 // FloatQueue  — J (float value, int stripe) pairs; works for every dtype (the
 //               16-bit formats widen to float exactly) and follows the
@@ -14,8 +14,10 @@
 //               rank by bit pattern (above +inf / below -inf) and -0.0 ties
 //               with +0.0 exactly as in a float compare.
 //
-// Both expose the same interface to the sweep kernels:
-//   init(), consume<SKIP>(q[V], raw, stripe), push_tail(elem bits, stripe),
+// Simd16Queue — scan-time form of PackedQueue on the vector path, see below.
+//
+// FloatQueue and PackedQueue expose the same interface to the sweep kernel:
+//   init(), consume<V, SKIP>(q[V], raw, stripe), push_tail(elem bits, stripe),
 //   store/merge through shared memory words, and accessors for the write-out.
 #pragma once
 
@@ -85,7 +87,6 @@ struct FloatQueue {
                                   static_cast<int>(base[(2 * q + 1) * stride]));
   }
 
-  __device__ __forceinline__ bool empty(int q) const { return FIRST && s[q] == kSentinelFirst; }
   __device__ __forceinline__ long long stripe(int q) const { return s[q]; }
   // value bits for the output; `elem` is only read to restore a zero's sign
   __device__ __forceinline__ typename ElemTraits<T>::Bits value_bits(int q, const T*) const {
@@ -190,7 +191,6 @@ struct PackedQueue {
     for (int q = 0; q < J; ++q) push(base[q * stride]);
   }
 
-  __device__ __forceinline__ bool empty(int q) const { return k[q] == 0u; }
   __device__ __forceinline__ long long stripe(int q) const {
     const uint32_t l = k[q] & 0xffffu;
     return FIRST ? (0xffffu - l) : l;

@@ -47,22 +47,17 @@ struct SweepParams {
   long long* part_idx;
 };
 
+// Threads per block.  128 measured best on the headline workload (64: +2 %,
+// 256: +4 %, 512: +15 % time); kept as a build knob.
 #ifndef ATK_SWEEP_THREADS
 #define ATK_SWEEP_THREADS 128
-#endif
-#ifndef ATK_SWEEP_MINBLOCKS
-#define ATK_SWEEP_MINBLOCKS 1
 #endif
 constexpr int kSweepMaxThreads = ATK_SWEEP_THREADS;
 
 template <int V, int WORDS> struct SweepUnroll {
   // independent 16-byte loads kept in flight per thread; fewer when the
   // queues themselves take many registers
-#ifdef ATK_DEBUG_U
-  static constexpr int kU = ATK_DEBUG_U;
-#else
   static constexpr int kU = (V * WORDS <= 32) ? 8 : 4;
-#endif
 };
 
 // Walk this thread's complete stripes (l_begin+ty, l_begin+ty+S, ... < lf) of its
@@ -154,7 +149,7 @@ __device__ __forceinline__ void sweep_merge(Q (&q)[V], uint32_t* smem, int cw, i
 // Stage 1 only: every block handles one tile of columns of one row and writes
 // the J candidates of each bucket (slot = bucket*J + q, ascending).
 template <typename T, typename Q, int J, int V, bool SKIP, bool SIMD>
-__global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
+__global__ void __launch_bounds__(kSweepMaxThreads)
 sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;

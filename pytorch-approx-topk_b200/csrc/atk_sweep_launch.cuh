@@ -67,10 +67,7 @@ int launch_stage1(const SweepLaunch& a) {
   const dim3 grid(static_cast<unsigned>(a.rows * pl.tiles * pl.Z));
   const dim3 block(static_cast<unsigned>(pl.cw), static_cast<unsigned>(pl.S));
   // The head test pays off once a thread walks a long column.
-  bool skip = (pl.z_chunk / pl.S) >= 256;
-#ifdef ATK_DEBUG_NO_SKIP
-  skip = false;
-#endif
+  const bool skip = (pl.z_chunk / pl.S) >= 256;
   if (skip)
     sweep_kernel<T, Q, J, V, true, SIMD><<<grid, block, smem, a.stream>>>(p);
   else
@@ -96,11 +93,7 @@ template <typename T, int J, int V, bool FIRST>
 int launch_by_queue(const SweepLaunch& a) {
   if constexpr (sizeof(T) == 2) {
     if (a.n / a.b + 1 <= 65536) {
-#ifdef ATK_NO_SIMD16
-      return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, false>(a);
-#else
       return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4)>(a);
-#endif
     }
   }
   return launch_stage1<T, FloatQueue<T, J, FIRST>, J, V, false>(a);
@@ -137,9 +130,7 @@ int launch_sweep(const SweepLaunch& a) {
            ((a.stripe_stride * s) % bytes == 0) && (a.b % v == 0);
   };
   if constexpr (sizeof(T) == 2) {
-#ifndef ATK_NO_HALF_VECTOR
     if (a.j >= 3 && fits(4)) return launch_by_j<T, 4>(a);
-#endif
     if (fits(kVec)) return launch_by_j<T, kVec>(a);
     if (fits(4)) return launch_by_j<T, 4>(a);
     return launch_by_j<T, 1>(a);
