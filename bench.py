@@ -235,7 +235,7 @@ def run_reference(args, rank: int) -> int:
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    args.out.emit(json.dumps(line))
     return 0
 
 
@@ -393,7 +393,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_path_rate(w, args.cpu_seconds, os.cpu_count() or 1)
-        print(json.dumps(line), flush=True)
+        args.out.emit(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -418,6 +418,21 @@ def run_e2e(w, dev, x_dev, e2e_steps, barrier) -> float:
     return (time.perf_counter() - t0) * 1e3
 
 
+class StdoutToStderr:
+    """Everything written to file descriptor 1 while this is active goes to stderr
+    (NCCL prints its version banner to stdout at communicator creation); the one
+    JSON line of the contract is written to the real stdout with emit()."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self._real = os.dup(1)
+        os.dup2(2, 1)
+
+    def emit(self, text: str) -> None:
+        sys.stdout.flush()
+        os.write(self._real, (text + "\n").encode())
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -434,6 +449,7 @@ def main() -> int:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    args.out = StdoutToStderr()
     if args.impl == "reference":
         return run_reference(args, rank)
     if world != args.gpus and world > 1:

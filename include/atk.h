@@ -97,10 +97,14 @@ int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_st
  * stripes x total_buckets view of the row; every bucket here has exactly
  * `stripes` elements.  Writes cols*j candidates whose indices are positions in
  * the full row: stripe*total_buckets + col_offset + col.
+ * workspace: optional scratch of atk_stage1_slab_workspace_bytes() bytes, same
+ * role as in atk_stage1 (a slab of few columns needs it to occupy the GPU).
  */
+size_t atk_stage1_slab_workspace_bytes(int dtype, int64_t stripes, int64_t cols, int j);
 int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols,
                     int64_t total_buckets, int64_t col_offset, int j,
-                    void* out_vals, int64_t* out_idx, void* stream);
+                    void* out_vals, int64_t* out_idx,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Stage 2 — exact top-k of k0 candidates per row, indices carried along.
@@ -137,7 +141,7 @@ int atk_select(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_
  * Limit: when atk_select_workspace_bytes(dtype, rows, k0, k) exceeds the
  * built-in 1 MiB the call is refused with ATK_ERR_SCRATCH_LIMIT and launches
  * nothing (rows of up to 32768 candidates need no scratch at all; one row of
- * 2^21 fp32 candidates needs about 6 KiB; 64 rows of 2^24 about 0.8 MiB).
+ * 2^21 fp32 candidates needs about 13 KiB; 16 rows of 2^20 about 0.13 MiB).
  *
  * First call on a device: looks up the device address of the array
  * (cudaGetSymbolAddress, with that device current) and caches it per device.

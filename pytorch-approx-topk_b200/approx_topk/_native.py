@@ -42,7 +42,8 @@ SIGNATURES = {
     "atk_device_supported": (_int, []),
     "atk_stage1_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _int]),
     "atk_stage1": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
-    "atk_stage1_slab": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp]),
+    "atk_stage1_slab_workspace_bytes": (_sz, [_int, _i64, _i64, _int]),
+    "atk_stage1_slab": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
     "atk_select_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "atk_select": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_select_static": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),

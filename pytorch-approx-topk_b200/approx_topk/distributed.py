@@ -75,10 +75,15 @@ def _native_stage1_slab(slab: Tensor, total_buckets: int, col_offset: int, j: in
     stripes, cols = slab.shape
     vals = torch.empty(cols * j, device=slab.device, dtype=slab.dtype)
     idx = torch.empty(cols * j, device=slab.device, dtype=torch.int64)
+    lib = _native.lib()
+    code = _native.dtype_code(slab.dtype)
     with torch.cuda.device(slab.device):
-        status = _native.lib().atk_stage1_slab(
-            slab.data_ptr(), _native.dtype_code(slab.dtype), stripes, cols, total_buckets, col_offset, j,
-            vals.data_ptr(), idx.data_ptr(), _native.current_stream_ptr(slab.device))
+        ws_bytes = lib.atk_stage1_slab_workspace_bytes(code, stripes, cols, j)
+        ws = torch.empty(ws_bytes, device=slab.device, dtype=torch.uint8) if ws_bytes else None
+        status = lib.atk_stage1_slab(
+            slab.data_ptr(), code, stripes, cols, total_buckets, col_offset, j,
+            vals.data_ptr(), idx.data_ptr(), ws.data_ptr() if ws is not None else None, ws_bytes,
+            _native.current_stream_ptr(slab.device))
     _native.check(status)
     return vals, idx
 

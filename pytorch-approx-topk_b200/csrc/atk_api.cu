@@ -145,8 +145,15 @@ int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_st
   return launch_contig(c, dtype);
 }
 
+size_t atk_stage1_slab_workspace_bytes(int dtype, int64_t stripes, int64_t cols, int j) {
+  const int s = elem_size(dtype);
+  if (s == 0 || stripes <= 0 || cols <= 0 || j < 1 || j > 4 || j > stripes) return 0;
+  return sweep_workspace_bytes(s, 1, stripes * cols, cols, j, sm_count_of_current_device());
+}
+
 int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols, int64_t total_buckets,
-                    int64_t col_offset, int j, void* out_vals, int64_t* out_idx, void* stream) {
+                    int64_t col_offset, int j, void* out_vals, int64_t* out_idx, void* workspace,
+                    size_t workspace_bytes, void* stream) {
   if (elem_size(dtype) == 0) return ATK_ERR_BAD_DTYPE;
   if (stripes < 0 || cols < 0 || total_buckets < cols || col_offset < 0) return ATK_ERR_BAD_ARG;
   if (stripes == 0 || cols == 0) return ATK_OK;
@@ -168,8 +175,8 @@ int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols, 
   a.j = j;
   a.first_wins = false;
   a.sm_count = sm_count_of_current_device();
-  a.workspace = nullptr;
-  a.workspace_bytes = 0;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
   return sweep_dispatch(a, dtype);
 }

@@ -21,7 +21,8 @@ namespace atk {
 namespace {
 
 constexpr int kSmallMaxK0 = 32768;   // 1024 threads x 32 candidates in registers
-constexpr int kChunk = 16384;        // candidates per block on the large path
+constexpr int kChunk = 2048;         // candidates per block on the large path
+constexpr int kLargeItems = kChunk / 256;  // per thread, all loaded before any is used
 constexpr int kLargeThreads = 256;
 
 template <typename T> struct KeyOf;
@@ -172,45 +173,21 @@ struct RowState {
   uint32_t prefix, mask, need, pad;
 };
 
+// One radix pass.  Every block histograms its chunk into the row's global
+// histogram; the block that finishes last for a row (a ticket counter, no
+// waiting) then picks the digit and advances the row's (prefix, mask, need).
+// `tickets` and `hist` must be zero on entry (one memset per select call).
 template <typename T>
 __global__ void __launch_bounds__(kLargeThreads)
 select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
-                   long long cand_row_stride, int pass, const RowState* __restrict__ state,
-                   uint32_t* __restrict__ hist /* [rows][passes][256] */) {
+                   long long cand_row_stride, int pass, long long k, RowState* __restrict__ state,
+                   uint32_t* __restrict__ hist /* [rows][passes][256] */,
+                   uint32_t* __restrict__ tickets /* [rows][passes + 1] */) {
   using K = KeyOf<T>;
   __shared__ uint32_t sh[256];
-  const long long row = blockIdx.y;
-  uint32_t prefix = 0, mask = 0;
-  if (pass > 0) {
-    prefix = state[row].prefix;
-    mask = state[row].mask;
-  }
-  const int shift = 24 - 8 * pass;
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = 0;
-  __syncthreads();
-  const long long begin = static_cast<long long>(blockIdx.x) * kChunk;
-  long long end = begin + kChunk;
-  if (end > k0) end = k0;
-  const auto* vrow = cand_vals + row * cand_row_stride;
-  for (long long base = begin; base < end; base += blockDim.x) {  // warp-uniform trip count
-    const long long i = base + threadIdx.x;
-    uint32_t key = 0u;
-    if (i < end) key = K::key(vrow[i]);
-    hist_add_warp(sh, (key >> shift) & 255u, i < end && (key & mask) == prefix, threadIdx.x & 31);
-  }
-  __syncthreads();
-  uint32_t* gh = hist + (row * K::kPasses + pass) * 256;
-  for (int i = threadIdx.x; i < 256; i += blockDim.x)
-    if (sh[i]) atomicAdd(&gh[i], sh[i]);
-}
-
-template <typename T>
-__global__ void __launch_bounds__(32)
-select_pick_kernel(int pass, long long k, RowState* __restrict__ state,
-                   const uint32_t* __restrict__ hist) {
-  using K = KeyOf<T>;
   __shared__ uint32_t res[2];
-  const long long row = blockIdx.x;
+  __shared__ bool last;
+  const long long row = blockIdx.y;
   RowState st;
   if (pass == 0) {
     st.prefix = 0;
@@ -220,10 +197,44 @@ select_pick_kernel(int pass, long long k, RowState* __restrict__ state,
   } else {
     st = state[row];
   }
-  pick_digit(hist + (row * K::kPasses + pass) * 256, st.need, threadIdx.x, &res[0], &res[1]);
-  __syncwarp();
+  const int shift = 24 - 8 * pass;
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const long long begin = static_cast<long long>(blockIdx.x) * kChunk;
+  long long end = begin + kChunk;
+  if (end > k0) end = k0;
+  const auto* vrow = cand_vals + row * cand_row_stride;
+  // all loads of the chunk are issued before the first histogram update, so the
+  // warp-synchronous updates do not serialise the memory latency
+  typename ElemTraits<T>::Bits raw[kLargeItems];
+#pragma unroll
+  for (int u = 0; u < kLargeItems; ++u) {
+    const long long i = begin + u * kLargeThreads + threadIdx.x;
+    raw[u] = i < end ? vrow[i] : typename ElemTraits<T>::Bits(0);
+  }
+#pragma unroll
+  for (int u = 0; u < kLargeItems; ++u) {
+    const long long i = begin + u * kLargeThreads + threadIdx.x;
+    const uint32_t key = K::key(raw[u]);
+    hist_add_warp(sh, (key >> shift) & 255u, i < end && (key & st.mask) == st.prefix, threadIdx.x & 31);
+  }
+  __syncthreads();
+  uint32_t* gh = hist + (row * K::kPasses + pass) * 256;
+  for (int i = threadIdx.x; i < 256; i += blockDim.x)
+    if (sh[i]) atomicAdd(&gh[i], sh[i]);
+  // publish, then take a ticket; the holder of the last ticket sees every add
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0)
+    last = atomicAdd(&tickets[row * (K::kPasses + 1) + pass], 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = __ldcg(&gh[i]);
+  __syncthreads();
+  if (threadIdx.x < 32) pick_digit(sh, st.need, threadIdx.x, &res[0], &res[1]);
+  __syncthreads();
   if (threadIdx.x == 0) {
-    const int shift = 24 - 8 * pass;
     st.prefix |= res[0] << shift;
     st.mask |= 255u << shift;
     st.need = res[1];
@@ -235,7 +246,7 @@ template <typename T>
 __global__ void __launch_bounds__(kLargeThreads)
 select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
                     long long cand_row_stride, const RowState* __restrict__ state,
-                    uint2* __restrict__ counts /* [rows][chunks] */) {
+                    uint2* __restrict__ counts /* [rows][chunks] */, uint32_t* __restrict__ tickets) {
   using K = KeyOf<T>;
   __shared__ uint32_t s_gt, s_eq;
   if (threadIdx.x == 0) {
@@ -250,10 +261,14 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
   if (end > k0) end = k0;
   const auto* vrow = cand_vals + row * cand_row_stride;
   uint32_t gt = 0, eq = 0;
-  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
-    const uint32_t key = K::key(vrow[i]);
-    gt += key > thr;
-    eq += key == thr;
+#pragma unroll
+  for (int u = 0; u < kLargeItems; ++u) {
+    const long long i = begin + u * kLargeThreads + threadIdx.x;
+    if (i < end) {
+      const uint32_t key = K::key(vrow[i]);
+      gt += key > thr;
+      eq += key == thr;
+    }
   }
 #pragma unroll
   for (int off = 16; off >= 1; off >>= 1) {
@@ -266,30 +281,36 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
   }
   __syncthreads();
   if (threadIdx.x == 0) counts[row * gridDim.x + blockIdx.x] = make_uint2(s_gt, s_eq);
-}
-
-// One warp per row: exclusive scan of the per-chunk (greater, equal) counts.
-__global__ void __launch_bounds__(32) select_scan_kernel(uint2* __restrict__ counts, int chunks) {
-  const long long row = blockIdx.x;
+  // The block that finishes last for the row turns the per-chunk counts into
+  // exclusive prefixes (one warp).
+  __shared__ bool last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0)
+    last = atomicAdd(&tickets[row * (K::kPasses + 1) + K::kPasses], 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!last || threadIdx.x >= 32) return;
+  __threadfence();
+  const int chunks = static_cast<int>(gridDim.x);
   uint2* c = counts + row * chunks;
   const int lane = threadIdx.x;
   uint32_t carry_gt = 0, carry_eq = 0;
   for (int base = 0; base < chunks; base += 32) {
     const int i = base + lane;
-    const uint2 v = i < chunks ? c[i] : make_uint2(0, 0);
-    uint32_t gt = v.x, eq = v.y;
+    const uint2 v = i < chunks ? __ldcg(&c[i]) : make_uint2(0, 0);
+    uint32_t a_gt = v.x, a_eq = v.y;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
-      const uint32_t a = __shfl_up_sync(0xffffffffu, gt, off);
-      const uint32_t b = __shfl_up_sync(0xffffffffu, eq, off);
+      const uint32_t a = __shfl_up_sync(0xffffffffu, a_gt, off);
+      const uint32_t b = __shfl_up_sync(0xffffffffu, a_eq, off);
       if (lane >= off) {
-        gt += a;
-        eq += b;
+        a_gt += a;
+        a_eq += b;
       }
     }
-    if (i < chunks) c[i] = make_uint2(carry_gt + gt - v.x, carry_eq + eq - v.y);
-    carry_gt += __shfl_sync(0xffffffffu, gt, 31);
-    carry_eq += __shfl_sync(0xffffffffu, eq, 31);
+    if (i < chunks) c[i] = make_uint2(carry_gt + a_gt - v.x, carry_eq + a_eq - v.y);
+    carry_gt += __shfl_sync(0xffffffffu, a_gt, 31);
+    carry_eq += __shfl_sync(0xffffffffu, a_eq, 31);
   }
 }
 
@@ -315,12 +336,19 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   const long long* irow = cand_idx + row * cand_row_stride;
   auto* ovrow = out_vals + row * out_row_stride;
   long long* oirow = out_idx + row * out_row_stride;
-  for (long long base = begin; base < end; base += blockDim.x) {
-    const long long i = base + threadIdx.x;
+  typename ElemTraits<T>::Bits raws[kLargeItems];
+  long long idxs[kLargeItems];
+#pragma unroll
+  for (int u = 0; u < kLargeItems; ++u) {
+    const long long i = begin + u * kLargeThreads + threadIdx.x;
+    raws[u] = i < end ? vrow[i] : typename ElemTraits<T>::Bits(0);
+    idxs[u] = i < end ? irow[i] : 0;
+  }
+#pragma unroll
+  for (int u = 0; u < kLargeItems; ++u) {
+    const long long i = begin + u * kLargeThreads + threadIdx.x;
     const bool in = i < end;
-    typename ElemTraits<T>::Bits raw = 0;
-    if (in) raw = vrow[i];
-    const uint32_t key = K::key(raw);
+    const uint32_t key = K::key(raws[u]);
     const bool gt = in && key > thr;
     const bool eq = in && key == thr;
     uint32_t r_gt, r_eq, t_gt, t_eq;
@@ -329,8 +357,8 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
     if (gt) pos = static_cast<long long>(gt_base) + r_gt;
     else if (eq && eq_base + r_eq < need) pos = n_gt + eq_base + r_eq;
     if (pos >= 0) {
-      ovrow[pos] = raw;
-      oirow[pos] = irow[i];
+      ovrow[pos] = raws[u];
+      oirow[pos] = idxs[u];
     }
     gt_base += t_gt;
     eq_base += t_eq;
@@ -344,7 +372,8 @@ template <typename T>
 size_t workspace_typed(long long rows, long long k0) {
   if (k0 <= kSmallMaxK0) return 0;
   const size_t state = align256(sizeof(RowState) * rows);
-  const size_t hist = align256(sizeof(uint32_t) * 256 * KeyOf<T>::kPasses * rows);
+  // digit histograms followed by the ticket counters: the part zeroed per call
+  const size_t hist = align256(sizeof(uint32_t) * (256 * KeyOf<T>::kPasses + KeyOf<T>::kPasses + 1) * rows);
   const size_t counts = align256(sizeof(uint2) * chunks_of(k0) * rows);
   return state + hist + counts;
 }
@@ -394,25 +423,23 @@ int select_typed(const SelectLaunch& a) {
   RowState* state = reinterpret_cast<RowState*>(ws);
   ws += align256(sizeof(RowState) * a.rows);
   uint32_t* hist = reinterpret_cast<uint32_t*>(ws);
-  const size_t hist_bytes = sizeof(uint32_t) * 256 * K::kPasses * a.rows;
-  ws += align256(hist_bytes);
+  const size_t hist_words = static_cast<size_t>(256) * K::kPasses * a.rows;
+  uint32_t* tickets = hist + hist_words;
+  const size_t zero_bytes = sizeof(uint32_t) * (hist_words + static_cast<size_t>(K::kPasses + 1) * a.rows);
+  ws += align256(zero_bytes);
   uint2* counts = reinterpret_cast<uint2*>(ws);
 
-  if (cudaMemsetAsync(hist, 0, hist_bytes, a.stream) != cudaSuccess) return ATK_ERR_CUDA;
+  if (cudaMemsetAsync(hist, 0, zero_bytes, a.stream) != cudaSuccess) return ATK_ERR_CUDA;
   const dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(a.rows));
-  for (int pass = 0; pass < K::kPasses; ++pass) {
-    select_hist_kernel<T><<<grid, kLargeThreads, 0, a.stream>>>(cv, a.k0, a.cand_row_stride, pass,
-                                                                 state, hist);
-    select_pick_kernel<T><<<static_cast<unsigned>(a.rows), 32, 0, a.stream>>>(pass, a.k, state, hist);
-  }
+  for (int pass = 0; pass < K::kPasses; ++pass)
+    select_hist_kernel<T><<<grid, kLargeThreads, 0, a.stream>>>(cv, a.k0, a.cand_row_stride, pass, a.k,
+                                                                 state, hist, tickets);
   select_count_kernel<T><<<grid, kLargeThreads, 0, a.stream>>>(cv, a.k0, a.cand_row_stride, state,
-                                                                counts);
-  select_scan_kernel<<<static_cast<unsigned>(a.rows), 32, 0, a.stream>>>(counts,
-                                                                          static_cast<int>(chunks));
+                                                                counts, tickets);
   select_write_kernel<T><<<grid, kLargeThreads, 0, a.stream>>>(cv, a.cand_idx, a.k0,
                                                                 a.cand_row_stride, a.k, state, counts,
                                                                 ov, a.out_idx, a.out_row_stride);
-  note_launch(2 * K::kPasses + 3);
+  note_launch(K::kPasses + 2);
   return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
 }
 

@@ -35,9 +35,13 @@ def stage1_slab(slab: torch.Tensor, total_buckets: int, col_offset: int, j: int)
     stripes, cols = slab.shape
     vals = torch.empty((cols * j,), device=slab.device, dtype=slab.dtype)
     idx = torch.empty((cols * j,), device=slab.device, dtype=torch.int64)
-    rc = _native.lib().atk_stage1_slab(slab.data_ptr(), _native.dtype_code(slab.dtype), stripes, cols,
-                                       total_buckets, col_offset, j, vals.data_ptr(), idx.data_ptr(),
-                                       _stream(slab))
+    lib = _native.lib()
+    code = _native.dtype_code(slab.dtype)
+    ws_bytes = lib.atk_stage1_slab_workspace_bytes(code, stripes, cols, j)
+    ws = torch.empty(max(ws_bytes, 1), device=slab.device, dtype=torch.uint8)
+    rc = lib.atk_stage1_slab(slab.data_ptr(), code, stripes, cols, total_buckets, col_offset, j,
+                             vals.data_ptr(), idx.data_ptr(), ws.data_ptr() if ws_bytes else None, ws_bytes,
+                             _stream(slab))
     _native.check(rc)
     return vals, idx
 
