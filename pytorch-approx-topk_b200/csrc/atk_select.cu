@@ -20,10 +20,14 @@
 namespace atk {
 namespace {
 
-constexpr int kSmallMaxK0 = 32768;   // 1024 threads x 32 candidates in registers
+constexpr int kSmallMaxK0 = 16384;   // 512 threads x 32 candidates in registers
 constexpr int kChunk = 2048;         // candidates per block on the large path
 constexpr int kLargeItems = kChunk / 256;  // per thread, all loaded before any is used
 constexpr int kLargeThreads = 256;
+#ifndef ATK_SELECT_ROW_THREADS
+#define ATK_SELECT_ROW_THREADS 512
+#endif
+constexpr int kSelectRowThreads = ATK_SELECT_ROW_THREADS;  // preferred block width of the one-block-per-row select
 
 template <typename T> struct KeyOf;
 template <> struct KeyOf<float> {
@@ -49,8 +53,8 @@ template <> struct KeyOf<__nv_bfloat16> {
 // [t*ITEMS, (t+1)*ITEMS): keys stay in registers through the radix passes, and
 // because slots are blocked per thread one block-wide scan of the per-thread
 // (greater, equal) counts gives every winner its output position in slot order.
-template <typename T, int ITEMS>
-__global__ void __launch_bounds__(1024)
+template <typename T, int ITEMS, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                   const long long* __restrict__ cand_idx, int k0, long long cand_row_stride, int k,
                   typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
@@ -151,19 +155,32 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   const uint32_t n_gt = static_cast<uint32_t>(k) - need;
   Bits* ovrow = out_vals + row * out_row_stride;
   long long* oirow = out_idx + row * out_row_stride;
+  // output position of every item first (no memory traffic), then the gathers
+  // of the winners' positions as independent loads, then the stores
+  int pos[ITEMS];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    if (slot0 + i >= k0) break;
-    long long pos = -1;
-    if (key[i] > prefix) {
-      pos = gt_rank++;
-    } else if (key[i] == prefix) {
-      if (eq_rank < need) pos = static_cast<long long>(n_gt) + eq_rank;
-      ++eq_rank;
+    pos[i] = -1;
+    if (slot0 + i < k0) {
+      if (key[i] > prefix) {
+        pos[i] = static_cast<int>(gt_rank++);
+      } else if (key[i] == prefix) {
+        if (eq_rank < need) pos[i] = static_cast<int>(n_gt + eq_rank);
+        ++eq_rank;
+      }
     }
-    if (pos >= 0) {
-      ovrow[pos] = raw[i];
-      oirow[pos] = kPrefetchIdx ? pidx[kPrefetchIdx ? i : 0] : irow[slot0 + i];
+  }
+  long long widx[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    widx[i] = 0;
+    if (pos[i] >= 0) widx[i] = kPrefetchIdx ? pidx[kPrefetchIdx ? i : 0] : irow[slot0 + i];
+  }
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    if (pos[i] >= 0) {
+      ovrow[pos[i]] = raw[i];
+      oirow[pos[i]] = widx[i];
     }
   }
 }
@@ -396,21 +413,18 @@ int select_typed(const SelectLaunch& a) {
       int t = (k0 + items - 1) / items;
       return ((t + 31) / 32) * 32;
     };
-    // 16 bytes of values per thread when that keeps the block within 1024
-    // threads, more items per thread for longer rows.
+    // At least 16 bytes of values per thread; more items per thread until the
+    // block is at most kSelectRowThreads wide (512 measured better than 256 on
+    // 4096-candidate rows, and equal to 1024), 32 items at most.
     constexpr int kBase = 16 / static_cast<int>(sizeof(Bits));
-    if (threads_for(kBase) <= 1024)
-      select_row_kernel<T, kBase><<<rows, threads_for(kBase), 0, a.stream>>>(
-          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
-    else if (threads_for(2 * kBase) <= 1024)
-      select_row_kernel<T, 2 * kBase><<<rows, threads_for(2 * kBase), 0, a.stream>>>(
-          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
-    else if (threads_for(4 * kBase) <= 1024)
-      select_row_kernel<T, 4 * kBase><<<rows, threads_for(4 * kBase), 0, a.stream>>>(
-          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
-    else
-      select_row_kernel<T, 32><<<rows, threads_for(32), 0, a.stream>>>(
-          cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);
+#define ATK_LAUNCH_SELECT_ROW(ITEMS, MAXT)                                                         \
+    select_row_kernel<T, ITEMS, MAXT><<<rows, threads_for(ITEMS), 0, a.stream>>>(                    \
+        cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok)
+    if (threads_for(kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(kBase, kSelectRowThreads);
+    else if (threads_for(2 * kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(2 * kBase, kSelectRowThreads);
+    else if (4 * kBase <= 32 && threads_for(4 * kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(4 * kBase, kSelectRowThreads);
+    else ATK_LAUNCH_SELECT_ROW(32, 512);
+#undef ATK_LAUNCH_SELECT_ROW
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
   }

@@ -37,6 +37,7 @@ struct SweepParams {
   int cw;                    // blockDim.x: threads across columns
   int s;                     // blockDim.y: stripe splits inside the block (power of two)
   int vec_out;               // 16-byte stores are legal for both outputs
+  int vec_part;              // ... and for the scratch planes of the stripe split
   // Cross-block stripe split: z blocks share one (row, tile); block z walks
   // stripes [z*z_chunk, (z+1)*z_chunk) and writes its partial candidates to
   // plane z of the scratch buffers (dense [z][rows][k0]); a merge kernel
@@ -198,7 +199,7 @@ sweep_kernel(const SweepParams p) {
   Bits* vdst = static_cast<Bits*>(p.z > 1 ? p.part_vals : p.out_vals) + out_base;
   long long* idst = (p.z > 1 ? p.part_idx : p.out_idx) + out_base;
   constexpr int kValBytes = V * J * static_cast<int>(sizeof(Bits));
-  if (kValBytes % 16 == 0 && p.vec_out && p.z == 1) {
+  if (kValBytes % 16 == 0 && (p.z > 1 ? p.vec_part : p.vec_out)) {
     const uint4* src = reinterpret_cast<const uint4*>(ov);
 #pragma unroll
     for (int i = 0; i < kValBytes / 16; ++i) st_out_16(reinterpret_cast<uint4*>(vdst) + i, src[i]);
@@ -214,11 +215,12 @@ sweep_kernel(const SweepParams p) {
   }
 }
 
-// Combine the z partial candidate planes written by a stripe-split sweep: one
-// warp per (row, bucket); lane l ranks the entries of planes l, l+32, ... by
-// value, then by position (later wins; earlier with FIRST), the 32 lanes merge
-// by xor-shuffles, and lane 0 writes the best J in ascending order — exactly
-// what one block walking the whole column would have produced.
+// Combine the z partial candidate planes written by a stripe-split sweep: a
+// group of g lanes per (row, bucket) (g = 1 for a few planes, up to a whole
+// warp for many); lane l ranks the entries of planes l, l+g, ... by value, then
+// by position (later wins; earlier with FIRST), the lanes merge by
+// xor-shuffles, and lane 0 writes the best J in ascending order — exactly what
+// one block walking the whole column would have produced.
 template <typename T, int J, bool FIRST>
 struct PlaneEntryQueue {
   using Bits = typename ElemTraits<T>::Bits;
@@ -254,13 +256,14 @@ struct PlaneEntryQueue {
 template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(256)
 sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_vals,
-                          const long long* __restrict__ part_idx, int z, long long rows, long long b,
+                          const long long* __restrict__ part_idx, int z, int g /* lanes per bucket */,
+                          long long rows, long long b,
                           typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
                           long long out_row_stride) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
-  const int lane = threadIdx.x & 31;
-  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x % g;            // g is a power of two <= 32, groups never straddle warps
+  const long long unit = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / g;
   const bool valid = unit < rows * b;          // whole warps stay for the shuffles
   const long long row = valid ? unit / b : 0;
   const long long c = valid ? unit - row * b : 0;
@@ -268,7 +271,7 @@ sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_
   PlaneEntryQueue<T, J, FIRST> q;
   q.init();
   if (valid) {
-    for (int zz = lane; zz < z; zz += 32) {
+    for (int zz = lane; zz < z; zz += g) {
       const long long base = (static_cast<long long>(zz) * rows + row) * k0 + c * J;
 #pragma unroll
       for (int j = 0; j < J; ++j) {
@@ -277,7 +280,7 @@ sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_
       }
     }
   }
-  for (int off = 16; off >= 1; off >>= 1) {
+  for (int off = g >> 1; off >= 1; off >>= 1) {
     float ov[J];
     long long oi[J];
     uint32_t ob[J];

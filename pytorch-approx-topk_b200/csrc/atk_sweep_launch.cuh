@@ -55,11 +55,13 @@ int launch_stage1(const SweepLaunch& a) {
   p.z_chunk = pl.z_chunk;
   p.part_vals = nullptr;
   p.part_idx = nullptr;
+  p.vec_part = 0;
   if (pl.Z > 1) {
     // dense planes [z][rows][k0]: all value planes first, then all position planes
     unsigned char* ws = static_cast<unsigned char*>(a.workspace);
     p.part_vals = ws;
     p.part_idx = reinterpret_cast<long long*>(ws + align256(static_cast<size_t>(pl.Z) * a.rows * k0 * sizeof(Bits)));
+    p.vec_part = (reinterpret_cast<uintptr_t>(ws) % 16 == 0) && ((k0 * sizeof(Bits)) % 16 == 0) && ((k0 * 8) % 16 == 0);
   }
   if (a.rows * pl.tiles * pl.Z >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
 
@@ -75,10 +77,12 @@ int launch_stage1(const SweepLaunch& a) {
   note_launch();
   if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   if (pl.Z > 1) {
-    const long long blocks = (a.rows * a.b + 7) / 8;   // one warp per (row, bucket), 8 warps per block
+    int g = 1;                                   // lanes per bucket: about 8 planes per lane
+    while (g < 32 && g * 8 < pl.Z) g *= 2;
+    const long long blocks = (a.rows * a.b * g + 255) / 256;
     if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     sweep_merge_planes_kernel<T, J, Q::kFirst><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
-        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, a.rows, a.b, static_cast<Bits*>(a.out_vals),
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, static_cast<Bits*>(a.out_vals),
         a.out_idx, a.out_row_stride);
     note_launch();
     if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;

@@ -9,7 +9,7 @@ carries 1 MiB of scratch inside its own image and ``atk_select_static`` uses
 that instead of a workspace argument.
 
 The test calls the new entry point through the C ABI, twice in a row on
-problems that really use the scratch (more than 32768 candidates per row) and
+problems that really use the scratch (more than 16384 candidates per row) and
 of different sizes, so the second call runs over whatever the first one left
 in the shared array, and requires bit-identical results to ``atk_select``.
 It also checks that a problem beyond the 1 MiB limit is refused with a clear
