@@ -54,6 +54,11 @@ struct SweepParams {
 #define ATK_SWEEP_THREADS 128
 #endif
 constexpr int kSweepMaxThreads = ATK_SWEEP_THREADS;
+// Minimum resident blocks the compiler must allow for.  1 leaves it free to keep
+// all loads of an unrolled batch in flight (more registers, fewer blocks).
+#ifndef ATK_SWEEP_MINBLOCKS
+#define ATK_SWEEP_MINBLOCKS 1
+#endif
 
 template <int V, int WORDS> struct SweepUnroll {
   // independent 16-byte loads kept in flight per thread; fewer when the
@@ -150,7 +155,7 @@ __device__ __forceinline__ void sweep_merge(Q (&q)[V], uint32_t* smem, int cw, i
 // Stage 1 only: every block handles one tile of columns of one row and writes
 // the J candidates of each bucket (slot = bucket*J + q, ascending).
 template <typename T, typename Q, int J, int V, bool SKIP, bool SIMD>
-__global__ void __launch_bounds__(kSweepMaxThreads)
+__global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
 sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
