@@ -127,6 +127,25 @@ def test_operator_single_row_small_k_uses_the_split_and_matches_oracle():
     assert torch.equal(bits(v), bits(ov)) and torch.equal(i.cpu(), oi)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("j", [1, 2, 4])
+def test_stage1_contiguous_bucket_lengths(dtype, j):
+    # contiguous buckets from a few elements (shared-memory tile kernel) over
+    # hundreds (lane groups, vector loads) to hundreds of thousands (block per
+    # bucket), with row bases that are not 16-byte aligned
+    for seed, (rows, n, k0) in enumerate([(3, 4096, 1024), (2, 4099, 400), (5, 9000, 96), (4, 128256, 256),
+                                          (1, 1 << 20, 64), (2, 300000, 8), (1, (1 << 20) + 13, 28),
+                                          (2, 50001, 12500)]):
+        k0 = (k0 // j) * j
+        for dist in ("randn", "ties"):
+            base = make(rows, n + 3, dtype, 700 + seed, dist)
+            x = base[:, 3:]                      # element-aligned only
+            v, i = api.stage1(x, k0, j, False)
+            ov, oi = oracle.stage1(x.cpu().contiguous(), k0, j, False)
+            assert torch.equal(bits(v), bits(ov)), (rows, n, k0, dist)
+            assert torch.equal(i.cpu(), oi), (rows, n, k0, dist)
+
+
 def test_stage1_row_stride_and_unaligned_base():
     base = make(9, 1100, torch.float32, 3)
     view = base[:, 3:1027]            # base pointer only 4-byte aligned, row stride 1100
