@@ -357,6 +357,13 @@ inline SweepPlan plan_sweep(long long rows, long long b, long long l_full, int V
     if (by_work < pl.S) pl.S = by_work;
     if (by_need < pl.S) pl.S = by_need;
     if (pl.S < 1) pl.S = 1;
+    // A full-width block leaves no room for splits: trade columns for splits
+    // (narrower tiles, more of them) while at least a warp of columns remains.
+    while (pl.S < by_need && pl.S < by_work && pl.cw >= 64 && pl.cw % 2 == 0) {
+      pl.cw /= 2;
+      pl.S *= 2;
+    }
+    pl.tiles = (col_threads + pl.cw - 1) / pl.cw;
   }
   have_threads *= pl.S;
   // Over blocks: only when a thread would otherwise walk a long column (a
