@@ -230,3 +230,35 @@ def test_non_contiguous_inputs():
     a = topk(strided, 30, -1, j=2)
     b = topk(strided.contiguous(), 30, -1, j=2)
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_runs_on_the_current_side_stream():
+    # the kernels must be queued on torch's current stream, not the default one
+    xs = torch.randn(64, 1 << 16, **rng_kwargs(8))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        big = torch.randn(1 << 26, device="cuda")       # keeps the side stream busy first
+        ys = xs * 2.0                                    # produced on the side stream
+        v, i = topk(ys, 128, -1, j=2, k_mult=2)
+    side.synchronize()
+    ev, ei = topk(xs * 2.0, 128, -1, j=2, k_mult=2)
+    assert torch.equal(v, ev) and torch.equal(i, ei)
+    del big
+
+
+def test_host_buffer_python_api():
+    from approx_topk.host_buffers import topk_host
+
+    x = torch.randn(19, 4096, **rng_kwargs(9)).bfloat16()
+    v, i = topk(x, 64, -1, j=4, k_mult=2)
+    hv, hi = topk_host(x.cpu().pin_memory(), 64, j=4, k_mult=2)
+    assert not hv.is_cuda and hv.is_pinned()
+    assert torch.equal(hv, v.cpu()) and torch.equal(hi, i.cpu())
+    out = (torch.empty(19, 64, dtype=torch.bfloat16), torch.empty(19, 64, dtype=torch.int64))
+    rv, ri = topk_host(x.cpu(), 64, j=4, k_mult=2, out=out, chunk_rows=4)
+    assert rv is out[0] and torch.equal(rv, v.cpu()) and torch.equal(ri, i.cpu())
+    with pytest.raises(RuntimeError, match="CPU tensor"):
+        topk_host(x, 64)
+    with pytest.raises(ValueError):
+        topk_host(x.cpu(), 64, out=(torch.empty(3, 3), torch.empty(3, 3, dtype=torch.int64)))
