@@ -93,3 +93,38 @@ def test_long_row_single_process_matches_oracle():
     v, i = atd.topk_long_row(slab, k, j, k_mult, stage1=oracle_stage1_slab, select=oracle_select)
     ev, ei = oracle.topk(row.reshape(1, -1), k, j=j, k_mult=k_mult)
     assert torch.equal(i.sort().values, ei.reshape(-1).sort().values)
+
+
+def _failing_worker(rank, world, port, out):
+    """Rank 1 fails on the host before the exchange; rank 0 must get an error from
+    the collective (short process-group timeout), not hang."""
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    row = torch.randn(1 << 12, generator=torch.Generator().manual_seed(1))
+    slab = atd.slab_of_row(row, 64, rank, world)
+    if rank == 1:
+        os._exit(17)                      # the rank disappears between steps, nothing in flight
+    try:
+        atd.topk_long_row(slab, 64, 1, 1, stage1=oracle_stage1_slab, select=oracle_select)
+        outcome = "no error"
+    except Exception as exc:              # noqa: BLE001 - any surfaced failure is the point
+        outcome = f"error: {type(exc).__name__}"
+    with open(os.path.join(out, "rank0.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)
+
+
+def test_peer_failure_surfaces_as_an_error_not_a_hang(tmp_path):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    assert all(not p.is_alive() for p in procs), "a rank hung after its peer failed"
+    assert procs[1].exitcode == 17
+    assert (tmp_path / "rank0.txt").read_text().startswith("error:")
