@@ -27,8 +27,15 @@
 extern "C" {
 #endif
 
-/* Element types of the input / value output. */
-enum { ATK_F32 = 0, ATK_F16 = 1, ATK_BF16 = 2 };
+/* Element types of the input / value output: the nine the reference's native
+ * operator dispatches over (AT_DISPATCH_ALL_TYPES_AND2(Half, BFloat16),
+ * approx_topk/priority_queue_approx_topk.cu:449-453).  The three float types
+ * of 32 bits or fewer are the tuned ones; the others run the same kernels with
+ * an exact integer / double compare. */
+enum {
+  ATK_F32 = 0, ATK_F16 = 1, ATK_BF16 = 2,
+  ATK_F64 = 3, ATK_I32 = 4, ATK_I64 = 5, ATK_I16 = 6, ATK_I8 = 7, ATK_U8 = 8
+};
 
 /* Status codes.  The Python host maps them to the exception types the
  * reference raises for the same condition. */

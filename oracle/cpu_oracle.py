@@ -1,9 +1,11 @@
 """ctypes front end of ``atk_oracle.c`` (test infrastructure only).
 
-Inputs are torch CPU tensors (fp32 / bf16 / fp16); 16-bit inputs are widened to
-float exactly, pushed through the scalar C restatement of the reference's CUDA
-semantics (approx_topk/priority_queue_approx_topk.cu:25-147) and the selected
-values narrowed back, which is an exact round trip.
+Inputs are torch CPU tensors of any element type of the reference's dispatch
+(approx_topk/priority_queue_approx_topk.cu:449-453).  Each is widened exactly
+to a carrier type -- float for fp32 / bf16 / fp16, double for float64, int64
+for the integer types -- pushed through the scalar C restatement of the
+reference's CUDA semantics (.cu:25-147) for that carrier, and the selected
+values are narrowed back, which is an exact round trip.
 """
 
 from __future__ import annotations
@@ -18,15 +20,27 @@ HERE = Path(__file__).resolve().parent
 _LIB_PATH = HERE / "libatk_oracle.so"
 _lib = None
 
-_f32p = ctypes.POINTER(ctypes.c_float)
 _i64p = ctypes.POINTER(ctypes.c_int64)
 _i64 = ctypes.c_int64
+
+# carrier name -> (symbol suffix, ctypes scalar, torch dtype)
+_CARRIERS = {
+    "f32": ("", ctypes.c_float, torch.float32),
+    "f64": ("_f64", ctypes.c_double, torch.float64),
+    "i64": ("_i64", ctypes.c_int64, torch.int64),
+}
+
+
+def carrier_of(dtype: torch.dtype) -> str:
+    if dtype == torch.float64:
+        return "f64"
+    return "f32" if dtype.is_floating_point else "i64"
 
 
 def build(force: bool = False) -> Path:
     """Compile the C oracle with the Makefile next to it."""
-    src = HERE / "atk_oracle.c"
-    if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < src.stat().st_mtime:
+    newest = max((HERE / name).stat().st_mtime for name in ("atk_oracle.c", "atk_oracle_body.inc"))
+    if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < newest:
         subprocess.run(["make", "-C", str(HERE), "-B", "libatk_oracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
     return _LIB_PATH
@@ -37,25 +51,35 @@ def lib() -> ctypes.CDLL:
     if _lib is None:
         build()
         L = ctypes.CDLL(str(_LIB_PATH))
-        L.atk_oracle_stage1.argtypes = [_f32p, _i64, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int,
-                                        ctypes.c_float, _f32p, _i64p]
-        L.atk_oracle_stage1.restype = ctypes.c_int
-        L.atk_oracle_select.argtypes = [_f32p, _i64p, _i64, _i64, _i64, _f32p, _i64p]
-        L.atk_oracle_select.restype = ctypes.c_int
-        L.atk_oracle_topk.argtypes = [_f32p, _i64, _i64, _i64, _i64, ctypes.c_int, _i64, ctypes.c_int,
-                                      ctypes.c_float, _f32p, _i64p]
-        L.atk_oracle_topk.restype = ctypes.c_int
-        L.atk_oracle_bucketed_argmax.argtypes = [_f32p, _i64, _i64, _i64, _i64, ctypes.c_int,
-                                                 ctypes.c_float, _f32p, _i64p]
-        L.atk_oracle_bucketed_argmax.restype = ctypes.c_int
-        L.atk_oracle_recall.argtypes = [_f32p, _i64, _i64, _i64, _f32p, _i64]
-        L.atk_oracle_recall.restype = ctypes.c_double
+        for suffix, scalar, _ in _CARRIERS.values():
+            ptr = ctypes.POINTER(scalar)
+            f = getattr(L, "atk_oracle_stage1" + suffix)
+            f.argtypes = [ptr, _i64, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int, scalar, ptr, _i64p]
+            f.restype = ctypes.c_int
+            f = getattr(L, "atk_oracle_select" + suffix)
+            f.argtypes = [ptr, _i64p, _i64, _i64, _i64, ptr, _i64p]
+            f.restype = ctypes.c_int
+            f = getattr(L, "atk_oracle_topk" + suffix)
+            f.argtypes = [ptr, _i64, _i64, _i64, _i64, ctypes.c_int, _i64, ctypes.c_int, scalar, ptr, _i64p]
+            f.restype = ctypes.c_int
+            f = getattr(L, "atk_oracle_bucketed_argmax" + suffix)
+            f.argtypes = [ptr, _i64, _i64, _i64, _i64, ctypes.c_int, scalar, ptr, _i64p]
+            f.restype = ctypes.c_int
+            f = getattr(L, "atk_oracle_recall" + suffix)
+            f.argtypes = [ptr, _i64, _i64, _i64, ptr, _i64]
+            f.restype = ctypes.c_double
         _lib = L
     return _lib
 
 
+def _fn(name: str, dtype: torch.dtype):
+    return getattr(lib(), name + _CARRIERS[carrier_of(dtype)][0])
+
+
 def _fp(t: torch.Tensor):
-    return ctypes.cast(t.data_ptr(), _f32p)
+    """Pointer to a carrier-typed tensor's data."""
+    scalar = {torch.float32: ctypes.c_float, torch.float64: ctypes.c_double, torch.int64: ctypes.c_int64}[t.dtype]
+    return ctypes.cast(t.data_ptr(), ctypes.POINTER(scalar))
 
 
 def _ip(t: torch.Tensor):
@@ -63,20 +87,30 @@ def _ip(t: torch.Tensor):
 
 
 def _rows(x: torch.Tensor) -> tuple[torch.Tensor, tuple[int, ...]]:
-    """Flatten to (rows, n) float32 contiguous on CPU; keep the batch shape."""
+    """Flatten to (rows, n) in the carrier type, contiguous on CPU; keep the batch shape."""
     if x.ndim == 0:
         x = x.reshape(1)
     batch = tuple(x.shape[:-1])
-    x2 = x.detach().to("cpu").reshape(-1, x.shape[-1]).to(torch.float32).contiguous()
+    carrier = _CARRIERS[carrier_of(x.dtype)][2]
+    x2 = x.detach().to("cpu").reshape(-1, x.shape[-1]).to(carrier).contiguous()
     return x2, batch
 
 
 NEG_INF = float("-inf")
 
 
-def lowest(dtype: torch.dtype) -> float:
+def lowest(dtype: torch.dtype):
     """The reference's queue sentinel, numeric_limits<T>::lowest() (.cu:95-101)."""
-    return torch.finfo(dtype).min
+    return torch.finfo(dtype).min if dtype.is_floating_point else torch.iinfo(dtype).min
+
+
+def _sentinel(dtype: torch.dtype, sentinel):
+    """Initial queue value in the carrier type: -inf for the float types unless
+    told otherwise; the type's lowest value for the integer types (where it is
+    what the reference uses too)."""
+    if dtype.is_floating_point:
+        return float(sentinel)
+    return int(lowest(dtype))
 
 
 def stage1(x: torch.Tensor, k0: int, j: int, interleaved: bool = True,
@@ -84,10 +118,10 @@ def stage1(x: torch.Tensor, k0: int, j: int, interleaved: bool = True,
     """Per-bucket top-j of the last dim; slot layout bucket*j + q, q ascending."""
     x2, batch = _rows(x)
     rows, n = x2.shape
-    vals = torch.empty((rows, k0), dtype=torch.float32)
+    vals = torch.empty((rows, k0), dtype=x2.dtype)
     idx = torch.empty((rows, k0), dtype=torch.int64)
-    rc = lib().atk_oracle_stage1(_fp(x2), rows, n, n, k0, j, int(interleaved), sentinel,
-                                 _fp(vals), _ip(idx))
+    rc = _fn("atk_oracle_stage1", x.dtype)(_fp(x2), rows, n, n, k0, j, int(interleaved),
+                                           _sentinel(x.dtype, sentinel), _fp(vals), _ip(idx))
     if rc != 0:
         raise ValueError(f"atk_oracle_stage1 rejected the arguments (rc={rc})")
     return vals.to(x.dtype).reshape(*batch, k0), idx.reshape(*batch, k0)
@@ -98,9 +132,9 @@ def select(cand_vals: torch.Tensor, cand_idx: torch.Tensor, k: int) -> tuple[tor
     v2, batch = _rows(cand_vals)
     i2 = cand_idx.detach().to("cpu").reshape(-1, cand_idx.shape[-1]).contiguous()
     rows, k0 = v2.shape
-    vals = torch.empty((rows, k), dtype=torch.float32)
+    vals = torch.empty((rows, k), dtype=v2.dtype)
     idx = torch.empty((rows, k), dtype=torch.int64)
-    rc = lib().atk_oracle_select(_fp(v2), _ip(i2), rows, k0, k, _fp(vals), _ip(idx))
+    rc = _fn("atk_oracle_select", cand_vals.dtype)(_fp(v2), _ip(i2), rows, k0, k, _fp(vals), _ip(idx))
     if rc != 0:
         raise ValueError(f"atk_oracle_select rejected the arguments (rc={rc})")
     return vals.to(cand_vals.dtype).reshape(*batch, k), idx.reshape(*batch, k)
@@ -111,10 +145,10 @@ def topk(x: torch.Tensor, k: int, j: int = 1, k_mult: int = 1, interleaved: bool
     """approx_topk.topk(x, k, dim=-1, j, k_mult, interleaved) on the CPU."""
     x2, batch = _rows(x)
     rows, n = x2.shape
-    vals = torch.empty((rows, k), dtype=torch.float32)
+    vals = torch.empty((rows, k), dtype=x2.dtype)
     idx = torch.empty((rows, k), dtype=torch.int64)
-    rc = lib().atk_oracle_topk(_fp(x2), rows, n, n, k, j, k_mult, int(interleaved), sentinel,
-                               _fp(vals), _ip(idx))
+    rc = _fn("atk_oracle_topk", x.dtype)(_fp(x2), rows, n, n, k, j, k_mult, int(interleaved),
+                                         _sentinel(x.dtype, sentinel), _fp(vals), _ip(idx))
     if rc != 0:
         raise ValueError(f"atk_oracle_topk rejected the arguments (rc={rc})")
     return vals.to(x.dtype).reshape(*batch, k), idx.reshape(*batch, k)
@@ -124,11 +158,11 @@ def bucketed_argmax(x: torch.Tensor, k: int, interleaved: bool) -> tuple[torch.T
     """k_b = 1 path with first-max tie rule and the padded geometry of topk_torch."""
     x2, batch = _rows(x)
     rows, n = x2.shape
-    vals = torch.empty((rows, k), dtype=torch.float32)
+    vals = torch.empty((rows, k), dtype=x2.dtype)
     idx = torch.empty((rows, k), dtype=torch.int64)
-    pad = torch.finfo(x.dtype).min if x.dtype.is_floating_point else float(torch.iinfo(x.dtype).min)
-    rc = lib().atk_oracle_bucketed_argmax(_fp(x2), rows, n, n, k, int(interleaved), pad,
-                                          _fp(vals), _ip(idx))
+    pad = lowest(x.dtype)
+    rc = _fn("atk_oracle_bucketed_argmax", x.dtype)(_fp(x2), rows, n, n, k, int(interleaved), pad,
+                                                    _fp(vals), _ip(idx))
     if rc != 0:
         raise ValueError(f"atk_oracle_bucketed_argmax rejected the arguments (rc={rc})")
     return vals.to(x.dtype).reshape(*batch, k), idx.reshape(*batch, k)
@@ -137,14 +171,14 @@ def bucketed_argmax(x: torch.Tensor, k: int, interleaved: bool) -> tuple[torch.T
 def recall(x: torch.Tensor, approx_vals: torch.Tensor) -> float:
     """Value-threshold recall (reference benchmarks/run_recall.py:27-36)."""
     x2, _ = _rows(x)
-    a2, _ = _rows(approx_vals)
+    a2, _ = _rows(approx_vals.to(x.dtype))
     rows, n = x2.shape
-    return float(lib().atk_oracle_recall(_fp(x2), rows, n, n, _fp(a2), a2.shape[-1]))
+    return float(_fn("atk_oracle_recall", x.dtype)(_fp(x2), rows, n, n, _fp(a2), a2.shape[-1]))
 
 
 def canonical(vals: torch.Tensor, idx: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """Sort every row's (value, index) pairs by value descending, index ascending."""
-    v = vals.detach().to("cpu").to(torch.float32).reshape(-1, vals.shape[-1])
+    v = vals.detach().to("cpu").to(_CARRIERS[carrier_of(vals.dtype)][2]).reshape(-1, vals.shape[-1])
     i = idx.detach().to("cpu").reshape(-1, idx.shape[-1])
     o1 = torch.argsort(i, dim=-1, stable=True)
     v, i = v.gather(-1, o1), i.gather(-1, o1)

@@ -28,7 +28,12 @@ ATK_ERR_TOO_LARGE = -7
 ATK_ERR_CUDA = -8
 ATK_ERR_SCRATCH_LIMIT = -9
 
-DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+# Codes of include/atk.h; the nine element types of the reference's native
+# dispatch (approx_topk/priority_queue_approx_topk.cu:449-453).
+DTYPE_CODES = {
+    torch.float32: 0, torch.float16: 1, torch.bfloat16: 2,
+    torch.float64: 3, torch.int32: 4, torch.int64: 5, torch.int16: 6, torch.int8: 7, torch.uint8: 8,
+}
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -99,8 +104,8 @@ def dtype_code(dtype: torch.dtype) -> int:
         return DTYPE_CODES[dtype]
     except KeyError:
         raise RuntimeError(
-            f"approx_topk: dtype {dtype} is not supported by this build "
-            "(float32, float16 and bfloat16 are)"
+            f"approx_topk: dtype {dtype} is not supported "
+            "(float32/16, bfloat16, float64, int8/16/32/64 and uint8 are)"
         ) from None
 
 

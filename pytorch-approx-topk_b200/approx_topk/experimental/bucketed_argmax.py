@@ -49,11 +49,6 @@ def _batch_contiguous(x: Tensor) -> Tensor:
 
 def _argmax_cuda(xs: Tensor, k: int, dim: int, interleaved: bool) -> tuple[Tensor, Tensor]:
     _native.require_cuda(xs)
-    if not xs.dtype.is_floating_point:
-        raise NotImplementedError(
-            f"bucketed arg-max: dtype {xs.dtype} is not supported by this build "
-            "(float32, float16 and bfloat16 are)"
-        )
     code = _native.dtype_code(xs.dtype)
     dim = dim % xs.ndim
     last = xs.ndim - 1

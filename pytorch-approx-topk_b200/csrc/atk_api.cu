@@ -19,6 +19,12 @@ int elem_size(int dtype) {
     case ATK_F32: return 4;
     case ATK_F16: return 2;
     case ATK_BF16: return 2;
+    case ATK_F64: return 8;
+    case ATK_I32: return 4;
+    case ATK_I64: return 8;
+    case ATK_I16: return 2;
+    case ATK_I8: return 1;
+    case ATK_U8: return 1;
     default: return 0;
   }
 }
@@ -45,6 +51,12 @@ int sweep_dispatch(const SweepLaunch& a, int dtype) {
     case ATK_F32: return launch_sweep_f32(a);
     case ATK_F16: return launch_sweep_f16(a);
     case ATK_BF16: return launch_sweep_bf16(a);
+    case ATK_F64: return launch_sweep_f64(a);
+    case ATK_I32: return launch_sweep_i32(a);
+    case ATK_I64: return launch_sweep_i64(a);
+    case ATK_I16: return launch_sweep_i16(a);
+    case ATK_I8: return launch_sweep_i8(a);
+    case ATK_U8: return launch_sweep_u8(a);
     default: return ATK_ERR_BAD_DTYPE;
   }
 }
@@ -72,7 +84,7 @@ const char* atk_strerror(int status) {
     case ATK_ERR_BAD_J: return "topk: j must 0 < j < 5";
     case ATK_ERR_J_DIVIDES_K: return "topk: j must divide k";
     case ATK_ERR_K_TOO_LARGE: return "topk: k must not be larger than topk size";
-    case ATK_ERR_BAD_DTYPE: return "topk: unsupported dtype (float32, float16 and bfloat16 are supported)";
+    case ATK_ERR_BAD_DTYPE: return "topk: unsupported dtype (float32/16, bfloat16, float64, int8/16/32/64 and uint8 are supported)";
     case ATK_ERR_BAD_ARG: return "topk: invalid argument";
     case ATK_ERR_WORKSPACE: return "topk: workspace missing or too small";
     case ATK_ERR_TOO_LARGE: return "topk: problem size exceeds the kernel's index range";

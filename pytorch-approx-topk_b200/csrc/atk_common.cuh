@@ -19,32 +19,80 @@ void note_launch(int n = 1);
 constexpr int kSentinelLast = -1;
 constexpr int kSentinelFirst = 0x7fffffff;
 
+// Per element type: the code in the C ABI, the preferred vector width of the
+// sweep (elements per load), the raw storage word (`Bits`), and the type the
+// compares run in (`Compute`: float for the three small float types, which
+// widen exactly; int for the integer types of 32 bits or fewer; the type itself
+// for the 64-bit ones).  `floor()` is the value of a never-filled queue slot:
+// it ranks below or equal to every element, and a real element of equal value
+// outranks it through the sentinel position.
 template <typename T> struct ElemTraits;
 template <> struct ElemTraits<float> {
   static constexpr int kDtype = ATK_F32;
   static constexpr int kVec = 4;  // elements per 16-byte load
+  static constexpr bool kHalfFloat = false;
   using Bits = uint32_t;
+  using Compute = float;
   static __device__ __forceinline__ float widen(Bits b) { return __uint_as_float(b); }
   static __device__ __forceinline__ Bits narrow(float f) { return __float_as_uint(f); }
   static __device__ __forceinline__ float lowest() { return -3.402823466e+38f; }
+  static __device__ __forceinline__ float floor() { return -INFINITY; }
 };
 template <> struct ElemTraits<__half> {
   static constexpr int kDtype = ATK_F16;
   static constexpr int kVec = 8;
+  static constexpr bool kHalfFloat = true;
   using Bits = uint16_t;
+  using Compute = float;
   static __device__ __forceinline__ float widen(Bits b) { return __half2float(__ushort_as_half(b)); }
   static __device__ __forceinline__ Bits narrow(float f) { return __half_as_ushort(__float2half_rn(f)); }
   static __device__ __forceinline__ float lowest() { return -65504.0f; }
+  static __device__ __forceinline__ float floor() { return -INFINITY; }
 };
 template <> struct ElemTraits<__nv_bfloat16> {
   static constexpr int kDtype = ATK_BF16;
   static constexpr int kVec = 8;
+  static constexpr bool kHalfFloat = true;
   using Bits = uint16_t;
+  using Compute = float;
   static __device__ __forceinline__ float widen(Bits b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
   // The float always originates from a bf16, so the low 16 bits are zero.
   static __device__ __forceinline__ Bits narrow(float f) { return static_cast<Bits>(__float_as_uint(f) >> 16); }
   static __device__ __forceinline__ float lowest() { return -3.3895313892515355e+38f; }
+  static __device__ __forceinline__ float floor() { return -INFINITY; }
 };
+template <> struct ElemTraits<double> {
+  static constexpr int kDtype = ATK_F64;
+  static constexpr int kVec = 2;
+  static constexpr bool kHalfFloat = false;
+  using Bits = unsigned long long;
+  using Compute = double;
+  static __device__ __forceinline__ double widen(Bits b) { return __longlong_as_double(static_cast<long long>(b)); }
+  static __device__ __forceinline__ Bits narrow(double f) { return static_cast<Bits>(__double_as_longlong(f)); }
+  static __device__ __forceinline__ double lowest() { return -1.7976931348623157e+308; }
+  static __device__ __forceinline__ double floor() { return -__longlong_as_double(0x7ff0000000000000ll); }
+};
+// Integer types: `SIGNED` is the signed type of the same width (or the type
+// itself), `lo` the smallest value.
+template <typename S, typename BITS, typename COMPUTE, int DTYPE, int VEC, long long LO>
+struct IntTraits {
+  static constexpr int kDtype = DTYPE;
+  static constexpr int kVec = VEC;
+  static constexpr bool kHalfFloat = false;
+  using Bits = BITS;
+  using Compute = COMPUTE;
+  static __device__ __forceinline__ COMPUTE widen(BITS b) { return static_cast<COMPUTE>(static_cast<S>(b)); }
+  static __device__ __forceinline__ BITS narrow(COMPUTE v) { return static_cast<BITS>(v); }
+  static __device__ __forceinline__ COMPUTE lowest() { return static_cast<COMPUTE>(LO); }
+  static __device__ __forceinline__ COMPUTE floor() { return static_cast<COMPUTE>(LO); }
+};
+template <> struct ElemTraits<int32_t> : IntTraits<int32_t, uint32_t, int, ATK_I32, 4, -2147483647ll - 1> {};
+template <> struct ElemTraits<long long>
+    : IntTraits<long long, unsigned long long, long long, ATK_I64, 2, -9223372036854775807ll - 1> {};
+template <> struct ElemTraits<int16_t> : IntTraits<int16_t, uint16_t, int, ATK_I16, 8, -32768> {};
+// 8-bit elements: 8 columns per thread (8-byte loads) keep the queues in registers
+template <> struct ElemTraits<int8_t> : IntTraits<int8_t, uint8_t, int, ATK_I8, 8, -128> {};
+template <> struct ElemTraits<uint8_t> : IntTraits<uint8_t, uint8_t, int, ATK_U8, 8, 0> {};
 
 // ---- loads of the input, which is read exactly once -------------------------
 // Input loads.  Plain cached loads measured 2-6 % faster than ld.global.cs /
@@ -80,10 +128,76 @@ __device__ __forceinline__ uint32_t ld_stream_4(const void* p) {
 __device__ __forceinline__ uint16_t ld_stream_2(const void* p) {
   return __ldcs(reinterpret_cast<const unsigned short*>(p));
 }
+__device__ __forceinline__ uint8_t ld_stream_1(const void* p) {
+  return __ldcs(reinterpret_cast<const unsigned char*>(p));
+}
 
-// Load V consecutive elements starting at p and widen them to float.
-// V == kVec: one aligned 16-byte load.  V == 1: one scalar load.
-template <typename T, int V> struct VecLoad;
+// One element as its raw storage word.
+template <typename T>
+__device__ __forceinline__ typename ElemTraits<T>::Bits load_elem_bits(const T* p) {
+  return __ldcs(reinterpret_cast<const typename ElemTraits<T>::Bits*>(p));
+}
+
+// A load of BYTES bytes and its view as 32-bit words (low word first).
+template <int BYTES> struct RawBytes;
+template <> struct RawBytes<16> {
+  using Raw = uint4;
+  static constexpr int kWords = 4;
+  static __device__ __forceinline__ Raw load(const void* p) { return ld_stream_16(p); }
+  static __device__ __forceinline__ void words(const Raw& r, uint32_t (&w)[4]) { w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w; }
+};
+template <> struct RawBytes<8> {
+  using Raw = uint2;
+  static constexpr int kWords = 2;
+  static __device__ __forceinline__ Raw load(const void* p) { return ld_stream_8(p); }
+  static __device__ __forceinline__ void words(const Raw& r, uint32_t (&w)[2]) { w[0] = r.x; w[1] = r.y; }
+};
+template <> struct RawBytes<4> {
+  using Raw = uint32_t;
+  static constexpr int kWords = 1;
+  static __device__ __forceinline__ Raw load(const void* p) { return ld_stream_4(p); }
+  static __device__ __forceinline__ void words(const Raw& r, uint32_t (&w)[1]) { w[0] = r; }
+};
+template <> struct RawBytes<2> {
+  using Raw = uint16_t;
+  static constexpr int kWords = 1;
+  static __device__ __forceinline__ Raw load(const void* p) { return ld_stream_2(p); }
+  static __device__ __forceinline__ void words(const Raw& r, uint32_t (&w)[1]) { w[0] = r; }
+};
+template <> struct RawBytes<1> {
+  using Raw = uint8_t;
+  static constexpr int kWords = 1;
+  static __device__ __forceinline__ Raw load(const void* p) { return ld_stream_1(p); }
+  static __device__ __forceinline__ void words(const Raw& r, uint32_t (&w)[1]) { w[0] = r; }
+};
+
+// Load V consecutive elements starting at p and widen them to the compute type.
+// V > 1: one aligned vector load of V * sizeof(T) bytes.  V == 1: one scalar load.
+// The primary template serves the integer and 64-bit types (elements are cut
+// out of the loaded words); the small float types have their own conversions.
+template <typename T, int V> struct VecLoad {
+  using Tr = ElemTraits<T>;
+  using RB = RawBytes<V * static_cast<int>(sizeof(T))>;
+  using Raw = typename RB::Raw;
+  static __device__ __forceinline__ Raw load(const T* p) { return RB::load(p); }
+  static __device__ __forceinline__ void widen(const Raw& r, typename Tr::Compute (&v)[V]) {
+    uint32_t w[RB::kWords];
+    RB::words(r, w);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      if constexpr (sizeof(T) == 8) {
+        v[e] = Tr::widen(static_cast<typename Tr::Bits>(w[2 * e]) |
+                         (static_cast<typename Tr::Bits>(w[2 * e + 1]) << 32));
+      } else if constexpr (sizeof(T) == 4) {
+        v[e] = Tr::widen(w[e]);
+      } else if constexpr (sizeof(T) == 2) {
+        v[e] = Tr::widen(static_cast<typename Tr::Bits>((w[e / 2] >> (16 * (e & 1))) & 0xffffu));
+      } else {
+        v[e] = Tr::widen(static_cast<typename Tr::Bits>((w[e / 4] >> (8 * (e & 3))) & 0xffu));
+      }
+    }
+  }
+};
 template <> struct VecLoad<float, 4> {
   using Raw = uint4;
   static __device__ __forceinline__ Raw load(const float* p) { return ld_stream_16(p); }
@@ -171,8 +285,8 @@ template <> struct VecLoad<__half, 1> {
 // the re-evaluated `head ? v : qv[0]` to qv[0] inside rolled loops, leaving a
 // stale value next to the right index.  Reusing the branch predicate itself
 // gives the optimiser nothing to "correlate".
-template <int J, bool FIRST>
-__device__ __forceinline__ void queue_push_scan(float (&qv)[J], int (&qi)[J], float v, int pos, bool head) {
+template <int J, bool FIRST, typename C>
+__device__ __forceinline__ void queue_push_scan(C (&qv)[J], int (&qi)[J], C v, int pos, bool head) {
   bool p[J + 1];
 #pragma unroll
   for (int i = 0; i < J; ++i) {
@@ -188,21 +302,21 @@ __device__ __forceinline__ void queue_push_scan(float (&qv)[J], int (&qi)[J], fl
   for (int i = 0; i < J; ++i) {
     // slot i takes slot i+1's content when the new item moves past i+1, the
     // new item when it stops here, otherwise it keeps its content.
-    const float nv = p[i + 1] ? qv[i + 1 < J ? i + 1 : i] : (p[i] ? v : qv[i]);
-    const int   ni = p[i + 1] ? qi[i + 1 < J ? i + 1 : i] : (p[i] ? pos : qi[i]);
+    const C   nv = p[i + 1] ? qv[i + 1 < J ? i + 1 : i] : (p[i] ? v : qv[i]);
+    const int ni = p[i + 1] ? qi[i + 1 < J ? i + 1 : i] : (p[i] ? pos : qi[i]);
     qv[i] = nv;
     qi[i] = ni;
   }
 }
-template <int J, bool FIRST>
-__device__ __forceinline__ void queue_push_scan(float (&qv)[J], int (&qi)[J], float v, int pos) {
-  queue_push_scan<J, FIRST>(qv, qi, v, pos, !(qv[0] > v));
+template <int J, bool FIRST, typename C>
+__device__ __forceinline__ void queue_push_scan(C (&qv)[J], int (&qi)[J], C v, int pos) {
+  queue_push_scan<J, FIRST, C>(qv, qi, v, pos, !(qv[0] > v));
 }
 
 // Order-independent insertion used when partial queues are merged: the rank is
 // (value, position) with the tie rule made explicit.
-template <int J, bool FIRST>
-__device__ __forceinline__ void queue_push_ranked(float (&qv)[J], int (&qi)[J], float v, int pos) {
+template <int J, bool FIRST, typename C>
+__device__ __forceinline__ void queue_push_ranked(C (&qv)[J], int (&qi)[J], C v, int pos) {
   bool p[J + 1];
 #pragma unroll
   for (int i = 0; i < J; ++i) {
@@ -212,8 +326,8 @@ __device__ __forceinline__ void queue_push_ranked(float (&qv)[J], int (&qi)[J], 
   p[J] = false;
 #pragma unroll
   for (int i = 0; i < J; ++i) {
-    const float nv = p[i + 1] ? qv[i + 1 < J ? i + 1 : i] : (p[i] ? v : qv[i]);
-    const int   ni = p[i + 1] ? qi[i + 1 < J ? i + 1 : i] : (p[i] ? pos : qi[i]);
+    const C   nv = p[i + 1] ? qv[i + 1 < J ? i + 1 : i] : (p[i] ? v : qv[i]);
+    const int ni = p[i + 1] ? qi[i + 1 < J ? i + 1 : i] : (p[i] ? pos : qi[i]);
     qv[i] = nv;
     qi[i] = ni;
   }

@@ -2,7 +2,7 @@
 //
 // A bucket is a contiguous segment of the row.  A group of G lanes (G a power
 // of two <= 32, chosen from the bucket length) strides through the segment
-// with coalesced (16-byte where aligned) loads, every lane keeping its own J-queue; the queues
+// with coalesced (vector where aligned) loads, every lane keeping its own J-queue; the queues
 // are then merged with xor-shuffles under the explicit tie rule and lane 0
 // writes the bucket's J slots (contig_kernel, used for long buckets).  Short
 // buckets go through contig_tile_kernel, which stages a span of 128 buckets in
@@ -36,21 +36,23 @@ struct ContigParams {
 // scalar tail.  Each lane sees its elements in increasing position order, so
 // the serial insertion rule applies; positions are offsets inside the segment.
 template <typename T, int J, bool FIRST>
-__device__ __forceinline__ void contig_scan_segment(const T* seg, long long size, int l, int nl, float (&qv)[J],
-                                                    int (&qi)[J]) {
+__device__ __forceinline__ void contig_scan_segment(const T* seg, long long size, int l, int nl,
+                                                    typename ElemTraits<T>::Compute (&qv)[J], int (&qi)[J]) {
+  using C = typename ElemTraits<T>::Compute;
   constexpr int V = ElemTraits<T>::kVec;
+  constexpr int kVecBytes = V * static_cast<int>(sizeof(T));
   const uintptr_t addr0 = reinterpret_cast<uintptr_t>(seg);
-  long long head = static_cast<long long>(((16 - (addr0 & 15)) & 15) / sizeof(T));
+  long long head = static_cast<long long>(((kVecBytes - (addr0 & (kVecBytes - 1))) & (kVecBytes - 1)) / sizeof(T));
   if (head > size) head = size;
   const long long body = (size - head) / V;
   for (long long i = l; i < head; i += nl) {
-    float f[1];
+    C f[1];
     VecLoad<T, 1>::widen(VecLoad<T, 1>::load(seg + i), f);
     queue_push_scan<J, FIRST>(qv, qi, f[0], static_cast<int>(i));
   }
   long long v = l;
   for (; v + nl < body; v += 2 * nl) {     // two independent vector loads in flight
-    float f0[V], f1[V];
+    C f0[V], f1[V];
     const typename VecLoad<T, V>::Raw r0 = VecLoad<T, V>::load(seg + head + v * V);
     const typename VecLoad<T, V>::Raw r1 = VecLoad<T, V>::load(seg + head + (v + nl) * V);
     VecLoad<T, V>::widen(r0, f0);
@@ -61,13 +63,13 @@ __device__ __forceinline__ void contig_scan_segment(const T* seg, long long size
     for (int e = 0; e < V; ++e) queue_push_scan<J, FIRST>(qv, qi, f1[e], static_cast<int>(head + (v + nl) * V + e));
   }
   for (; v < body; v += nl) {
-    float f[V];
+    C f[V];
     VecLoad<T, V>::widen(VecLoad<T, V>::load(seg + head + v * V), f);
 #pragma unroll
     for (int e = 0; e < V; ++e) queue_push_scan<J, FIRST>(qv, qi, f[e], static_cast<int>(head + v * V + e));
   }
   for (long long i = head + body * V + l; i < size; i += nl) {
-    float f[1];
+    C f[1];
     VecLoad<T, 1>::widen(VecLoad<T, 1>::load(seg + i), f);
     queue_push_scan<J, FIRST>(qv, qi, f[0], static_cast<int>(i));
   }
@@ -77,6 +79,7 @@ template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(256) contig_kernel(const ContigParams p) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
+  using C = typename Tr::Compute;
   const int G = p.g;
   const long long gid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / G;
   const int lane = threadIdx.x % G;
@@ -98,18 +101,18 @@ __global__ void __launch_bounds__(256) contig_kernel(const ContigParams p) {
   }
   if (!valid) size = 0;
 
-  float qv[J];
+  C qv[J];
   int qi[J];
 #pragma unroll
   for (int q = 0; q < J; ++q) {
-    qv[q] = -INFINITY;
+    qv[q] = Tr::floor();
     qi[q] = FIRST ? kSentinelFirst : kSentinelLast;
   }
   const T* seg = static_cast<const T*>(p.x) + row * p.row_stride + start;
   contig_scan_segment<T, J, FIRST>(seg, size, lane, G, qv, qi);
   // Butterfly merge inside the group; all 32 lanes of the warp take part.
   for (int off = G >> 1; off >= 1; off >>= 1) {
-    float ov[J];
+    C ov[J];
     int oi[J];
 #pragma unroll
     for (int q = 0; q < J; ++q) {
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(256) contig_kernel(const ContigParams p) {
   long long* idst = p.out_idx + row * p.out_row_stride + c * J;
 #pragma unroll
   for (int q = 0; q < J; ++q) {
-    float val = qv[q];
+    C val = qv[q];
     long long pos = qi[q];
     if (FIRST && qi[q] == kSentinelFirst) {  // empty (all padding) bucket
       val = Tr::lowest();
@@ -142,7 +145,8 @@ template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(256) contig_block_kernel(const ContigParams p) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
-  __shared__ float sv[8][J];
+  using C = typename Tr::Compute;
+  __shared__ C sv[8][J];
   __shared__ int si[8][J];
   const long long gid = blockIdx.x;
   const long long row = gid / p.b;
@@ -161,17 +165,17 @@ __global__ void __launch_bounds__(256) contig_block_kernel(const ContigParams p)
     start = big * (p.base + 1) + normal * p.base;
     size = p.base + (c < p.rem ? 1 : 0);
   }
-  float qv[J];
+  C qv[J];
   int qi[J];
 #pragma unroll
   for (int q = 0; q < J; ++q) {
-    qv[q] = -INFINITY;
+    qv[q] = Tr::floor();
     qi[q] = FIRST ? kSentinelFirst : kSentinelLast;
   }
   const T* seg = static_cast<const T*>(p.x) + row * p.row_stride + start;
   contig_scan_segment<T, J, FIRST>(seg, size, threadIdx.x, 256, qv, qi);
   for (int off = 16; off >= 1; off >>= 1) {
-    float ov[J];
+    C ov[J];
     int oi[J];
 #pragma unroll
     for (int q = 0; q < J; ++q) {
@@ -197,7 +201,7 @@ __global__ void __launch_bounds__(256) contig_block_kernel(const ContigParams p)
   long long* idst = p.out_idx + row * p.out_row_stride + c * J;
 #pragma unroll
   for (int q = 0; q < J; ++q) {
-    float val = qv[q];
+    C val = qv[q];
     long long pos = qi[q];
     if (FIRST && qi[q] == kSentinelFirst) {
       val = Tr::lowest();
@@ -212,8 +216,8 @@ __global__ void __launch_bounds__(256) contig_block_kernel(const ContigParams p)
 // Short buckets (at most kTileMaxBucket elements): one block takes kTileBuckets
 // consecutive buckets of a row, i.e. one contiguous span of the row.  The span
 // is loaded cooperatively with coalesced (16-byte where aligned) loads into
-// shared memory as floats, then thread t scans bucket t from shared memory with
-// the reference's serial insertion rule.  The float index i is stored at
+// shared memory in the compute type, then thread t scans bucket t from shared memory with
+// the reference's serial insertion rule.  Element i of the span is stored at
 // i + i/32, which makes the per-thread strides conflict-free for every bucket
 // length.
 constexpr int kTileBuckets = 128;    // buckets per block = threads per block
@@ -238,8 +242,11 @@ template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(kTileBuckets) contig_tile_kernel(const ContigParams p, long long tiles) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
+  using C = typename Tr::Compute;
   constexpr int V = Tr::kVec;
-  extern __shared__ __align__(16) float tile_smem[];
+  constexpr int kVecBytes = V * static_cast<int>(sizeof(T));
+  extern __shared__ __align__(16) unsigned char tile_smem_raw[];
+  C* tile_smem = reinterpret_cast<C*>(tile_smem_raw);
   const int t = threadIdx.x;
   const long long row = static_cast<long long>(blockIdx.x) / tiles;
   const long long tile = static_cast<long long>(blockIdx.x) - row * tiles;
@@ -257,16 +264,16 @@ __global__ void __launch_bounds__(kTileBuckets) contig_tile_kernel(const ContigP
 
   // head up to the first 16-byte boundary, aligned body, tail: all inside [g0, g1)
   const uintptr_t addr0 = reinterpret_cast<uintptr_t>(src + g0);
-  long long head = static_cast<long long>(((16 - (addr0 & 15)) & 15) / sizeof(T));
+  long long head = static_cast<long long>(((kVecBytes - (addr0 & (kVecBytes - 1))) & (kVecBytes - 1)) / sizeof(T));
   if (head > span) head = span;
   const long long body = (span - head) / V;    // whole vectors
   for (long long i = t; i < head; i += kTileBuckets) {
-    float f[1];
+    C f[1];
     VecLoad<T, 1>::widen(VecLoad<T, 1>::load(src + g0 + i), f);
     tile_smem[i + (i >> 5)] = f[0];
   }
   for (long long v = t; v < body; v += kTileBuckets) {
-    float f[V];
+    C f[V];
     VecLoad<T, V>::widen(VecLoad<T, V>::load(src + g0 + head + v * V), f);
 #pragma unroll
     for (int e = 0; e < V; ++e) {
@@ -275,7 +282,7 @@ __global__ void __launch_bounds__(kTileBuckets) contig_tile_kernel(const ContigP
     }
   }
   for (long long i = head + body * V + t; i < span; i += kTileBuckets) {
-    float f[1];
+    C f[1];
     VecLoad<T, 1>::widen(VecLoad<T, 1>::load(src + g0 + i), f);
     tile_smem[i + (i >> 5)] = f[0];
   }
@@ -285,11 +292,11 @@ __global__ void __launch_bounds__(kTileBuckets) contig_tile_kernel(const ContigP
   if (c >= c_end) return;
   long long start, size;
   bucket_extent(p, c, start, size);
-  float qv[J];
+  C qv[J];
   int qi[J];
 #pragma unroll
   for (int q = 0; q < J; ++q) {
-    qv[q] = -INFINITY;
+    qv[q] = Tr::floor();
     qi[q] = FIRST ? kSentinelFirst : kSentinelLast;
   }
   const long long o = start - g0;
@@ -301,7 +308,7 @@ __global__ void __launch_bounds__(kTileBuckets) contig_tile_kernel(const ContigP
   long long* idst = p.out_idx + row * p.out_row_stride + c * J;
 #pragma unroll
   for (int q = 0; q < J; ++q) {
-    float val = qv[q];
+    C val = qv[q];
     long long pos = qi[q];
     if (FIRST && qi[q] == kSentinelFirst) {  // empty (all padding) bucket
       val = Tr::lowest();
@@ -338,7 +345,7 @@ int launch_typed(const ContigLaunch& a) {
     const long long tiles = (a.b + kTileBuckets - 1) / kTileBuckets;
     if (a.rows * tiles >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     const long long span = static_cast<long long>(kTileBuckets) * (p.base + 1);
-    const size_t smem = static_cast<size_t>(span + span / 32 + 2) * sizeof(float);
+    const size_t smem = static_cast<size_t>(span + span / 32 + 2) * sizeof(typename ElemTraits<T>::Compute);
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(contig_tile_kernel<T, J, FIRST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
@@ -388,6 +395,12 @@ int launch_contig(const ContigLaunch& a, int dtype) {
     case ATK_F32: return launch_by_j<float>(a);
     case ATK_F16: return launch_by_j<__half>(a);
     case ATK_BF16: return launch_by_j<__nv_bfloat16>(a);
+    case ATK_F64: return launch_by_j<double>(a);
+    case ATK_I32: return launch_by_j<int32_t>(a);
+    case ATK_I64: return launch_by_j<long long>(a);
+    case ATK_I16: return launch_by_j<int16_t>(a);
+    case ATK_I8: return launch_by_j<int8_t>(a);
+    case ATK_U8: return launch_by_j<uint8_t>(a);
     default: return ATK_ERR_BAD_DTYPE;
   }
 }

@@ -1,9 +1,11 @@
 // Per-column queues of the J best elements, in three register layouts.
 //
-// FloatQueue  — J (float value, int stripe) pairs; works for every dtype (the
-//               16-bit formats widen to float exactly) and follows the
-//               reference's insertion rule instruction for instruction,
-//               NaN behaviour included.
+// FloatQueue  — J (value, int stripe) pairs with the value in the element
+//               type's compute type (float for the float types of 32 bits or
+//               fewer, which widen exactly; int / long long / double for the
+//               rest).  Works for every dtype and follows the reference's
+//               insertion rule instruction for instruction, NaN behaviour
+//               included.
 // PackedQueue — for 16-bit inputs whose columns have at most 65536 stripes:
 //               one 32-bit word per entry, (order-preserving image of the
 //               value) << 16 | stripe, so that the (value, position) ranking
@@ -26,20 +28,57 @@
 namespace atk {
 
 // ---------------------------------------------------------------- FloatQueue
+// 32-bit words of a compute-type value, for the trip through shared memory.
+template <typename C> struct ComputeWords;
+template <> struct ComputeWords<float> {
+  static constexpr int kN = 1;
+  static __device__ __forceinline__ void put(float v, uint32_t* base, int stride) { base[0] = __float_as_uint(v); }
+  static __device__ __forceinline__ float get(const uint32_t* base, int stride) { return __uint_as_float(base[0]); }
+};
+template <> struct ComputeWords<int> {
+  static constexpr int kN = 1;
+  static __device__ __forceinline__ void put(int v, uint32_t* base, int stride) { base[0] = static_cast<uint32_t>(v); }
+  static __device__ __forceinline__ int get(const uint32_t* base, int stride) { return static_cast<int>(base[0]); }
+};
+template <> struct ComputeWords<long long> {
+  static constexpr int kN = 2;
+  static __device__ __forceinline__ void put(long long v, uint32_t* base, int stride) {
+    base[0] = static_cast<uint32_t>(static_cast<unsigned long long>(v));
+    base[stride] = static_cast<uint32_t>(static_cast<unsigned long long>(v) >> 32);
+  }
+  static __device__ __forceinline__ long long get(const uint32_t* base, int stride) {
+    return static_cast<long long>(static_cast<unsigned long long>(base[0]) |
+                                  (static_cast<unsigned long long>(base[stride]) << 32));
+  }
+};
+template <> struct ComputeWords<double> {
+  static constexpr int kN = 2;
+  static __device__ __forceinline__ void put(double v, uint32_t* base, int stride) {
+    ComputeWords<long long>::put(__double_as_longlong(v), base, stride);
+  }
+  static __device__ __forceinline__ double get(const uint32_t* base, int stride) {
+    return __longlong_as_double(ComputeWords<long long>::get(base, stride));
+  }
+};
+
 template <typename T, int J, bool FIRST>
 struct FloatQueue {
-  static constexpr int kWords = 2 * J;  // 32-bit words per queue in shared memory
+  using Tr = ElemTraits<T>;
+  using C = typename Tr::Compute;
+  using CW = ComputeWords<C>;
+  static constexpr int kEntryWords = CW::kN + 1;
+  static constexpr int kWords = kEntryWords * J;  // 32-bit words per queue in shared memory
   static constexpr bool kPacked = false;
   static constexpr int kCols = 1;       // columns served by one queue object
   static constexpr int kJ = J;
   static constexpr bool kFirst = FIRST;
-  float v[J];
+  C v[J];
   int s[J];
 
   __device__ __forceinline__ void init() {
 #pragma unroll
     for (int q = 0; q < J; ++q) {
-      v[q] = -INFINITY;
+      v[q] = Tr::floor();
       s[q] = FIRST ? kSentinelFirst : kSentinelLast;
     }
   }
@@ -47,7 +86,7 @@ struct FloatQueue {
   template <int V, bool SKIP>
   static __device__ __forceinline__ void consume(FloatQueue (&q)[V], const typename VecLoad<T, V>::Raw& raw,
                                                  int stripe) {
-    float x[V];
+    C x[V];
     VecLoad<T, V>::widen(raw, x);
     bool head[V];
 #pragma unroll
@@ -69,34 +108,27 @@ struct FloatQueue {
   }
 
   // one element of the ragged last stripe
-  __device__ __forceinline__ void push_tail(typename ElemTraits<T>::Bits bits, int stripe) {
-    queue_push_scan<J, FIRST>(v, s, ElemTraits<T>::widen(bits), stripe);
+  __device__ __forceinline__ void push_tail(typename Tr::Bits bits, int stripe) {
+    queue_push_scan<J, FIRST>(v, s, Tr::widen(bits), stripe);
   }
 
   __device__ __forceinline__ void store(uint32_t* base, int stride) const {
 #pragma unroll
     for (int q = 0; q < J; ++q) {
-      base[(2 * q) * stride] = __float_as_uint(v[q]);
-      base[(2 * q + 1) * stride] = static_cast<uint32_t>(s[q]);
+      CW::put(v[q], base + (kEntryWords * q) * stride, stride);
+      base[(kEntryWords * q + CW::kN) * stride] = static_cast<uint32_t>(s[q]);
     }
   }
   __device__ __forceinline__ void merge(const uint32_t* base, int stride) {
 #pragma unroll
     for (int q = 0; q < J; ++q)
-      queue_push_ranked<J, FIRST>(v, s, __uint_as_float(base[(2 * q) * stride]),
-                                  static_cast<int>(base[(2 * q + 1) * stride]));
+      queue_push_ranked<J, FIRST>(v, s, CW::get(base + (kEntryWords * q) * stride, stride),
+                                  static_cast<int>(base[(kEntryWords * q + CW::kN) * stride]));
   }
 
   __device__ __forceinline__ long long stripe(int q) const { return s[q]; }
-  // value bits for the output; `elem` is only read to restore a zero's sign
-  __device__ __forceinline__ typename ElemTraits<T>::Bits value_bits(int q, const T*) const {
-    return ElemTraits<T>::narrow(v[q]);
-  }
-  // order-preserving 32-bit image of the value for the exact select
-  __device__ __forceinline__ uint32_t select_key(int q) const {
-    const uint32_t u = __float_as_uint(v[q]);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-  }
+  // value bits for the output (`elem` is unused: the compute value is exact)
+  __device__ __forceinline__ typename Tr::Bits value_bits(int q, const T*) const { return Tr::narrow(v[q]); }
 };
 
 // --------------------------------------------------------------- PackedQueue
@@ -202,7 +234,6 @@ struct PackedQueue {
     if (o == 0x8000u) return ld_stream_2(elem);
     return ord16_inverse(o);
   }
-  __device__ __forceinline__ uint32_t select_key(int q) const { return k[q] & 0xffff0000u; }
 };
 
 

@@ -20,7 +20,7 @@
 namespace atk {
 namespace {
 
-constexpr int kSmallMaxK0 = 16384;   // 512 threads x 32 candidates in registers
+constexpr int kSmallMaxK0 = 16384;   // 512 threads x 32 candidates in registers (32-bit keys)
 constexpr int kChunk = 2048;         // candidates per block on the large path
 constexpr int kLargeThreads = 256;
 #ifndef ATK_SELECT_ROW_THREADS
@@ -28,24 +28,67 @@ constexpr int kLargeThreads = 256;
 #endif
 constexpr int kSelectRowThreads = ATK_SELECT_ROW_THREADS;  // preferred block width of the one-block-per-row select
 
+// Order-preserving unsigned image of an element ("key"), its width, and the
+// number of 8-bit radix passes, most significant digit first.  Keys of the
+// types of 32 bits or fewer sit in the top bits of a 32-bit word; the 64-bit
+// types use 64-bit keys.
 template <typename T> struct KeyOf;
 template <> struct KeyOf<float> {
+  using Key = uint32_t;
   static constexpr int kPasses = 4;
-  static __device__ __forceinline__ uint32_t key(uint32_t u) {
+  static __device__ __forceinline__ Key key(uint32_t u) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
   }
 };
 template <> struct KeyOf<__half> {
+  using Key = uint32_t;
   static constexpr int kPasses = 2;
-  static __device__ __forceinline__ uint32_t key(uint16_t h) {
+  static __device__ __forceinline__ Key key(uint16_t h) {
     const uint32_t u = h;
     return ((u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u)) << 16;
   }
 };
 template <> struct KeyOf<__nv_bfloat16> {
+  using Key = uint32_t;
   static constexpr int kPasses = 2;
-  static __device__ __forceinline__ uint32_t key(uint16_t h) { return KeyOf<__half>::key(h); }
+  static __device__ __forceinline__ Key key(uint16_t h) { return KeyOf<__half>::key(h); }
 };
+template <> struct KeyOf<double> {
+  using Key = unsigned long long;
+  static constexpr int kPasses = 8;
+  static __device__ __forceinline__ Key key(unsigned long long u) {
+    return (u >> 63) ? ~u : (u | 0x8000000000000000ull);
+  }
+};
+template <> struct KeyOf<int32_t> {
+  using Key = uint32_t;
+  static constexpr int kPasses = 4;
+  static __device__ __forceinline__ Key key(uint32_t u) { return u ^ 0x80000000u; }
+};
+template <> struct KeyOf<long long> {
+  using Key = unsigned long long;
+  static constexpr int kPasses = 8;
+  static __device__ __forceinline__ Key key(unsigned long long u) { return u ^ 0x8000000000000000ull; }
+};
+template <> struct KeyOf<int16_t> {
+  using Key = uint32_t;
+  static constexpr int kPasses = 2;
+  static __device__ __forceinline__ Key key(uint16_t u) { return (static_cast<uint32_t>(u) ^ 0x8000u) << 16; }
+};
+template <> struct KeyOf<int8_t> {
+  using Key = uint32_t;
+  static constexpr int kPasses = 1;
+  static __device__ __forceinline__ Key key(uint8_t u) { return (static_cast<uint32_t>(u) ^ 0x80u) << 24; }
+};
+template <> struct KeyOf<uint8_t> {
+  using Key = uint32_t;
+  static constexpr int kPasses = 1;
+  static __device__ __forceinline__ Key key(uint8_t u) { return static_cast<uint32_t>(u) << 24; }
+};
+// shift of the digit examined in `pass`
+template <typename K> __device__ __forceinline__ int digit_shift(int pass) {
+  return static_cast<int>(sizeof(typename K::Key)) * 8 - 8 - 8 * pass;
+}
 
 // ------------------------------------------------------------------ small path
 // One block per row.  Thread t owns the ITEMS consecutive candidate slots
@@ -73,8 +116,9 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   const long long* irow = cand_idx + row * cand_row_stride;
   const int slot0 = tid * ITEMS;
 
+  using Key = typename K::Key;
   __align__(16) Bits raw[ITEMS];
-  uint32_t key[ITEMS];
+  Key key[ITEMS];
   constexpr int kRawBytes = ITEMS * static_cast<int>(sizeof(Bits));
   if (vec_ok && kRawBytes % 16 == 0 && slot0 + ITEMS <= k0) {
 #pragma unroll
@@ -101,22 +145,24 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   }
   // Slots past the end get key 0; every use below is guarded by the slot bound.
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) key[i] = slot0 + i < k0 ? K::key(raw[i]) : 0u;
+  for (int i = 0; i < ITEMS; ++i) key[i] = slot0 + i < k0 ? K::key(raw[i]) : Key(0);
 
-  uint32_t prefix = 0, mask = 0, need = static_cast<uint32_t>(k);
+  Key prefix = 0, mask = 0;
+  uint32_t need = static_cast<uint32_t>(k);
 #pragma unroll 1
   for (int pass = 0; pass < K::kPasses; ++pass) {
-    const int shift = 24 - 8 * pass;
+    const int shift = digit_shift<K>(pass);
     for (int i = tid; i < 256; i += nthr) hist[i] = 0;
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i)
-      if (slot0 + i < k0 && (key[i] & mask) == prefix) atomicAdd(&hist[(key[i] >> shift) & 255u], 1u);
+      if (slot0 + i < k0 && (key[i] & mask) == prefix)
+        atomicAdd(&hist[static_cast<uint32_t>(key[i] >> shift) & 255u], 1u);
     __syncthreads();
     if (tid < 32) pick_digit(hist, need, tid, &misc[0], &misc[1]);
     __syncthreads();
-    prefix |= misc[0] << shift;
-    mask |= 255u << shift;
+    prefix |= static_cast<Key>(misc[0]) << shift;
+    mask |= static_cast<Key>(255u) << shift;
     need = misc[1];
   }
 
@@ -185,8 +231,10 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 }
 
 // ------------------------------------------------------------------ large path
+template <typename KEY>
 struct RowState {
-  uint32_t prefix, mask, need, pad;
+  KEY prefix, mask;
+  uint32_t need, pad;
 };
 
 // One radix pass.  Every block histograms its chunk into the row's global
@@ -196,15 +244,17 @@ struct RowState {
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kLargeThreads)
 select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
-                   long long cand_row_stride, int pass, long long k, RowState* __restrict__ state,
+                   long long cand_row_stride, int pass, long long k,
+                   RowState<typename KeyOf<T>::Key>* __restrict__ state,
                    uint32_t* __restrict__ hist /* [rows][passes][256] */,
                    uint32_t* __restrict__ tickets /* [rows][passes + 1] */, int cpb /* chunks per block */) {
   using K = KeyOf<T>;
+  using Key = typename K::Key;
   __shared__ uint32_t sh[256];
   __shared__ uint32_t res[2];
   __shared__ bool last;
   const long long row = blockIdx.y;
-  RowState st;
+  RowState<Key> st;
   if (pass == 0) {
     st.prefix = 0;
     st.mask = 0;
@@ -213,7 +263,7 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   } else {
     st = state[row];
   }
-  const int shift = 24 - 8 * pass;
+  const int shift = digit_shift<K>(pass);
   for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = 0;
   __syncthreads();
   const auto* vrow = cand_vals + row * cand_row_stride;
@@ -232,8 +282,8 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
 #pragma unroll
     for (int u = 0; u < ITEMS; ++u) {
       const long long i = begin + u * kLargeThreads + threadIdx.x;
-      const uint32_t key = K::key(raw[u]);
-      if (i < end && (key & st.mask) == st.prefix) atomicAdd(&sh[(key >> shift) & 255u], 1u);
+      const Key key = K::key(raw[u]);
+      if (i < end && (key & st.mask) == st.prefix) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & 255u], 1u);
     }
   }
   __syncthreads();
@@ -253,8 +303,8 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   if (threadIdx.x < 32) pick_digit(sh, st.need, threadIdx.x, &res[0], &res[1]);
   __syncthreads();
   if (threadIdx.x == 0) {
-    st.prefix |= res[0] << shift;
-    st.mask |= 255u << shift;
+    st.prefix |= static_cast<Key>(res[0]) << shift;
+    st.mask |= static_cast<Key>(255u) << shift;
     st.need = res[1];
     state[row] = st;
   }
@@ -263,14 +313,15 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kLargeThreads)
 select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
-                    long long cand_row_stride, const RowState* __restrict__ state,
+                    long long cand_row_stride, const RowState<typename KeyOf<T>::Key>* __restrict__ state,
                     uint2* __restrict__ counts /* [rows][chunks] */, uint32_t* __restrict__ tickets, int chunks,
                     int cpb /* chunks per block */) {
   using K = KeyOf<T>;
+  using Key = typename K::Key;
   __shared__ uint32_t s_gt, s_eq;
   __shared__ bool last;
   const long long row = blockIdx.y;
-  const uint32_t thr = state[row].prefix;
+  const Key thr = state[row].prefix;
   const auto* vrow = cand_vals + row * cand_row_stride;
   for (int cc = 0; cc < cpb; ++cc) {
     const long long chunk = static_cast<long long>(blockIdx.x) * cpb + cc;
@@ -288,7 +339,7 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
     for (int u = 0; u < ITEMS; ++u) {
       const long long i = begin + u * kLargeThreads + threadIdx.x;
       if (i < end) {
-        const uint32_t key = K::key(vrow[i]);
+        const Key key = K::key(vrow[i]);
         gt += key > thr;
         eq += key == thr;
       }
@@ -341,13 +392,14 @@ template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kLargeThreads)
 select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                     const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride,
-                    long long k, const RowState* __restrict__ state,
+                    long long k, const RowState<typename KeyOf<T>::Key>* __restrict__ state,
                     const uint2* __restrict__ bases, typename ElemTraits<T>::Bits* __restrict__ out_vals,
                     long long* __restrict__ out_idx, long long out_row_stride) {
   using K = KeyOf<T>;
+  using Key = typename K::Key;
   __shared__ uint32_t wsum[32];
   const long long row = blockIdx.y;
-  const uint32_t thr = state[row].prefix;
+  const Key thr = state[row].prefix;
   const uint32_t need = state[row].need;
   const long long n_gt = k - need;
   const uint2 b = bases[row * gridDim.x + blockIdx.x];
@@ -366,7 +418,7 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   const long long slot0 = begin + static_cast<long long>(threadIdx.x) * ITEMS;
   typename ElemTraits<T>::Bits raws[ITEMS];
   long long idxs[ITEMS];
-  uint32_t keys[ITEMS];
+  Key keys[ITEMS];
 #pragma unroll
   for (int u = 0; u < ITEMS; ++u) {
     const long long i = slot0 + u;
@@ -423,10 +475,14 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 inline long long chunks_of(long long k0) { return (k0 + kChunk - 1) / kChunk; }
 inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
+// Largest row the one-block path takes: 512 threads x 32 candidates in
+// registers, half that for 64-bit elements.
+template <typename T> constexpr int small_max_k0() { return sizeof(T) == 8 ? kSmallMaxK0 / 2 : kSmallMaxK0; }
+
 template <typename T>
 size_t workspace_typed(long long rows, long long k0) {
-  if (k0 <= kSmallMaxK0) return 0;
-  const size_t state = align256(sizeof(RowState) * rows);
+  if (k0 <= small_max_k0<T>()) return 0;
+  const size_t state = align256(sizeof(RowState<typename KeyOf<T>::Key>) * rows);
   // digit histograms followed by the ticket counters: the part zeroed per call
   const size_t hist = align256(sizeof(uint32_t) * (256 * KeyOf<T>::kPasses + KeyOf<T>::kPasses + 1) * rows);
   const size_t counts = align256(sizeof(uint2) * chunks_of(k0) * rows);
@@ -439,7 +495,8 @@ int select_typed(const SelectLaunch& a) {
   using K = KeyOf<T>;
   const Bits* cv = static_cast<const Bits*>(a.cand_vals);
   Bits* ov = static_cast<Bits*>(a.out_vals);
-  if (a.k0 <= kSmallMaxK0) {
+  using State = RowState<typename K::Key>;
+  if (a.k0 <= small_max_k0<T>()) {
     if (a.rows >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     const int k0 = static_cast<int>(a.k0);
     const int k = static_cast<int>(a.k);
@@ -455,13 +512,15 @@ int select_typed(const SelectLaunch& a) {
     // block is at most kSelectRowThreads wide (512 measured better than 256 on
     // 4096-candidate rows, and equal to 1024), 32 items at most.
     constexpr int kBase = 16 / static_cast<int>(sizeof(Bits));
+    constexpr int kMost = sizeof(Bits) == 8 ? 16 : 32;           // per-thread candidates the registers hold
+    constexpr int kMid = 4 * kBase <= kMost ? 4 * kBase : kMost;
 #define ATK_LAUNCH_SELECT_ROW(ITEMS, MAXT)                                                         \
     select_row_kernel<T, ITEMS, MAXT><<<rows, threads_for(ITEMS), 0, a.stream>>>(                    \
         cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok)
     if (threads_for(kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(kBase, kSelectRowThreads);
     else if (threads_for(2 * kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(2 * kBase, kSelectRowThreads);
-    else if (4 * kBase <= 32 && threads_for(4 * kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(4 * kBase, kSelectRowThreads);
-    else ATK_LAUNCH_SELECT_ROW(32, 512);
+    else if (threads_for(kMid) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(kMid, kSelectRowThreads);
+    else ATK_LAUNCH_SELECT_ROW(kMost, 512);
 #undef ATK_LAUNCH_SELECT_ROW
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
@@ -472,8 +531,8 @@ int select_typed(const SelectLaunch& a) {
   if (a.workspace == nullptr || a.workspace_bytes < need_ws) return ATK_ERR_WORKSPACE;
   const long long chunks = chunks_of(a.k0);
   unsigned char* ws = static_cast<unsigned char*>(a.workspace);
-  RowState* state = reinterpret_cast<RowState*>(ws);
-  ws += align256(sizeof(RowState) * a.rows);
+  State* state = reinterpret_cast<State*>(ws);
+  ws += align256(sizeof(State) * a.rows);
   uint32_t* hist = reinterpret_cast<uint32_t*>(ws);
   const size_t hist_words = static_cast<size_t>(256) * K::kPasses * a.rows;
   uint32_t* tickets = hist + hist_words;
@@ -512,6 +571,12 @@ size_t select_workspace_bytes(int dtype, long long rows, long long k0) {
     case ATK_F32: return workspace_typed<float>(rows, k0);
     case ATK_F16: return workspace_typed<__half>(rows, k0);
     case ATK_BF16: return workspace_typed<__nv_bfloat16>(rows, k0);
+    case ATK_F64: return workspace_typed<double>(rows, k0);
+    case ATK_I32: return workspace_typed<int32_t>(rows, k0);
+    case ATK_I64: return workspace_typed<long long>(rows, k0);
+    case ATK_I16: return workspace_typed<int16_t>(rows, k0);
+    case ATK_I8: return workspace_typed<int8_t>(rows, k0);
+    case ATK_U8: return workspace_typed<uint8_t>(rows, k0);
     default: return 0;
   }
 }
@@ -568,6 +633,12 @@ int launch_select(const SelectLaunch& a, int dtype) {
     case ATK_F32: return select_typed<float>(a);
     case ATK_F16: return select_typed<__half>(a);
     case ATK_BF16: return select_typed<__nv_bfloat16>(a);
+    case ATK_F64: return select_typed<double>(a);
+    case ATK_I32: return select_typed<int32_t>(a);
+    case ATK_I64: return select_typed<long long>(a);
+    case ATK_I16: return select_typed<int16_t>(a);
+    case ATK_I8: return select_typed<int8_t>(a);
+    case ATK_U8: return select_typed<uint8_t>(a);
     default: return ATK_ERR_BAD_DTYPE;
   }
 }

@@ -126,7 +126,7 @@ __device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, cons
     const T* last = xrow + p.l_full * p.stripe_stride + c0;
 #pragma unroll
     for (int e = 0; e < V; ++e) {
-      if (c0 + e < p.rem) q[e].push_tail(VecLoad<T, 1>::load(last + e), static_cast<int>(p.l_full));
+      if (c0 + e < p.rem) q[e].push_tail(load_elem_bits<T>(last + e), static_cast<int>(p.l_full));
     }
   }
 }
@@ -229,18 +229,19 @@ sweep_kernel(const SweepParams p) {
 template <typename T, int J, bool FIRST>
 struct PlaneEntryQueue {
   using Bits = typename ElemTraits<T>::Bits;
-  float v[J];
+  using C = typename ElemTraits<T>::Compute;
+  C v[J];
   long long i[J];
-  Bits b[J];   // raw bits travel with the entries so signed zeros survive
+  Bits b[J];   // raw bits travel with the entries so NaN payloads survive
   __device__ __forceinline__ void init() {
 #pragma unroll
     for (int q = 0; q < J; ++q) {
-      v[q] = -INFINITY;
+      v[q] = ElemTraits<T>::floor();
       i[q] = FIRST ? 0x7fffffffffffffffll : -1ll;
-      b[q] = ElemTraits<T>::narrow(-INFINITY);
+      b[q] = ElemTraits<T>::narrow(ElemTraits<T>::floor());
     }
   }
-  __device__ __forceinline__ void push(float nv, long long ni, Bits nb) {
+  __device__ __forceinline__ void push(C nv, long long ni, Bits nb) {
     bool p[J + 1];
 #pragma unroll
     for (int q = 0; q < J; ++q) p[q] = (nv > v[q]) || (nv == v[q] && (FIRST ? ni < i[q] : ni > i[q]));
@@ -248,7 +249,7 @@ struct PlaneEntryQueue {
 #pragma unroll
     for (int q = 0; q < J; ++q) {
       const int up = q + 1 < J ? q + 1 : q;
-      const float tv = p[q + 1] ? v[up] : (p[q] ? nv : v[q]);
+      const C tv = p[q + 1] ? v[up] : (p[q] ? nv : v[q]);
       const long long ti = p[q + 1] ? i[up] : (p[q] ? ni : i[q]);
       const Bits tb = p[q + 1] ? b[up] : (p[q] ? nb : b[q]);
       v[q] = tv;
@@ -257,6 +258,15 @@ struct PlaneEntryQueue {
     }
   }
 };
+
+// xor-shuffle of a raw element word of any width
+template <typename B>
+__device__ __forceinline__ B shfl_xor_bits(B v, int off) {
+  if constexpr (sizeof(B) == 8)
+    return static_cast<B>(__shfl_xor_sync(0xffffffffu, static_cast<unsigned long long>(v), off));
+  else
+    return static_cast<B>(__shfl_xor_sync(0xffffffffu, static_cast<uint32_t>(v), off));
+}
 
 template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(256)
@@ -286,17 +296,17 @@ sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_
     }
   }
   for (int off = g >> 1; off >= 1; off >>= 1) {
-    float ov[J];
+    typename Tr::Compute ov[J];
     long long oi[J];
-    uint32_t ob[J];
+    Bits ob[J];
 #pragma unroll
     for (int j = 0; j < J; ++j) {
       ov[j] = __shfl_xor_sync(0xffffffffu, q.v[j], off);
       oi[j] = __shfl_xor_sync(0xffffffffu, q.i[j], off);
-      ob[j] = __shfl_xor_sync(0xffffffffu, static_cast<uint32_t>(q.b[j]), off);
+      ob[j] = shfl_xor_bits<Bits>(q.b[j], off);
     }
 #pragma unroll
-    for (int j = 0; j < J; ++j) q.push(ov[j], oi[j], static_cast<Bits>(ob[j]));
+    for (int j = 0; j < J; ++j) q.push(ov[j], oi[j], ob[j]);
   }
   if (!valid || lane != 0) return;
   Bits* vdst = out_vals + row * out_row_stride + c * J;
@@ -405,8 +415,8 @@ struct SweepLaunch {
 // uses as many planes as the scratch it is given holds.
 inline size_t sweep_workspace_bytes(int elem_size, long long rows, long long n, long long b, int j, int sm_count) {
   if (rows <= 0 || b <= 0 || n < b) return 0;
-  const int vec = 16 / elem_size;
-  const sweep_detail::SweepPlan pl = sweep_detail::plan_sweep(rows, b, n / b, (j >= 3 && elem_size == 2) ? 4 : vec, sm_count);
+  const int vec = elem_size == 1 ? 8 : 16 / elem_size;   // ElemTraits<T>::kVec by element size
+  const sweep_detail::SweepPlan pl = sweep_detail::plan_sweep(rows, b, n / b, (j >= 3 && elem_size <= 2) ? vec / 2 : vec, sm_count);
   if (pl.Z <= 1) return 0;
   const size_t k0 = static_cast<size_t>(b) * j;
   return sweep_detail::align256(static_cast<size_t>(pl.Z) * rows * k0 * elem_size) +
@@ -416,5 +426,11 @@ inline size_t sweep_workspace_bytes(int elem_size, long long rows, long long n, 
 int launch_sweep_f32(const SweepLaunch& a);
 int launch_sweep_f16(const SweepLaunch& a);
 int launch_sweep_bf16(const SweepLaunch& a);
+int launch_sweep_f64(const SweepLaunch& a);
+int launch_sweep_i32(const SweepLaunch& a);
+int launch_sweep_i64(const SweepLaunch& a);
+int launch_sweep_i16(const SweepLaunch& a);
+int launch_sweep_i8(const SweepLaunch& a);
+int launch_sweep_u8(const SweepLaunch& a);
 
 }  // namespace atk

@@ -95,7 +95,7 @@ int launch_stage1(const SweepLaunch& a) {
 // vector path); everything else uses (float, int) pairs.
 template <typename T, int J, int V, bool FIRST>
 int launch_by_queue(const SweepLaunch& a) {
-  if constexpr (sizeof(T) == 2) {
+  if constexpr (ElemTraits<T>::kHalfFloat) {
     if (a.n / a.b + 1 <= 65536) {
       return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4)>(a);
     }
@@ -119,10 +119,11 @@ int launch_by_j(const SweepLaunch& a) {
 }
 
 // Columns per thread.  A vector of V elements is loaded per stripe, so it must
-// be aligned and lie inside one stripe.  16-byte vectors by default; queues of
-// three or four entries take half as many columns per thread (8-byte loads for
-// the 16-bit types), which halves their register footprint and doubles the
-// number of threads that hide each other's latency.
+// be aligned and lie inside one stripe.  The type's preferred vector (16 bytes;
+// 8 bytes for 8-bit elements) by default; for elements of 16 bits or fewer,
+// queues of three or four entries take half as many columns per thread, which
+// halves their register footprint and doubles the number of threads that hide
+// each other's latency.
 template <typename T>
 int launch_sweep(const SweepLaunch& a) {
   constexpr int s = static_cast<int>(sizeof(T));
@@ -133,10 +134,11 @@ int launch_sweep(const SweepLaunch& a) {
     return (reinterpret_cast<uintptr_t>(a.x) % bytes == 0) && ((a.row_stride * s) % bytes == 0) &&
            ((a.stripe_stride * s) % bytes == 0) && (a.b % v == 0);
   };
-  if constexpr (sizeof(T) == 2) {
-    if (a.j >= 3 && fits(4)) return launch_by_j<T, 4>(a);
+  if constexpr (sizeof(T) <= 2) {
+    constexpr int kHalfVec = kVec / 2;
+    if (a.j >= 3 && fits(kHalfVec)) return launch_by_j<T, kHalfVec>(a);
     if (fits(kVec)) return launch_by_j<T, kVec>(a);
-    if (fits(4)) return launch_by_j<T, 4>(a);
+    if (fits(kHalfVec)) return launch_by_j<T, kHalfVec>(a);
     return launch_by_j<T, 1>(a);
   } else {
     return fits(kVec) ? launch_by_j<T, kVec>(a) : launch_by_j<T, 1>(a);

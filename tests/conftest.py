@@ -31,3 +31,15 @@ def golden():
     data = np.load(ROOT / "tests" / "golden" / "reference_cpu_vectors.npz")
     meta = json.loads(bytes(data["meta"]).decode())
     return data, meta
+
+
+@pytest.fixture(scope="session")
+def golden_all_dtypes():
+    """Reference CPU outputs for float64 and the integer element types."""
+    import json
+
+    import numpy as np
+
+    data = np.load(ROOT / "tests" / "golden" / "reference_cpu_vectors_all_dtypes.npz")
+    meta = json.loads(bytes(data["meta"]).decode())
+    return data, meta

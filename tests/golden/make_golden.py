@@ -15,6 +15,11 @@ Stored per case (prefix ``c<i>_``): ``x`` (float32; 16-bit inputs are stored
 widened, which is exact), ``values`` and ``indices`` each sorted ascending along
 the last axis (order inside the reference's output is not part of its
 contract), and a JSON header with the call arguments.
+
+A second file, ``reference_cpu_vectors_all_dtypes.npz``, holds the same kind of
+cases for the other element types of the reference's native dispatch (float64,
+int64, int32, int16, int8, uint8), with ``x`` and ``values`` stored in the
+element type itself.
 """
 
 from __future__ import annotations
@@ -30,6 +35,10 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "reference_cpu_vectors.npz"
+OUT_WIDE = HERE / "reference_cpu_vectors_all_dtypes.npz"
+
+WIDE_DTYPES = {"float64": torch.float64, "int64": torch.int64, "int32": torch.int32,
+               "int16": torch.int16, "int8": torch.int8, "uint8": torch.uint8}
 
 DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
 
@@ -57,6 +66,67 @@ def make_input(rows, n, dtype, dist, seed):
     else:
         x = torch.linspace(0, 1, n)[None, :] + 0.01 * torch.randn(rows, n, generator=g)
     return x.to(DTYPES[dtype])
+
+
+def make_wide_input(rows, n, dtype, seed):
+    """Seeded input of one of the wider dispatch types: the full value range,
+    with the type's extreme values planted so that the sentinel handling shows."""
+    g = torch.Generator().manual_seed(seed)
+    t = WIDE_DTYPES[dtype]
+    if t == torch.float64:
+        x = torch.randn(rows, n, generator=g, dtype=torch.float64) * 1e100
+    else:
+        info = torch.iinfo(t)
+        if t == torch.int64:
+            hi = torch.randint(-2**31, 2**31, (rows, n), generator=g, dtype=torch.int64)
+            lo = torch.randint(0, 2**32, (rows, n), generator=g, dtype=torch.int64)
+            x = hi * 2**32 + lo
+        else:
+            x = torch.randint(info.min, info.max + 1, (rows, n), generator=g, dtype=torch.int64).to(t)
+        x[:, 3] = info.min
+        x[:, n // 2] = info.max
+        x[:, n - 1] = info.min
+    return x
+
+
+def wide_cases():
+    out = []
+    for dtype in WIDE_DTYPES:
+        for interleaved in (True, False):
+            for j in (1, 2, 3, 4):
+                out.append((2, 1001, 12 * j, j, 1, interleaved, dtype))     # b does not divide n
+            out.append((2, 1000, 16, 2, 4, interleaved, dtype))             # stage 2
+            out.append((1, 300, 296, 4, 1, interleaved, dtype))             # buckets of 4 or 5 elements
+    return out
+
+
+def write_wide(bucketed_torch_topk, topk_torch) -> None:
+    store: dict[str, np.ndarray] = {}
+    meta = []
+    for i, (rows, n, k, j, k_mult, interleaved, dtype) in enumerate(wide_cases()):
+        x = make_wide_input(rows, n, dtype, seed=3000 + i)
+        v, idx = bucketed_torch_topk(x, k=k, dim=-1, k_mult=k_mult, k_per_bucket=j, interleaved=interleaved)
+        store[f"c{i}_x"] = x.numpy()
+        store[f"c{i}_values"] = v.sort(dim=-1).values.numpy()
+        store[f"c{i}_indices"] = idx.sort(dim=-1).values.numpy()
+        meta.append(dict(kind="bucketed_torch_topk", rows=rows, n=n, k=k, j=j, k_mult=k_mult,
+                         interleaved=interleaved, dtype=dtype))
+    base = len(meta)
+    t = 0
+    for dtype in WIDE_DTYPES:
+        for rows, n, k in ((2, 1000, 64), (2, 37, 5)):
+            for interleaved in (True, False):
+                i = base + t
+                t += 1
+                x = make_wide_input(rows, n, dtype, seed=4000 + i)
+                v, idx = topk_torch(x, k=k, dim=-1, interleaved=interleaved)
+                store[f"c{i}_x"] = x.numpy()
+                store[f"c{i}_values"] = v.numpy()
+                store[f"c{i}_indices"] = idx.numpy()
+                meta.append(dict(kind="topk_torch", rows=rows, n=n, k=k, interleaved=interleaved, dtype=dtype))
+    store["meta"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
+    np.savez_compressed(OUT_WIDE, **store)
+    print(f"wrote {OUT_WIDE} ({OUT_WIDE.stat().st_size} bytes, {len(meta)} cases)")
 
 
 def main() -> int:
@@ -98,6 +168,7 @@ def main() -> int:
     store["meta"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
     np.savez_compressed(OUT, **store)
     print(f"wrote {OUT} ({OUT.stat().st_size} bytes, {len(meta)} cases)")
+    write_wide(bucketed_torch_topk, topk_torch)
     return 0
 
 

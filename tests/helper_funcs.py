@@ -12,7 +12,22 @@ def assert_close_up_to_permutation(x: Tensor, y: Tensor, dim: int = -1) -> None:
 
 
 def widen(t: Tensor) -> Tensor:
-    return t.detach().to("cpu").to(torch.float32)
+    """CPU copy in a type that holds every value of `t` exactly: float32 for the
+    float types of 32 bits or fewer, float64 for float64, int64 for integers."""
+    if t.dtype == torch.float64:
+        wide = torch.float64
+    else:
+        wide = torch.float32 if t.dtype.is_floating_point else torch.int64
+    return t.detach().to("cpu").to(wide)
+
+
+def _bits(t: Tensor) -> Tensor:
+    """Integer view of a widened tensor, so that comparisons are bit-exact."""
+    if t.dtype == torch.float32:
+        return t.view(torch.int32)
+    if t.dtype == torch.float64:
+        return t.view(torch.int64)
+    return t
 
 
 def assert_pairs_identical(values: Tensor, indices: Tensor, ref_values: Tensor, ref_indices: Tensor) -> None:
@@ -22,7 +37,7 @@ def assert_pairs_identical(values: Tensor, indices: Tensor, ref_values: Tensor, 
 
     v, i = canonical(values, indices)
     rv, ri = canonical(ref_values, ref_indices)
-    assert torch.equal(v.view(torch.int32), rv.view(torch.int32)), "selected values differ"
+    assert torch.equal(_bits(v), _bits(rv)), "selected values differ"
     assert torch.equal(i, ri), "selected indices differ"
 
 

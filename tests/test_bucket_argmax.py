@@ -83,7 +83,10 @@ def test_config_c1_shape_recall():
     assert 0.55 < r < 0.72      # analytic value for k_b = 1, b = k is about 0.63
 
 
-def test_integer_input_is_rejected_clearly():
+def test_integer_input_first_maximum_wins():
+    # ten distinct values over 64 positions: every bucket has tied maxima
     x = torch.randint(0, 10, (2, 64), device="cuda")
-    with pytest.raises(NotImplementedError, match="not supported"):
-        topk_torch(x, k=4, dim=1, interleaved=True)
+    v, i = topk_torch(x, k=4, dim=1, interleaved=True)
+    ov, oi = oracle.bucketed_argmax(x.cpu(), 4, True)
+    assert v.dtype == torch.int64
+    assert torch.equal(v.cpu(), ov) and torch.equal(i.cpu(), oi)

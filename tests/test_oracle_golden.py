@@ -136,6 +136,37 @@ def test_reference_fixtures(golden):
                 assert torch.equal(idx, ei), m
 
 
+def _rows_have_ties(x):
+    s = x.reshape(-1, x.shape[-1]).sort(dim=-1).values
+    return bool((s[:, 1:] == s[:, :-1]).any())
+
+
+def test_reference_fixtures_all_dtypes(golden_all_dtypes):
+    # float64 and the integer element types of the reference's native dispatch,
+    # against the reference's Python (CPU) path run on the same inputs.
+    data, meta = golden_all_dtypes
+    assert len(meta) >= 90
+    seen = set()
+    for i, m in enumerate(meta):
+        x = torch.from_numpy(data[f"c{i}_x"])
+        assert str(x.dtype) == "torch." + m["dtype"]
+        seen.add(m["dtype"])
+        ev = torch.from_numpy(data[f"c{i}_values"])
+        ei = torch.from_numpy(data[f"c{i}_indices"])
+        if m["kind"] == "bucketed_torch_topk":
+            v, idx = oracle.topk(x, m["k"], j=m["j"], k_mult=m["k_mult"], interleaved=m["interleaved"])
+            assert v.dtype == x.dtype
+            assert torch.equal(v.sort(dim=-1).values, ev), m
+            assert torch.equal(x.gather(-1, idx), v), m
+            if not _rows_have_ties(x):        # tie-free rows pin the indices too
+                assert torch.equal(idx.sort(dim=-1).values, ei), m
+        else:
+            v, idx = oracle.bucketed_argmax(x, m["k"], interleaved=m["interleaved"])
+            assert torch.equal(v, ev), m
+            assert torch.equal(idx, ei), m    # first maximum wins in both
+    assert seen == {"float64", "int64", "int32", "int16", "int8", "uint8"}
+
+
 def test_tie_rule_last_wins():
     # Reference insertion rule (priority_queue_approx_topk.cu:58-79): of equal
     # values the later position survives; slots ascend inside a bucket.
