@@ -96,7 +96,9 @@ int launch_stage1(const SweepLaunch& a) {
 template <typename T, int J, int V, bool FIRST>
 int launch_by_queue(const SweepLaunch& a) {
   if constexpr (ElemTraits<T>::kHalfFloat) {
-    if (a.n / a.b + 1 <= 65536) {
+    // stripes are numbered 0 .. n/b (the last one only when b does not divide n)
+    const long long stripes = a.n / a.b + (a.n % a.b != 0 ? 1 : 0);
+    if (stripes <= 65536) {
       return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4)>(a);
     }
   }

@@ -72,6 +72,21 @@ def test_stage1_tie_rule(dtype, j, interleaved):
         check_stage1_exact(make(rows, n, dtype, 50 + seed, "ties"), k0, j, interleaved)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("j", [1, 2, 4])
+def test_stage1_sixteen_bit_stripe_numbers_at_the_limit(dtype, j):
+    # The packed queues of the 16-bit types hold the stripe number in 16 bits:
+    # exactly 65536 stripes (with and without a ragged last one) still fit, one
+    # more does not and takes the wide queues.  Tie-heavy data makes the last
+    # stripes win, so a wrapped stripe number would show.
+    b = 8
+    for n in (65536 * b, 65536 * b - 3, 65536 * b + 3):
+        for dist in ("ties", "randn"):
+            check_stage1_exact(make(3, n, dtype, 60 + j, dist), b * j, j, True)
+    # many rows: no stripe split inside the block, every thread walks all 65536 stripes
+    check_stage1_exact(make(300, 65536 * 4, dtype, 61, "ties"), 4 * j, j, True)
+
+
 def test_stage1_all_equal_row():
     x = torch.ones(2, 4096, device="cuda")
     v, i = check_stage1_exact(x, 64, 2, True)
