@@ -90,18 +90,87 @@ template <typename K> __device__ __forceinline__ int digit_shift(int pass) {
   return static_cast<int>(sizeof(typename K::Key)) * 8 - 8 - 8 * pass;
 }
 
+// ITEMS consecutive raw candidates of one thread, loaded with the widest
+// vector loads their size allows (16 bytes at a time).
+template <typename B, int ITEMS>
+struct alignas((ITEMS * sizeof(B)) % 16 == 0 ? 16 : 8) ItemPack {
+  B v[ITEMS];
+};
+static_assert(sizeof(ItemPack<uint16_t, 8>) == 16 && sizeof(ItemPack<uint8_t, 8>) == 8, "pack layout");
+
+// Loads slots [first, first + ITEMS) of a row into raw[]; slots at or past
+// `end` read as zero.  `vec` says the row is aligned for vector loads.
+template <typename B, int ITEMS>
+__device__ __forceinline__ void load_items(const B* __restrict__ row, long long first, long long end, int vec,
+                                           B (&raw)[ITEMS]) {
+  if (vec && first + ITEMS <= end) {
+    const ItemPack<B, ITEMS> pk = *reinterpret_cast<const ItemPack<B, ITEMS>*>(row + first);
+#pragma unroll
+    for (int u = 0; u < ITEMS; ++u) raw[u] = pk.v[u];
+  } else {
+#pragma unroll
+    for (int u = 0; u < ITEMS; ++u) raw[u] = first + u < end ? row[first + u] : B(0);
+  }
+}
+
+template <typename KEY>
+struct RowState {
+  KEY prefix, mask;
+  uint32_t need, pad;
+};
+
+// ---- write-out through shared memory ------------------------------------------
+// Winners leave a thread at scattered output positions (a thread owns a run of
+// candidate slots, only some of which win), which costs one memory sector per
+// element when stored directly.  Instead the block collects a tile of
+// kStageTile consecutive output positions in shared memory and then copies the
+// tile out with fully coalesced (16-byte where aligned) stores.
+constexpr int kStageTile = 2048;
+// Staging buffer of a block that writes at most `k` entries: the positions of
+// one tile, then (16-byte aligned) its values.
+__host__ __device__ inline int stage_tile(long long k) { return k < kStageTile ? static_cast<int>(k) : kStageTile; }
+__host__ __device__ inline size_t stage_val_offset(int tile) { return (static_cast<size_t>(tile) * 8 + 15) & ~static_cast<size_t>(15); }
+template <typename B> size_t stage_bytes(long long k) {
+  return stage_val_offset(stage_tile(k)) + static_cast<size_t>(stage_tile(k)) * sizeof(B);
+}
+
+// Copies staged entries [0, cnt) to out_vals/out_idx[dst ...]; all threads of
+// the block take part.  `vec`: both destinations are 16-byte aligned at dst.
+template <typename B>
+__device__ __forceinline__ void stage_copy_out(const long long* sidx, const B* sval, int cnt, B* __restrict__ ov,
+                                               long long* __restrict__ oi, int tid, int nthr, bool vec) {
+  if (vec) {
+    const int ni = cnt / 2;                                   // 16-byte pieces of positions
+    for (int q = tid; q < ni; q += nthr) reinterpret_cast<uint4*>(oi)[q] = reinterpret_cast<const uint4*>(sidx)[q];
+    for (int p = 2 * ni + tid; p < cnt; p += nthr) oi[p] = sidx[p];
+    constexpr int kPer = 16 / static_cast<int>(sizeof(B));
+    const int nv = cnt / kPer;
+    for (int q = tid; q < nv; q += nthr) reinterpret_cast<uint4*>(ov)[q] = reinterpret_cast<const uint4*>(sval)[q];
+    for (int p = nv * kPer + tid; p < cnt; p += nthr) ov[p] = sval[p];
+  } else {
+    for (int p = tid; p < cnt; p += nthr) {
+      oi[p] = sidx[p];
+      ov[p] = sval[p];
+    }
+  }
+}
+
 // ------------------------------------------------------------------ small path
 // One block per row.  Thread t owns the ITEMS consecutive candidate slots
 // [t*ITEMS, (t+1)*ITEMS): keys stay in registers through the radix passes, and
 // because slots are blocked per thread one block-wide scan of the per-thread
 // (greater, equal) counts gives every winner its output position in slot order.
-template <typename T, int ITEMS, int MAXT>
+// FULL: the row has exactly blockDim.x * ITEMS candidates and is aligned for
+// vector loads, so no slot needs a bounds test (the common case: candidate
+// counts are powers of two).
+template <typename T, int ITEMS, int MAXT, bool FULL>
 __global__ void __launch_bounds__(MAXT)
 select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                   const long long* __restrict__ cand_idx, int k0, long long cand_row_stride, int k,
                   typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
                   long long out_row_stride, int vec_ok) {
   using K = KeyOf<T>;
+  using Key = typename K::Key;
   using Bits = typename ElemTraits<T>::Bits;
   __shared__ uint32_t hist[256];
   __shared__ uint32_t misc[2];
@@ -115,49 +184,41 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   const Bits* vrow = cand_vals + row * cand_row_stride;
   const long long* irow = cand_idx + row * cand_row_stride;
   const int slot0 = tid * ITEMS;
-
-  using Key = typename K::Key;
-  __align__(16) Bits raw[ITEMS];
-  Key key[ITEMS];
-  constexpr int kRawBytes = ITEMS * static_cast<int>(sizeof(Bits));
-  if (vec_ok && kRawBytes % 16 == 0 && slot0 + ITEMS <= k0) {
-#pragma unroll
-    for (int i = 0; i < kRawBytes / 16; ++i)
-      reinterpret_cast<uint4*>(raw)[i] = reinterpret_cast<const uint4*>(vrow + slot0)[i];
-  } else {
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) raw[i] = slot0 + i < k0 ? vrow[slot0 + i] : Bits(0);
+  // number of this thread's slots that exist
+  int valid = ITEMS;
+  if (!FULL) {
+    valid = k0 - slot0;
+    valid = valid < 0 ? 0 : (valid > ITEMS ? ITEMS : valid);
   }
+  const bool vec = FULL || (vec_ok && valid == ITEMS);
+
+  Bits raw[ITEMS];
+  load_items<Bits, ITEMS>(vrow, slot0, slot0 + valid, vec, raw);
   // The positions travel with their candidates.  For short per-thread runs
   // they are fetched up front with the values (contiguous, 16-byte loads), so
   // the write-out at the end does not wait on a chain of dependent gathers.
   constexpr bool kPrefetchIdx = ITEMS <= 8;
-  __align__(16) long long pidx[kPrefetchIdx ? ITEMS : 1];
-  if (kPrefetchIdx) {
-    if (vec_ok && ITEMS % 2 == 0 && slot0 + ITEMS <= k0) {
+  long long pidx[kPrefetchIdx ? ITEMS : 1];
+  if constexpr (kPrefetchIdx) load_items<long long, ITEMS>(irow, slot0, slot0 + valid, vec, pidx);
+  Key key[ITEMS];
 #pragma unroll
-      for (int i = 0; i < ITEMS / 2; ++i)
-        reinterpret_cast<uint4*>(pidx)[i] = reinterpret_cast<const uint4*>(irow + slot0)[i];
-    } else {
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) pidx[i] = slot0 + i < k0 ? irow[slot0 + i] : 0;
-    }
-  }
-  // Slots past the end get key 0; every use below is guarded by the slot bound.
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) key[i] = slot0 + i < k0 ? K::key(raw[i]) : Key(0);
+  for (int i = 0; i < ITEMS; ++i) key[i] = K::key(raw[i]);
 
   Key prefix = 0, mask = 0;
   uint32_t need = static_cast<uint32_t>(k);
-#pragma unroll 1
+  // up to four passes are unrolled so that shifts are immediates and the first
+  // pass has no prefix test; the eight passes of 64-bit keys stay a loop
+#pragma unroll(K::kPasses <= 4 ? K::kPasses : 1)
   for (int pass = 0; pass < K::kPasses; ++pass) {
     const int shift = digit_shift<K>(pass);
     for (int i = tid; i < 256; i += nthr) hist[i] = 0;
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i)
-      if (slot0 + i < k0 && (key[i] & mask) == prefix)
-        atomicAdd(&hist[static_cast<uint32_t>(key[i] >> shift) & 255u], 1u);
+    for (int i = 0; i < ITEMS; ++i) {
+      bool in = FULL || i < valid;
+      if (pass > 0) in = in && (key[i] & mask) == prefix;
+      if (in) atomicAdd(&hist[static_cast<uint32_t>(key[i] >> shift) & 255u], 1u);
+    }
     __syncthreads();
     if (tid < 32) pick_digit(hist, need, tid, &misc[0], &misc[1]);
     __syncthreads();
@@ -170,7 +231,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   uint32_t mine = 0;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const bool in = slot0 + i < k0;
+    const bool in = FULL || i < valid;
     mine += (in && key[i] > prefix) ? 1u : 0u;
     mine += (in && key[i] == prefix) ? 0x10000u : 0u;
   }
@@ -200,13 +261,12 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   const uint32_t n_gt = static_cast<uint32_t>(k) - need;
   Bits* ovrow = out_vals + row * out_row_stride;
   long long* oirow = out_idx + row * out_row_stride;
-  // output position of every item first (no memory traffic), then the gathers
-  // of the winners' positions as independent loads, then the stores
+  // output position of every item (-1: not selected)
   int pos[ITEMS];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     pos[i] = -1;
-    if (slot0 + i < k0) {
+    if (FULL || i < valid) {
       if (key[i] > prefix) {
         pos[i] = static_cast<int>(gt_rank++);
       } else if (key[i] == prefix) {
@@ -215,28 +275,31 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
       }
     }
   }
-  long long widx[ITEMS];
+  // Winners go to shared memory at their output position, one tile of output
+  // positions at a time, and leave it with coalesced stores.
+  extern __shared__ __align__(16) unsigned char stage_smem[];
+  long long* sidx = reinterpret_cast<long long*>(stage_smem);
+  const int tile = stage_tile(k);
+  Bits* sval = reinterpret_cast<Bits*>(stage_smem + stage_val_offset(tile));
+  const bool vec_out = (reinterpret_cast<uintptr_t>(ovrow) % 16 == 0) && (reinterpret_cast<uintptr_t>(oirow) % 16 == 0);
+  for (int base = 0; base < k; base += tile) {
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    widx[i] = 0;
-    if (pos[i] >= 0) widx[i] = kPrefetchIdx ? pidx[kPrefetchIdx ? i : 0] : irow[slot0 + i];
-  }
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    if (pos[i] >= 0) {
-      ovrow[pos[i]] = raw[i];
-      oirow[pos[i]] = widx[i];
+    for (int i = 0; i < ITEMS; ++i) {
+      // pos - base in [0, tile) as one unsigned compare; -1 never passes
+      const uint32_t rel = static_cast<uint32_t>(pos[i] - base);
+      if (pos[i] >= 0 && rel < static_cast<uint32_t>(tile)) {
+        sval[rel] = raw[i];
+        sidx[rel] = kPrefetchIdx ? pidx[kPrefetchIdx ? i : 0] : irow[slot0 + i];
+      }
     }
+    __syncthreads();
+    const int cnt = k - base < tile ? k - base : tile;
+    stage_copy_out<Bits>(sidx, sval, cnt, ovrow + base, oirow + base, tid, nthr, vec_out);
+    if (base + tile < k) __syncthreads();
   }
 }
 
 // ------------------------------------------------------------------ large path
-template <typename KEY>
-struct RowState {
-  KEY prefix, mask;
-  uint32_t need, pad;
-};
-
 // One radix pass.  Every block histograms its chunk into the row's global
 // histogram; the block that finishes last for a row (a ticket counter, no
 // waiting) then picks the digit and advances the row's (prefix, mask, need).
@@ -247,7 +310,8 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
                    long long cand_row_stride, int pass, long long k,
                    RowState<typename KeyOf<T>::Key>* __restrict__ state,
                    uint32_t* __restrict__ hist /* [rows][passes][256] */,
-                   uint32_t* __restrict__ tickets /* [rows][passes + 1] */, int cpb /* chunks per block */) {
+                   uint32_t* __restrict__ tickets /* [rows][passes + 1] */, int cpb /* chunks per block */,
+                   int vec /* rows are aligned for vector loads */) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
   __shared__ uint32_t sh[256];
@@ -272,19 +336,26 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
     if (begin >= k0) break;
     long long end = begin + kLargeThreads * ITEMS;
     if (end > k0) end = k0;
-    // all loads of the chunk are issued before the first histogram update
+    // thread t takes the ITEMS consecutive candidates begin + t*ITEMS ...
+    const long long first = begin + static_cast<long long>(threadIdx.x) * ITEMS;
     typename ElemTraits<T>::Bits raw[ITEMS];
+    load_items<typename ElemTraits<T>::Bits, ITEMS>(vrow, first, end, vec, raw);
+    // Neighbouring candidates often share a digit (always in the first passes,
+    // where few digits occur at all): runs of equal digits become one update.
+    uint32_t run_bin = 0xffffffffu, run_len = 0;
 #pragma unroll
     for (int u = 0; u < ITEMS; ++u) {
-      const long long i = begin + u * kLargeThreads + threadIdx.x;
-      raw[u] = i < end ? vrow[i] : typename ElemTraits<T>::Bits(0);
-    }
-#pragma unroll
-    for (int u = 0; u < ITEMS; ++u) {
-      const long long i = begin + u * kLargeThreads + threadIdx.x;
       const Key key = K::key(raw[u]);
-      if (i < end && (key & st.mask) == st.prefix) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & 255u], 1u);
+      const bool in = first + u < end && (key & st.mask) == st.prefix;
+      const uint32_t bin = in ? (static_cast<uint32_t>(key >> shift) & 255u) : 0xffffffffu;
+      if (bin != run_bin) {
+        if (run_len) atomicAdd(&sh[run_bin], run_len);
+        run_bin = bin;
+        run_len = 0;
+      }
+      run_len += in ? 1u : 0u;
     }
+    if (run_len) atomicAdd(&sh[run_bin], run_len);
   }
   __syncthreads();
   uint32_t* gh = hist + (row * K::kPasses + pass) * 256;
@@ -315,7 +386,7 @@ __global__ void __launch_bounds__(kLargeThreads)
 select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
                     long long cand_row_stride, const RowState<typename KeyOf<T>::Key>* __restrict__ state,
                     uint2* __restrict__ counts /* [rows][chunks] */, uint32_t* __restrict__ tickets, int chunks,
-                    int cpb /* chunks per block */) {
+                    int cpb /* chunks per block */, int vec) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
   __shared__ uint32_t s_gt, s_eq;
@@ -335,14 +406,15 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
     long long end = begin + kLargeThreads * ITEMS;
     if (end > k0) end = k0;
     uint32_t gt = 0, eq = 0;
+    const long long first = begin + static_cast<long long>(threadIdx.x) * ITEMS;
+    typename ElemTraits<T>::Bits raw[ITEMS];
+    load_items<typename ElemTraits<T>::Bits, ITEMS>(vrow, first, end, vec, raw);
 #pragma unroll
     for (int u = 0; u < ITEMS; ++u) {
-      const long long i = begin + u * kLargeThreads + threadIdx.x;
-      if (i < end) {
-        const Key key = K::key(vrow[i]);
-        gt += key > thr;
-        eq += key == thr;
-      }
+      const Key key = K::key(raw[u]);
+      const bool in = first + u < end;
+      gt += (in && key > thr) ? 1u : 0u;
+      eq += (in && key == thr) ? 1u : 0u;
     }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) {
@@ -394,16 +466,19 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                     const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride,
                     long long k, const RowState<typename KeyOf<T>::Key>* __restrict__ state,
                     const uint2* __restrict__ bases, typename ElemTraits<T>::Bits* __restrict__ out_vals,
-                    long long* __restrict__ out_idx, long long out_row_stride) {
+                    long long* __restrict__ out_idx, long long out_row_stride, int vec) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
   __shared__ uint32_t wsum[32];
+  __shared__ uint32_t block_total;
+  __shared__ __align__(16) long long sidx[kLargeThreads * ITEMS];
+  __shared__ __align__(16) typename ElemTraits<T>::Bits sval[kLargeThreads * ITEMS];
   const long long row = blockIdx.y;
   const Key thr = state[row].prefix;
   const uint32_t need = state[row].need;
   const long long n_gt = k - need;
   const uint2 b = bases[row * gridDim.x + blockIdx.x];
-  uint32_t gt_base = b.x, eq_base = b.y;
+  const uint32_t gt_base = b.x, eq_base = b.y;
   const long long begin = static_cast<long long>(blockIdx.x) * (kLargeThreads * ITEMS);
   long long end = begin + kLargeThreads * ITEMS;
   if (end > k0) end = k0;
@@ -419,12 +494,8 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   typename ElemTraits<T>::Bits raws[ITEMS];
   long long idxs[ITEMS];
   Key keys[ITEMS];
-#pragma unroll
-  for (int u = 0; u < ITEMS; ++u) {
-    const long long i = slot0 + u;
-    raws[u] = i < end ? vrow[i] : typename ElemTraits<T>::Bits(0);
-    idxs[u] = i < end ? irow[i] : 0;
-  }
+  load_items<typename ElemTraits<T>::Bits, ITEMS>(vrow, slot0, end, vec, raws);
+  load_items<long long, ITEMS>(irow, slot0, end, vec, idxs);
   uint32_t mine = 0;
 #pragma unroll
   for (int u = 0; u < ITEMS; ++u) {
@@ -450,26 +521,44 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
       if (lane >= off) wi += nb;
     }
     wsum[lane] = wi - w;
+    if (lane == 31) block_total = wi;
   }
   __syncthreads();
   const uint32_t excl = wsum[warp] + incl - mine;
-  uint32_t gt_rank = gt_base + (excl & 0xffffu);
-  uint32_t eq_rank = eq_base + (excl >> 16);
+  // The block's winners occupy two contiguous output ranges: those above the
+  // threshold at gt_base ..., the selected ones equal to it at n_gt + eq_base ....
+  // They are collected in shared memory in that order and copied out coalesced.
+  const uint32_t tot_gt = block_total & 0xffffu;
+  const uint32_t tot_eq = block_total >> 16;
+  uint32_t sel_eq = need > eq_base ? need - eq_base : 0u;   // equal candidates this block may still take
+  if (sel_eq > tot_eq) sel_eq = tot_eq;
+  uint32_t lgt = excl & 0xffffu;
+  uint32_t leq = excl >> 16;
 #pragma unroll
   for (int u = 0; u < ITEMS; ++u) {
-    if (slot0 + u >= end) break;
-    long long pos = -1;
-    if (keys[u] > thr) {
-      pos = gt_rank++;
-    } else if (keys[u] == thr) {
-      if (eq_rank < need) pos = n_gt + eq_rank;
-      ++eq_rank;
-    }
-    if (pos >= 0) {
-      ovrow[pos] = raws[u];
-      oirow[pos] = idxs[u];
+    if (slot0 + u < end) {
+      int at = -1;
+      if (keys[u] > thr) {
+        at = static_cast<int>(lgt++);
+      } else if (keys[u] == thr) {
+        if (leq < sel_eq) at = static_cast<int>(tot_gt + leq);
+        ++leq;
+      }
+      if (at >= 0) {
+        sval[at] = raws[u];
+        sidx[at] = idxs[u];
+      }
     }
   }
+  __syncthreads();
+  auto* gv = ovrow + gt_base;
+  long long* gi = oirow + gt_base;
+  const bool vec_gt = (reinterpret_cast<uintptr_t>(gv) % 16 == 0) && (reinterpret_cast<uintptr_t>(gi) % 16 == 0);
+  stage_copy_out<typename ElemTraits<T>::Bits>(sidx, sval, static_cast<int>(tot_gt), gv, gi, threadIdx.x,
+                                               kLargeThreads, vec_gt);
+  stage_copy_out<typename ElemTraits<T>::Bits>(sidx + tot_gt, sval + tot_gt, static_cast<int>(sel_eq),
+                                               ovrow + n_gt + eq_base, oirow + n_gt + eq_base, threadIdx.x,
+                                               kLargeThreads, false);
 }
 
 inline long long chunks_of(long long k0) { return (k0 + kChunk - 1) / kChunk; }
@@ -514,9 +603,15 @@ int select_typed(const SelectLaunch& a) {
     constexpr int kBase = 16 / static_cast<int>(sizeof(Bits));
     constexpr int kMost = sizeof(Bits) == 8 ? 16 : 32;           // per-thread candidates the registers hold
     constexpr int kMid = 4 * kBase <= kMost ? 4 * kBase : kMost;
-#define ATK_LAUNCH_SELECT_ROW(ITEMS, MAXT)                                                         \
-    select_row_kernel<T, ITEMS, MAXT><<<rows, threads_for(ITEMS), 0, a.stream>>>(                    \
-        cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok)
+#define ATK_LAUNCH_SELECT_ROW(ITEMS, MAXT)                                                             \
+    do {                                                                                                 \
+      if (vec_ok && threads_for(ITEMS) * (ITEMS) == k0)                                                  \
+        select_row_kernel<T, ITEMS, MAXT, true><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
+            cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);          \
+      else                                                                                               \
+        select_row_kernel<T, ITEMS, MAXT, false><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
+            cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);          \
+    } while (0)
     if (threads_for(kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(kBase, kSelectRowThreads);
     else if (threads_for(2 * kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(2 * kBase, kSelectRowThreads);
     else if (threads_for(kMid) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(kMid, kSelectRowThreads);
@@ -553,13 +648,16 @@ int select_typed(const SelectLaunch& a) {
   const long long groups = (chunks + cpb - 1) / cpb;
   const dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(a.rows));
   const dim3 grid_g(static_cast<unsigned>(groups), static_cast<unsigned>(a.rows));
+  // vector loads need 16-byte aligned rows of values and of positions
+  const int vec = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * sizeof(Bits)) % 16 == 0) &&
+                  (reinterpret_cast<uintptr_t>(a.cand_idx) % 16 == 0) && ((a.cand_row_stride * 8) % 16 == 0);
   for (int pass = 0; pass < K::kPasses; ++pass)
     select_hist_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
-        cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb));
+        cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
   select_count_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
-      cv, a.k0, a.cand_row_stride, state, counts, tickets, static_cast<int>(chunks), static_cast<int>(cpb));
+      cv, a.k0, a.cand_row_stride, state, counts, tickets, static_cast<int>(chunks), static_cast<int>(cpb), vec);
   select_write_kernel<T, kItems><<<grid, kLargeThreads, 0, a.stream>>>(
-      cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, counts, ov, a.out_idx, a.out_row_stride);
+      cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, counts, ov, a.out_idx, a.out_row_stride, vec);
   note_launch(K::kPasses + 2);
   return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
 }
