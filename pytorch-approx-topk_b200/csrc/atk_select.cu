@@ -26,7 +26,12 @@ constexpr int kLargeThreads = 256;
 #ifndef ATK_SELECT_ROW_THREADS
 #define ATK_SELECT_ROW_THREADS 512
 #endif
-constexpr int kSelectRowThreads = ATK_SELECT_ROW_THREADS;  // preferred block width of the one-block-per-row select
+constexpr int kSelectRowThreads = ATK_SELECT_ROW_THREADS;
+// Resident blocks the compiler must allow for in the variants with at most eight
+// candidates per thread (a build knob for measurements).
+#ifndef ATK_SELECT_ROW_MINBLOCKS
+#define ATK_SELECT_ROW_MINBLOCKS 1
+#endif  // preferred block width of the one-block-per-row select
 
 // Order-preserving unsigned image of an element ("key"), its width, and the
 // number of 8-bit radix passes, most significant digit first.  Keys of the
@@ -36,16 +41,20 @@ template <typename T> struct KeyOf;
 template <> struct KeyOf<float> {
   using Key = uint32_t;
   static constexpr int kPasses = 4;
+  // negative: all bits flipped; positive: sign bit set (shift, then one logic op)
   static __device__ __forceinline__ Key key(uint32_t u) {
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    const uint32_t s = static_cast<uint32_t>(static_cast<int32_t>(u) >> 31);
+    return u ^ (s | 0x80000000u);
   }
 };
 template <> struct KeyOf<__half> {
   using Key = uint32_t;
   static constexpr int kPasses = 2;
+  // the same on the 16 bits moved to the top half; the low half stays zero
   static __device__ __forceinline__ Key key(uint16_t h) {
-    const uint32_t u = h;
-    return ((u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u)) << 16;
+    const uint32_t x = static_cast<uint32_t>(h) << 16;
+    const uint32_t s = static_cast<uint32_t>(static_cast<int32_t>(x) >> 31);
+    return x ^ ((s & 0x7fff0000u) | 0x80000000u);
   }
 };
 template <> struct KeyOf<__nv_bfloat16> {
@@ -57,7 +66,8 @@ template <> struct KeyOf<double> {
   using Key = unsigned long long;
   static constexpr int kPasses = 8;
   static __device__ __forceinline__ Key key(unsigned long long u) {
-    return (u >> 63) ? ~u : (u | 0x8000000000000000ull);
+    const unsigned long long s = static_cast<unsigned long long>(static_cast<long long>(u) >> 63);
+    return u ^ (s | 0x8000000000000000ull);
   }
 };
 template <> struct KeyOf<int32_t> {
@@ -164,7 +174,7 @@ __device__ __forceinline__ void stage_copy_out(const long long* sidx, const B* s
 // vector loads, so no slot needs a bounds test (the common case: candidate
 // counts are powers of two).
 template <typename T, int ITEMS, int MAXT, bool FULL>
-__global__ void __launch_bounds__(MAXT)
+__global__ void __launch_bounds__(MAXT, (ITEMS <= 8 && MAXT == 512) ? ATK_SELECT_ROW_MINBLOCKS : 1)
 select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                   const long long* __restrict__ cand_idx, int k0, long long cand_row_stride, int k,
                   typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
@@ -172,7 +182,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   using K = KeyOf<T>;
   using Key = typename K::Key;
   using Bits = typename ElemTraits<T>::Bits;
-  __shared__ uint32_t hist[256];
+  __shared__ __align__(16) uint32_t hist[256 * K::kPasses];
   __shared__ uint32_t misc[2];
   __shared__ uint32_t wsum[32];
 
@@ -184,6 +194,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   const Bits* vrow = cand_vals + row * cand_row_stride;
   const long long* irow = cand_idx + row * cand_row_stride;
   const int slot0 = tid * ITEMS;
+  for (int i = tid; i < 256 * K::kPasses; i += nthr) hist[i] = 0;
   // number of this thread's slots that exist
   int valid = ITEMS;
   if (!FULL) {
@@ -203,24 +214,35 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   Key key[ITEMS];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) key[i] = K::key(raw[i]);
+  __syncthreads();   // histograms are clear
 
   Key prefix = 0, mask = 0;
   uint32_t need = static_cast<uint32_t>(k);
-  // up to four passes are unrolled so that shifts are immediates and the first
-  // pass has no prefix test; the eight passes of 64-bit keys stay a loop
+  // One histogram per pass, all cleared up front (under the latency of the
+  // loads above): two block barriers per pass instead of three.  (Letting every
+  // warp pick the digit for itself saves one more barrier but measured slower
+  // when the rows fill the GPU.)  Up to four passes are unrolled so that shifts
+  // are immediates and the first pass has no prefix test; the eight passes of
+  // 64-bit keys stay a loop.
 #pragma unroll(K::kPasses <= 4 ? K::kPasses : 1)
   for (int pass = 0; pass < K::kPasses; ++pass) {
     const int shift = digit_shift<K>(pass);
-    for (int i = tid; i < 256; i += nthr) hist[i] = 0;
-    __syncthreads();
+    uint32_t* h = hist + 256 * pass;
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
       bool in = FULL || i < valid;
       if (pass > 0) in = in && (key[i] & mask) == prefix;
-      if (in) atomicAdd(&hist[static_cast<uint32_t>(key[i] >> shift) & 255u], 1u);
+      if (in) atomicAdd(&h[static_cast<uint32_t>(key[i] >> shift) & 255u], 1u);
     }
     __syncthreads();
-    if (tid < 32) pick_digit(hist, need, tid, &misc[0], &misc[1]);
+    if (warp == 0) {
+      uint32_t digit, new_need;
+      pick_digit_all(h, need, lane, digit, new_need);
+      if (lane == 0) {
+        misc[0] = digit;
+        misc[1] = new_need;
+      }
+    }
     __syncthreads();
     prefix |= static_cast<Key>(misc[0]) << shift;
     mask |= static_cast<Key>(255u) << shift;
@@ -330,32 +352,45 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   const int shift = digit_shift<K>(pass);
   for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = 0;
   __syncthreads();
-  const auto* vrow = cand_vals + row * cand_row_stride;
-  for (int cc = 0; cc < cpb; ++cc) {
-    const long long begin = (static_cast<long long>(blockIdx.x) * cpb + cc) * (kLargeThreads * ITEMS);
-    if (begin >= k0) break;
-    long long end = begin + kLargeThreads * ITEMS;
-    if (end > k0) end = k0;
-    // thread t takes the ITEMS consecutive candidates begin + t*ITEMS ...
-    const long long first = begin + static_cast<long long>(threadIdx.x) * ITEMS;
-    typename ElemTraits<T>::Bits raw[ITEMS];
-    load_items<typename ElemTraits<T>::Bits, ITEMS>(vrow, first, end, vec, raw);
-    // Neighbouring candidates often share a digit (always in the first passes,
-    // where few digits occur at all): runs of equal digits become one update.
-    uint32_t run_bin = 0xffffffffu, run_len = 0;
+  // The block owns cpb consecutive chunks = one contiguous range of the row.
+  // Thread t takes packs t, t + 256, ... of ITEMS consecutive candidates, kHistBatch
+  // packs (vector loads) in flight before the first histogram update.
+  const long long blk_begin = static_cast<long long>(blockIdx.x) * cpb * (kLargeThreads * ITEMS);
+  long long blk_len_ll = k0 - blk_begin;
+  if (blk_len_ll > static_cast<long long>(cpb) * (kLargeThreads * ITEMS)) blk_len_ll = static_cast<long long>(cpb) * (kLargeThreads * ITEMS);
+  const int blk_len = blk_len_ll > 0 ? static_cast<int>(blk_len_ll) : 0;
+  const auto* vblk = cand_vals + row * cand_row_stride + blk_begin;
+  constexpr int kHistBatch = 2;
+  for (int p0 = threadIdx.x * ITEMS; p0 < blk_len; p0 += kLargeThreads * ITEMS * kHistBatch) {
+    typename ElemTraits<T>::Bits raw[kHistBatch][ITEMS];
 #pragma unroll
-    for (int u = 0; u < ITEMS; ++u) {
-      const Key key = K::key(raw[u]);
-      const bool in = first + u < end && (key & st.mask) == st.prefix;
-      const uint32_t bin = in ? (static_cast<uint32_t>(key >> shift) & 255u) : 0xffffffffu;
-      if (bin != run_bin) {
-        if (run_len) atomicAdd(&sh[run_bin], run_len);
-        run_bin = bin;
-        run_len = 0;
-      }
-      run_len += in ? 1u : 0u;
+    for (int bb = 0; bb < kHistBatch; ++bb) {
+      const int first = p0 + bb * kLargeThreads * ITEMS;
+      if (first < blk_len) load_items<typename ElemTraits<T>::Bits, ITEMS>(vblk, first, blk_len, vec, raw[bb]);
     }
-    if (run_len) atomicAdd(&sh[run_bin], run_len);
+#pragma unroll
+    for (int bb = 0; bb < kHistBatch; ++bb) {
+      const int first = p0 + bb * kLargeThreads * ITEMS;
+      const int valid = blk_len - first;       // > 0 exactly for the packs that were loaded
+      if (valid <= 0) continue;
+      // Neighbouring candidates often share a digit (always in the first passes,
+      // where few digits occur at all): runs of equal digits become one update.
+      uint32_t run_bin = 0xffffffffu, run_len = 0;
+#pragma unroll
+      for (int u = 0; u < ITEMS; ++u) {
+        const Key key = K::key(raw[bb][u]);
+        bool in = (key & st.mask) == st.prefix;
+        if (valid < ITEMS) in = in && u < valid;        // only the last pack of a row is short
+        const uint32_t bin = in ? (static_cast<uint32_t>(key >> shift) & 255u) : 0xffffffffu;
+        if (bin != run_bin) {
+          if (run_len) atomicAdd(&sh[run_bin], run_len);
+          run_bin = bin;
+          run_len = 0;
+        }
+        run_len += in ? 1u : 0u;
+      }
+      if (run_len) atomicAdd(&sh[run_bin], run_len);
+    }
   }
   __syncthreads();
   uint32_t* gh = hist + (row * K::kPasses + pass) * 256;
@@ -381,53 +416,64 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   }
 }
 
+// How many candidates of every chunk lie above / on the threshold.  One warp per
+// chunk (no block barriers): lane l takes packs l, l + 32, ... of the chunk,
+// several vector loads in flight.  The block that finishes last for a row turns
+// the per-chunk counts into exclusive prefixes.
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kLargeThreads)
 select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
                     long long cand_row_stride, const RowState<typename KeyOf<T>::Key>* __restrict__ state,
                     uint2* __restrict__ counts /* [rows][chunks] */, uint32_t* __restrict__ tickets, int chunks,
-                    int cpb /* chunks per block */, int vec) {
+                    int cpw /* chunks per warp */, int vec) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
-  __shared__ uint32_t s_gt, s_eq;
+  using Bits = typename ElemTraits<T>::Bits;
   __shared__ bool last;
   const long long row = blockIdx.y;
   const Key thr = state[row].prefix;
-  const auto* vrow = cand_vals + row * cand_row_stride;
-  for (int cc = 0; cc < cpb; ++cc) {
-    const long long chunk = static_cast<long long>(blockIdx.x) * cpb + cc;
-    if (chunk >= chunks) break;
-    if (threadIdx.x == 0) {
-      s_gt = 0;
-      s_eq = 0;
-    }
-    __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long chunk0 = (static_cast<long long>(blockIdx.x) * (kLargeThreads / 32) + (threadIdx.x >> 5)) * cpw;
+  for (long long chunk = chunk0; chunk < chunk0 + cpw && chunk < chunks; ++chunk) {
     const long long begin = chunk * (kLargeThreads * ITEMS);
-    long long end = begin + kLargeThreads * ITEMS;
-    if (end > k0) end = k0;
+    long long len_ll = k0 - begin;
+    if (len_ll > kLargeThreads * ITEMS) len_ll = kLargeThreads * ITEMS;
+    const int len = static_cast<int>(len_ll);
+    const Bits* vchunk = cand_vals + row * cand_row_stride + begin;
+    constexpr int kPacks = kLargeThreads / 32;                       // packs per lane
+    constexpr int kBatch = sizeof(Bits) <= 4 ? 4 : 2;
     uint32_t gt = 0, eq = 0;
-    const long long first = begin + static_cast<long long>(threadIdx.x) * ITEMS;
-    typename ElemTraits<T>::Bits raw[ITEMS];
-    load_items<typename ElemTraits<T>::Bits, ITEMS>(vrow, first, end, vec, raw);
 #pragma unroll
-    for (int u = 0; u < ITEMS; ++u) {
-      const Key key = K::key(raw[u]);
-      const bool in = first + u < end;
-      gt += (in && key > thr) ? 1u : 0u;
-      eq += (in && key == thr) ? 1u : 0u;
-    }
+    for (int b0 = 0; b0 < kPacks; b0 += kBatch) {
+      Bits raw[kBatch][ITEMS];
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-      gt += __shfl_xor_sync(0xffffffffu, gt, off);
-      eq += __shfl_xor_sync(0xffffffffu, eq, off);
+      for (int bb = 0; bb < kBatch; ++bb) {
+        const int first = ((b0 + bb) * 32 + lane) * ITEMS;
+        if (first < len) load_items<Bits, ITEMS>(vchunk, first, len, vec, raw[bb]);
+      }
+#pragma unroll
+      for (int bb = 0; bb < kBatch; ++bb) {
+        const int valid = len - ((b0 + bb) * 32 + lane) * ITEMS;
+        if (valid >= ITEMS) {
+#pragma unroll
+          for (int u = 0; u < ITEMS; ++u) {
+            const Key key = K::key(raw[bb][u]);
+            gt += key > thr ? 1u : 0u;
+            eq += key == thr ? 1u : 0u;
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < ITEMS; ++u) {
+            const Key key = K::key(raw[bb][u]);
+            gt += (u < valid && key > thr) ? 1u : 0u;
+            eq += (u < valid && key == thr) ? 1u : 0u;
+          }
+        }
+      }
     }
-    if ((threadIdx.x & 31) == 0) {
-      atomicAdd(&s_gt, gt);
-      atomicAdd(&s_eq, eq);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) counts[row * chunks + chunk] = make_uint2(s_gt, s_eq);
-    __syncthreads();
+    gt = __reduce_add_sync(0xffffffffu, gt);
+    eq = __reduce_add_sync(0xffffffffu, eq);
+    if (lane == 0) counts[row * chunks + chunk] = make_uint2(gt, eq);
   }
   // The block that finishes last for the row turns the per-chunk counts into
   // exclusive prefixes (one warp).
@@ -439,7 +485,6 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
   if (!last || threadIdx.x >= 32) return;
   __threadfence();
   uint2* c = counts + row * chunks;
-  const int lane = threadIdx.x;
   uint32_t carry_gt = 0, carry_eq = 0;
   for (int base = 0; base < chunks; base += 32) {
     const int i = base + lane;
@@ -496,11 +541,14 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   Key keys[ITEMS];
   load_items<typename ElemTraits<T>::Bits, ITEMS>(vrow, slot0, end, vec, raws);
   load_items<long long, ITEMS>(irow, slot0, end, vec, idxs);
+  // slots of this thread that exist (only the last thread of a row can be short)
+  long long valid_ll = end - slot0;
+  const int valid = valid_ll >= ITEMS ? ITEMS : (valid_ll > 0 ? static_cast<int>(valid_ll) : 0);
   uint32_t mine = 0;
 #pragma unroll
   for (int u = 0; u < ITEMS; ++u) {
     keys[u] = K::key(raws[u]);
-    const bool in = slot0 + u < end;
+    const bool in = valid == ITEMS || u < valid;
     mine += (in && keys[u] > thr) ? 1u : 0u;
     mine += (in && keys[u] == thr) ? 0x10000u : 0u;
   }
@@ -536,7 +584,7 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   uint32_t leq = excl >> 16;
 #pragma unroll
   for (int u = 0; u < ITEMS; ++u) {
-    if (slot0 + u < end) {
+    if (valid == ITEMS || u < valid) {
       int at = -1;
       if (keys[u] > thr) {
         at = static_cast<int>(lgt++);
@@ -642,9 +690,9 @@ int select_typed(const SelectLaunch& a) {
   // The histogram and count blocks loop over several chunks when there are many
   // more chunks than the GPU holds blocks, so that the per-block epilogue (global
   // flush, fence, ticket) is paid once per group of chunks.
-  long long cpb = (a.rows * chunks) / (148 * 16);
+  long long cpb = (a.rows * chunks + 148ll * 6 - 1) / (148ll * 6);
   if (cpb < 1) cpb = 1;
-  if (cpb > 16) cpb = 16;
+  if (cpb > 64) cpb = 64;
   const long long groups = (chunks + cpb - 1) / cpb;
   const dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(a.rows));
   const dim3 grid_g(static_cast<unsigned>(groups), static_cast<unsigned>(a.rows));
@@ -654,8 +702,14 @@ int select_typed(const SelectLaunch& a) {
   for (int pass = 0; pass < K::kPasses; ++pass)
     select_hist_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
         cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
-  select_count_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
-      cv, a.k0, a.cand_row_stride, state, counts, tickets, static_cast<int>(chunks), static_cast<int>(cpb), vec);
+  // count: one warp per cpw chunks, about one wave of blocks (every block ends with a fence and a ticket)
+  constexpr int kWarps = kLargeThreads / 32;
+  long long cpw = (a.rows * chunks + 148ll * 8 * kWarps - 1) / (148ll * 8 * kWarps);
+  if (cpw < 1) cpw = 1;
+  if (cpw > 16) cpw = 16;
+  const dim3 grid_c(static_cast<unsigned>((chunks + kWarps * cpw - 1) / (kWarps * cpw)), static_cast<unsigned>(a.rows));
+  select_count_kernel<T, kItems><<<grid_c, kLargeThreads, 0, a.stream>>>(
+      cv, a.k0, a.cand_row_stride, state, counts, tickets, static_cast<int>(chunks), static_cast<int>(cpw), vec);
   select_write_kernel<T, kItems><<<grid, kLargeThreads, 0, a.stream>>>(
       cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, counts, ov, a.out_idx, a.out_row_stride, vec);
   note_launch(K::kPasses + 2);
