@@ -210,6 +210,25 @@ int atk_topk_host(const void* x_host, int dtype, int64_t rows, int64_t n, int64_
                   void* out_vals_host, int64_t* out_idx_host,
                   void* device_scratch, size_t scratch_bytes, int64_t chunk_rows);
 
+/*
+ * Consumer-side step: gather the records the operator selected.  No counterpart
+ * in the reference (its users call torch.gather / index_select on the indices
+ * that approx_topk.topk returns, e.g. to fetch the selected keys and values of
+ * an attention head).
+ *
+ *   src   rows x n records of `record_bytes` bytes each; record (r, i) starts at
+ *         src + r*src_row_stride_bytes + i*record_bytes
+ *   idx   rows x k positions in [0, n), row r at idx + r*idx_row_stride (elements)
+ *   out   rows x k records, dense: record (r, q) at out + (r*k + q)*record_bytes
+ *
+ * Records move in 16-byte pieces when `record_bytes`, the strides and the
+ * pointers are multiples of 16, else in pieces of 4, 2 or 1 bytes.  A position
+ * outside [0, n) yields a record of zero bytes (nothing is read for it).
+ */
+int atk_gather_records(const void* src, int64_t rows, int64_t n, int64_t record_bytes,
+                       int64_t src_row_stride_bytes, const int64_t* idx, int64_t k,
+                       int64_t idx_row_stride, void* out, void* stream);
+
 /* Number of kernel launches issued by this library on the calling thread since
  * the last atk_reset_launch_count(); benchmarks use it to report launches. */
 int64_t atk_launch_count(void);

@@ -57,6 +57,7 @@ SIGNATURES = {
     "atk_bucketed_argmax": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_topk_host_scratch_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64, _i64]),
     "atk_topk_host": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _vp, _vp, _vp, _sz, _i64]),
+    "atk_gather_records": (_int, [_vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
     "atk_launch_count": (_i64, []),
     "atk_reset_launch_count": (None, []),
 }
