@@ -100,6 +100,7 @@ def test_stage1_without_scratch_and_on_views(dtype):
 @pytest.mark.parametrize("rows,k0,k", [
     (5, 256, 64), (3, 4096, 2048), (2, 16384, 5000), (2, 8192, 8191),   # one block per row
     (2, 20000, 777), (1, 300000, 150000), (3, 70000, 1),                # several blocks per row
+    (3, 20001, 5000), (2, 70003, 35001),                                # ... with rows that break the vector alignment
 ])
 def test_select_matches_oracle(dtype, rows, k0, k):
     for dist in ("full", "ties"):

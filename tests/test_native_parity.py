@@ -215,7 +215,8 @@ def test_block_per_bucket_reference_kernel_same_selection(j):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,k0,k", [(4, 256, 64), (16, 4096, 2048), (3, 1000, 1), (2, 1000, 1000),
                                        (5, 777, 300), (2, 16384, 5000), (2, 32768, 5000), (1, 40000, 20000),
-                                       (2, 100000, 777), (1, 1 << 21, 1 << 20)])
+                                       (2, 100000, 777), (1, 1 << 21, 1 << 20),
+                                       (3, 20001, 5000), (2, 70003, 35001), (7, 4097, 100)])   # rows off the vector alignment
 def test_select_matches_oracle(dtype, rows, k0, k):
     for dist in ("randn", "ties"):
         cv = make(rows, k0, dtype, 300 + k, dist)
