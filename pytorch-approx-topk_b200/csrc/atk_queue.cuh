@@ -6,9 +6,10 @@
 //               rest).  Works for every dtype and follows the reference's
 //               insertion rule instruction for instruction, NaN behaviour
 //               included.
-// PackedQueue — for 16-bit inputs whose columns have at most 65536 stripes:
+// PackedQueue — for 8- and 16-bit inputs (float or integer) whose stripe numbers
+//               fit beside the value (65536 / 2^24 stripes):
 //               one 32-bit word per entry, (order-preserving image of the
-//               value) << 16 | stripe, so that the (value, position) ranking
+//               value) << 16 or 24 | stripe, so that the (value, position) ranking
 //               "largest value first, later position wins" is a plain unsigned
 //               compare and an insertion is 2J-1 integer min/max operations
 //               with the stripe carried for free.  Differences from the
@@ -152,9 +153,60 @@ __device__ __forceinline__ void raw_words(const uint2& r, uint32_t (&w)[2]) {
   w[0] = r.x; w[1] = r.y;
 }
 
+__device__ __forceinline__ void raw_words(const uint32_t& r, uint32_t (&w)[1]) { w[0] = r; }
+
+// Order-preserving unsigned image of the elements packed in one 32-bit word
+// (two 16-bit or four 8-bit elements), and the way back for one element.
+template <typename T> struct PackedImage;
+template <> struct PackedImage<__half> {
+  static constexpr int kBits = 16;
+  static __device__ __forceinline__ uint32_t word(uint32_t w) { return ord16x2(w); }
+  // Both zeros share one image; the element itself is read back to return the
+  // sign the input had (a load that almost never executes).
+  static __device__ __forceinline__ uint16_t inverse(uint32_t o, const __half* elem) {
+    if (o == 0x8000u) return ld_stream_2(elem);
+    return ord16_inverse(o);
+  }
+};
+template <> struct PackedImage<__nv_bfloat16> {
+  static constexpr int kBits = 16;
+  static __device__ __forceinline__ uint32_t word(uint32_t w) { return ord16x2(w); }
+  static __device__ __forceinline__ uint16_t inverse(uint32_t o, const __nv_bfloat16* elem) {
+    if (o == 0x8000u) return ld_stream_2(elem);
+    return ord16_inverse(o);
+  }
+};
+template <> struct PackedImage<int16_t> {
+  static constexpr int kBits = 16;
+  static __device__ __forceinline__ uint32_t word(uint32_t w) { return w ^ 0x80008000u; }
+  static __device__ __forceinline__ uint16_t inverse(uint32_t o, const int16_t*) { return static_cast<uint16_t>(o ^ 0x8000u); }
+};
+template <> struct PackedImage<int8_t> {
+  static constexpr int kBits = 8;
+  static __device__ __forceinline__ uint32_t word(uint32_t w) { return w ^ 0x80808080u; }
+  static __device__ __forceinline__ uint8_t inverse(uint32_t o, const int8_t*) { return static_cast<uint8_t>(o ^ 0x80u); }
+};
+template <> struct PackedImage<uint8_t> {
+  static constexpr int kBits = 8;
+  static __device__ __forceinline__ uint32_t word(uint32_t w) { return w; }
+  static __device__ __forceinline__ uint8_t inverse(uint32_t o, const uint8_t*) { return static_cast<uint8_t>(o); }
+};
+
+// Entry = (image of the value) << kShift | stripe, kShift = 32 - bits of the
+// element: 65536 stripes for 16-bit elements, 2^24 for 8-bit ones.  Entry 0
+// means "never filled"; for the integer types it is also the entry of the
+// lowest value at stripe 0, and an empty slot decodes to exactly that element,
+// which is the right answer whenever the slot has to be reported (a bucket
+// holds at least J elements).
 template <typename T, int J, bool FIRST>
 struct PackedQueue {
-  static_assert(sizeof(T) == 2, "packed queues are for 16-bit element types");
+  static_assert(sizeof(T) <= 2, "packed queues are for 8- and 16-bit element types");
+  using Img = PackedImage<T>;
+  static constexpr int kBits = Img::kBits;
+  static constexpr int kShift = 32 - kBits;
+  static constexpr uint32_t kStripeMask = (1u << kShift) - 1u;
+  static constexpr long long kMaxStripes = 1ll << kShift;
+  static constexpr int kPerWord = 32 / kBits;       // elements per 32-bit word of a vector load
   static constexpr int kWords = J;
   static constexpr bool kPacked = true;
   static constexpr int kCols = 1;
@@ -167,10 +219,10 @@ struct PackedQueue {
     for (int q = 0; q < J; ++q) k[q] = 0u;
   }
 
-  // With FIRST the earlier position must win a tie, so the low half holds the
+  // With FIRST the earlier position must win a tie, so the low part holds the
   // complement of the stripe number.
   static __device__ __forceinline__ uint32_t low(int stripe) {
-    return FIRST ? (0xffffu - static_cast<uint32_t>(stripe)) : static_cast<uint32_t>(stripe);
+    return FIRST ? (kStripeMask - static_cast<uint32_t>(stripe)) : static_cast<uint32_t>(stripe);
   }
 
   __device__ __forceinline__ void push(uint32_t key) {
@@ -182,22 +234,27 @@ struct PackedQueue {
     for (int q = 0; q < J; ++q) k[q] = n[q];
   }
 
+  // entry of element `e` (0 = lowest address) of an image word
+  static __device__ __forceinline__ uint32_t key_of(uint32_t image_word, int e, uint32_t lo) {
+    return ((image_word << (kShift - kBits * e)) & ~kStripeMask) | lo;
+  }
+
   template <int V, bool SKIP>
   static __device__ __forceinline__ void consume(PackedQueue (&q)[V], const typename VecLoad<T, V>::Raw& raw,
                                                  int stripe) {
     const uint32_t lo = low(stripe);
     if constexpr (V == 1) {
-      const uint32_t key = ((ord16x2(raw) & 0xffffu) << 16) | lo;
+      const uint32_t key = key_of(Img::word(raw), 0, lo);
       if (!SKIP || key > q[0].k[0]) q[0].push(key);
     } else {
-      uint32_t w[V / 2];
+      uint32_t w[V / kPerWord];
       raw_words(raw, w);
       uint32_t key[V];
 #pragma unroll
-      for (int i = 0; i < V / 2; ++i) {
-        const uint32_t o = ord16x2(w[i]);
-        key[2 * i] = (o << 16) | lo;
-        key[2 * i + 1] = (o & 0xffff0000u) | lo;
+      for (int i = 0; i < V / kPerWord; ++i) {
+        const uint32_t o = Img::word(w[i]);
+#pragma unroll
+        for (int e = 0; e < kPerWord; ++e) key[kPerWord * i + e] = key_of(o, e, lo);
       }
       if (SKIP) {
         bool any = false;
@@ -210,8 +267,8 @@ struct PackedQueue {
     }
   }
 
-  __device__ __forceinline__ void push_tail(uint16_t bits, int stripe) {
-    push(((ord16x2(bits) & 0xffffu) << 16) | low(stripe));
+  __device__ __forceinline__ void push_tail(typename ElemTraits<T>::Bits bits, int stripe) {
+    push(key_of(Img::word(bits), 0, low(stripe)));
   }
 
   __device__ __forceinline__ void store(uint32_t* base, int stride) const {
@@ -224,15 +281,11 @@ struct PackedQueue {
   }
 
   __device__ __forceinline__ long long stripe(int q) const {
-    const uint32_t l = k[q] & 0xffffu;
-    return FIRST ? (0xffffu - l) : l;
+    const uint32_t l = k[q] & kStripeMask;
+    return FIRST ? (kStripeMask - l) : l;
   }
-  // Both zeros share one key; the element itself is read back to return the
-  // sign the input had (a load that almost never executes).
-  __device__ __forceinline__ uint16_t value_bits(int q, const T* elem) const {
-    const uint32_t o = k[q] >> 16;
-    if (o == 0x8000u) return ld_stream_2(elem);
-    return ord16_inverse(o);
+  __device__ __forceinline__ typename ElemTraits<T>::Bits value_bits(int q, const T* elem) const {
+    return Img::inverse(k[q] >> kShift, elem);
   }
 };
 

@@ -326,7 +326,10 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 // histogram; the block that finishes last for a row (a ticket counter, no
 // waiting) then picks the digit and advances the row's (prefix, mask, need).
 // `tickets` and `hist` must be zero on entry (one memset per select call).
-template <typename T, int ITEMS>
+// RLE: merge runs of equal digits inside a thread before updating the
+// histogram (first pass, where few digits occur at all); later passes count
+// only the candidates that match the prefix and update one by one.
+template <typename T, int ITEMS, bool RLE>
 __global__ void __launch_bounds__(kLargeThreads)
 select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
                    long long cand_row_stride, int pass, long long k,
@@ -373,23 +376,31 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
       const int first = p0 + bb * kLargeThreads * ITEMS;
       const int valid = blk_len - first;       // > 0 exactly for the packs that were loaded
       if (valid <= 0) continue;
-      // Neighbouring candidates often share a digit (always in the first passes,
-      // where few digits occur at all): runs of equal digits become one update.
-      uint32_t run_bin = 0xffffffffu, run_len = 0;
+      if constexpr (RLE) {
+        uint32_t run_bin = 0xffffffffu, run_len = 0;
 #pragma unroll
-      for (int u = 0; u < ITEMS; ++u) {
-        const Key key = K::key(raw[bb][u]);
-        bool in = (key & st.mask) == st.prefix;
-        if (valid < ITEMS) in = in && u < valid;        // only the last pack of a row is short
-        const uint32_t bin = in ? (static_cast<uint32_t>(key >> shift) & 255u) : 0xffffffffu;
-        if (bin != run_bin) {
-          if (run_len) atomicAdd(&sh[run_bin], run_len);
-          run_bin = bin;
-          run_len = 0;
+        for (int u = 0; u < ITEMS; ++u) {
+          const Key key = K::key(raw[bb][u]);
+          bool in = (key & st.mask) == st.prefix;
+          if (valid < ITEMS) in = in && u < valid;        // only the last pack of a row is short
+          const uint32_t bin = in ? (static_cast<uint32_t>(key >> shift) & 255u) : 0xffffffffu;
+          if (bin != run_bin) {
+            if (run_len) atomicAdd(&sh[run_bin], run_len);
+            run_bin = bin;
+            run_len = 0;
+          }
+          run_len += in ? 1u : 0u;
         }
-        run_len += in ? 1u : 0u;
+        if (run_len) atomicAdd(&sh[run_bin], run_len);
+      } else {
+#pragma unroll
+        for (int u = 0; u < ITEMS; ++u) {
+          const Key key = K::key(raw[bb][u]);
+          bool in = (key & st.mask) == st.prefix;
+          if (valid < ITEMS) in = in && u < valid;
+          if (in) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & 255u], 1u);
+        }
       }
-      if (run_len) atomicAdd(&sh[run_bin], run_len);
     }
   }
   __syncthreads();
@@ -699,8 +710,10 @@ int select_typed(const SelectLaunch& a) {
   // vector loads need 16-byte aligned rows of values and of positions
   const int vec = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * sizeof(Bits)) % 16 == 0) &&
                   (reinterpret_cast<uintptr_t>(a.cand_idx) % 16 == 0) && ((a.cand_row_stride * 8) % 16 == 0);
-  for (int pass = 0; pass < K::kPasses; ++pass)
-    select_hist_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
+  select_hist_kernel<T, kItems, true><<<grid_g, kLargeThreads, 0, a.stream>>>(
+      cv, a.k0, a.cand_row_stride, 0, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
+  for (int pass = 1; pass < K::kPasses; ++pass)
+    select_hist_kernel<T, kItems, false><<<grid_g, kLargeThreads, 0, a.stream>>>(
         cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
   // count: one warp per cpw chunks, about one wave of blocks (every block ends with a fence and a ticket)
   constexpr int kWarps = kLargeThreads / 32;

@@ -90,16 +90,18 @@ int launch_stage1(const SweepLaunch& a) {
   return ATK_OK;
 }
 
-// Queue layout: 16-bit inputs use packed 32-bit entries whenever the stripe
-// number fits in 16 bits (scanned with the two-column SIMD queues on the
-// vector path); everything else uses (float, int) pairs.
+// Queue layout: 8- and 16-bit inputs use packed 32-bit entries whenever the
+// stripe number fits beside the value (the float formats scanned with the
+// two-column SIMD queues on the vector path); everything else uses (value,
+// stripe) pairs.
 template <typename T, int J, int V, bool FIRST>
 int launch_by_queue(const SweepLaunch& a) {
-  if constexpr (ElemTraits<T>::kHalfFloat) {
+  if constexpr (sizeof(T) <= 2) {
     // stripes are numbered 0 .. n/b (the last one only when b does not divide n)
     const long long stripes = a.n / a.b + (a.n % a.b != 0 ? 1 : 0);
-    if (stripes <= 65536) {
-      return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4)>(a);
+    if (stripes <= PackedQueue<T, J, FIRST>::kMaxStripes) {
+      // the two-column SIMD scan exists for the float formats only
+      return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4 && ElemTraits<T>::kHalfFloat)>(a);
     }
   }
   return launch_stage1<T, FloatQueue<T, J, FIRST>, J, V, false>(a);

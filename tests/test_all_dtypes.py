@@ -82,6 +82,23 @@ def test_stage1_matches_oracle_slot_for_slot(dtype, j, interleaved):
 
 
 @pytest.mark.parametrize("dtype", WIDE)
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_rows_full_of_the_lowest_value(dtype, interleaved):
+    # Every bucket holds exactly j elements, all equal to the type's lowest value
+    # (the value the queues start from): every position must come back once.
+    low = float("-inf") if dtype.is_floating_point else torch.iinfo(dtype).min
+    for j in (1, 2, 4):
+        x = torch.full((3, 64), low, device="cuda", dtype=dtype)
+        check_stage1_exact(x, 64, j, interleaved)
+        v, i = api.stage1(x, 64, j, interleaved)
+        assert torch.equal(i.sort(dim=-1).values.cpu(), torch.arange(64).expand(3, 64))
+        assert bool((v == low).all())
+        # longer buckets: the last j positions of every bucket win
+        x = torch.full((2, 640), low, device="cuda", dtype=dtype)
+        check_stage1_exact(x, 64, j, interleaved)
+
+
+@pytest.mark.parametrize("dtype", WIDE)
 def test_stage1_without_scratch_and_on_views(dtype):
     # no workspace: the split over blocks is off, same answer
     x = make(1, 600000, dtype, 5)
