@@ -23,6 +23,16 @@ namespace {
 constexpr int kSmallMaxK0 = 16384;   // 512 threads x 32 candidates in registers (32-bit keys)
 constexpr int kChunk = 2048;         // candidates per block on the large path
 constexpr int kLargeThreads = 256;
+// Vector loads a thread keeps in flight before it starts computing, in the
+// histogram and in the count kernel of the multi-block path (build knobs; more
+// cost registers and with them resident blocks: 2 measured best for 16-bit
+// elements, 4 for 32-bit ones in the count kernel).
+#ifndef ATK_HIST_BATCH
+#define ATK_HIST_BATCH 2
+#endif
+#ifndef ATK_COUNT_BATCH
+#define ATK_COUNT_BATCH (sizeof(Bits) == 4 ? 4 : 2)
+#endif
 #ifndef ATK_SELECT_ROW_THREADS
 #define ATK_SELECT_ROW_THREADS 512
 #endif
@@ -326,10 +336,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 // histogram; the block that finishes last for a row (a ticket counter, no
 // waiting) then picks the digit and advances the row's (prefix, mask, need).
 // `tickets` and `hist` must be zero on entry (one memset per select call).
-// RLE: merge runs of equal digits inside a thread before updating the
-// histogram (first pass, where few digits occur at all); later passes count
-// only the candidates that match the prefix and update one by one.
-template <typename T, int ITEMS, bool RLE>
+template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kLargeThreads)
 select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
                    long long cand_row_stride, int pass, long long k,
@@ -363,7 +370,7 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   if (blk_len_ll > static_cast<long long>(cpb) * (kLargeThreads * ITEMS)) blk_len_ll = static_cast<long long>(cpb) * (kLargeThreads * ITEMS);
   const int blk_len = blk_len_ll > 0 ? static_cast<int>(blk_len_ll) : 0;
   const auto* vblk = cand_vals + row * cand_row_stride + blk_begin;
-  constexpr int kHistBatch = 2;
+  constexpr int kHistBatch = ATK_HIST_BATCH;
   for (int p0 = threadIdx.x * ITEMS; p0 < blk_len; p0 += kLargeThreads * ITEMS * kHistBatch) {
     typename ElemTraits<T>::Bits raw[kHistBatch][ITEMS];
 #pragma unroll
@@ -376,30 +383,14 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
       const int first = p0 + bb * kLargeThreads * ITEMS;
       const int valid = blk_len - first;       // > 0 exactly for the packs that were loaded
       if (valid <= 0) continue;
-      if constexpr (RLE) {
-        uint32_t run_bin = 0xffffffffu, run_len = 0;
+      // plain shared-memory atomics: merging runs of equal digits inside a thread
+      // first was measured slower in every pass (42 vs 55 us in the first one)
 #pragma unroll
-        for (int u = 0; u < ITEMS; ++u) {
-          const Key key = K::key(raw[bb][u]);
-          bool in = (key & st.mask) == st.prefix;
-          if (valid < ITEMS) in = in && u < valid;        // only the last pack of a row is short
-          const uint32_t bin = in ? (static_cast<uint32_t>(key >> shift) & 255u) : 0xffffffffu;
-          if (bin != run_bin) {
-            if (run_len) atomicAdd(&sh[run_bin], run_len);
-            run_bin = bin;
-            run_len = 0;
-          }
-          run_len += in ? 1u : 0u;
-        }
-        if (run_len) atomicAdd(&sh[run_bin], run_len);
-      } else {
-#pragma unroll
-        for (int u = 0; u < ITEMS; ++u) {
-          const Key key = K::key(raw[bb][u]);
-          bool in = (key & st.mask) == st.prefix;
-          if (valid < ITEMS) in = in && u < valid;
-          if (in) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & 255u], 1u);
-        }
+      for (int u = 0; u < ITEMS; ++u) {
+        const Key key = K::key(raw[bb][u]);
+        bool in = (key & st.mask) == st.prefix;
+        if (valid < ITEMS) in = in && u < valid;        // only the last pack of a row is short
+        if (in) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & 255u], 1u);
       }
     }
   }
@@ -452,7 +443,7 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
     const int len = static_cast<int>(len_ll);
     const Bits* vchunk = cand_vals + row * cand_row_stride + begin;
     constexpr int kPacks = kLargeThreads / 32;                       // packs per lane
-    constexpr int kBatch = sizeof(Bits) <= 4 ? 4 : 2;
+    constexpr int kBatch = ATK_COUNT_BATCH;
     uint32_t gt = 0, eq = 0;
 #pragma unroll
     for (int b0 = 0; b0 < kPacks; b0 += kBatch) {
@@ -710,10 +701,8 @@ int select_typed(const SelectLaunch& a) {
   // vector loads need 16-byte aligned rows of values and of positions
   const int vec = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * sizeof(Bits)) % 16 == 0) &&
                   (reinterpret_cast<uintptr_t>(a.cand_idx) % 16 == 0) && ((a.cand_row_stride * 8) % 16 == 0);
-  select_hist_kernel<T, kItems, true><<<grid_g, kLargeThreads, 0, a.stream>>>(
-      cv, a.k0, a.cand_row_stride, 0, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
-  for (int pass = 1; pass < K::kPasses; ++pass)
-    select_hist_kernel<T, kItems, false><<<grid_g, kLargeThreads, 0, a.stream>>>(
+  for (int pass = 0; pass < K::kPasses; ++pass)
+    select_hist_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
         cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
   // count: one warp per cpw chunks, about one wave of blocks (every block ends with a fence and a ticket)
   constexpr int kWarps = kLargeThreads / 32;
