@@ -138,6 +138,7 @@ int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_st
     a.sm_count = sm_count_of_current_device();
     a.workspace = workspace;
     a.workspace_bytes = workspace_bytes;
+    a.out_keys = nullptr;
     a.stream = static_cast<cudaStream_t>(stream);
     return sweep_dispatch(a, dtype);
   }
@@ -189,6 +190,7 @@ int atk_stage1_slab(const void* slab, int dtype, int64_t stripes, int64_t cols, 
   a.sm_count = sm_count_of_current_device();
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
+  a.out_keys = nullptr;
   a.stream = static_cast<cudaStream_t>(stream);
   return sweep_dispatch(a, dtype);
 }
@@ -286,6 +288,52 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
   ws += cand_v;
   int64_t* cand_idx = reinterpret_cast<int64_t*>(ws);
   ws += cand_i;
+  // 8- and 16-bit elements, interleaved buckets, rows the one-block select takes:
+  // stage 1 hands its packed queue entries (4 bytes per candidate, in the space
+  // of the candidate values) straight to a select that works on them; values and
+  // positions are rebuilt for the k winners only.  Shapes without packed entries
+  // (too many stripes, stripes split over blocks) fall through to the plain form.
+  if (interleaved && s <= 2 && k0 <= select_packed_max_k0() && j >= 1 && j <= 4 && k0 % j == 0 && k0 <= n &&
+      rows > 0 && n > 0 && x != nullptr && out_vals != nullptr && out_idx != nullptr && row_stride >= 0 &&
+      out_row_stride >= 0 && static_cast<size_t>(rows) * k0 * 4 <= cand_v + cand_i) {
+    SweepLaunch a;
+    a.x = x;
+    a.out_vals = nullptr;
+    a.out_idx = nullptr;
+    a.rows = rows;
+    a.n = n;
+    a.row_stride = row_stride;
+    a.out_row_stride = k0;
+    a.b = k0 / j;
+    a.stripe_stride = a.b;
+    a.idx_stride = a.b;
+    a.idx_offset = 0;
+    a.j = j;
+    a.first_wins = false;
+    a.sm_count = sm_count_of_current_device();
+    a.workspace = nullptr;
+    a.workspace_bytes = 0;
+    a.out_keys = static_cast<uint32_t*>(cand_vals);
+    a.stream = static_cast<cudaStream_t>(stream);
+    const int prc = sweep_dispatch(a, dtype);
+    if (prc == ATK_OK) {
+      SelectPackedLaunch sp;
+      sp.keys = a.out_keys;
+      sp.rows = rows;
+      sp.k0 = k0;
+      sp.k = k;
+      sp.x = x;
+      sp.x_row_stride = row_stride;
+      sp.b = a.b;
+      sp.j = j;
+      sp.out_vals = out_vals;
+      sp.out_idx = reinterpret_cast<long long*>(out_idx);
+      sp.out_row_stride = out_row_stride;
+      sp.stream = a.stream;
+      return launch_select_packed(sp, dtype);
+    }
+    if (prc != kPackedUnavailable) return prc;
+  }
   int rc = atk_stage1(x, dtype, rows, n, row_stride, k0, j, interleaved, mode, cand_vals, cand_idx, k0,
                       split_ws, split_bytes, stream);
   if (rc != ATK_OK) return rc;
@@ -319,6 +367,7 @@ int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64
     a.sm_count = sm_count_of_current_device();
     a.workspace = workspace;
     a.workspace_bytes = workspace_bytes;
+    a.out_keys = nullptr;
     a.stream = static_cast<cudaStream_t>(stream);
     return sweep_dispatch(a, dtype);
   }

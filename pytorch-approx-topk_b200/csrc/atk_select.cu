@@ -16,6 +16,7 @@
 
 #include "atk_select.cuh"
 #include "atk_block_select.cuh"
+#include "atk_queue.cuh"
 
 namespace atk {
 namespace {
@@ -322,6 +323,146 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
       if (pos[i] >= 0 && rel < static_cast<uint32_t>(tile)) {
         sval[rel] = raw[i];
         sidx[rel] = kPrefetchIdx ? pidx[kPrefetchIdx ? i : 0] : irow[slot0 + i];
+      }
+    }
+    __syncthreads();
+    const int cnt = k - base < tile ? k - base : tile;
+    stage_copy_out<Bits>(sidx, sval, cnt, ovrow + base, oirow + base, tid, nthr, vec_out);
+    if (base + tile < k) __syncthreads();
+  }
+}
+
+// ------------------------------------------------- small path, packed hand-off
+// Same selection as select_row_kernel on the packed queue entries of stage 1:
+// the top bits of an entry are the order-preserving image of the value (the
+// radix digits), the low bits the stripe.  Nothing but the entries is read;
+// value bits and positions are rebuilt for the winners only.
+template <typename T, int ITEMS, int MAXT, bool FULL>
+__global__ void __launch_bounds__(MAXT)
+select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const T* __restrict__ x,
+                         long long x_row_stride, long long b, int j,
+                         typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
+                         long long out_row_stride, int vec_ok) {
+  using Bits = typename ElemTraits<T>::Bits;
+  using PQ = PackedQueue<T, 1, false>;
+  using Img = PackedImage<T>;
+  constexpr int kPasses = PQ::kBits / 8;
+  constexpr uint32_t kValMask = ~PQ::kStripeMask;
+  __shared__ __align__(16) uint32_t hist[256 * kPasses];
+  __shared__ uint32_t misc[2];
+  __shared__ uint32_t wsum[32];
+
+  const int tid = threadIdx.x;
+  const int nthr = blockDim.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const long long row = blockIdx.x;
+  const uint32_t* krow = keys + row * k0;
+  const int slot0 = tid * ITEMS;
+  for (int i = tid; i < 256 * kPasses; i += nthr) hist[i] = 0;
+  int valid = ITEMS;
+  if (!FULL) {
+    valid = k0 - slot0;
+    valid = valid < 0 ? 0 : (valid > ITEMS ? ITEMS : valid);
+  }
+  uint32_t key[ITEMS];
+  load_items<uint32_t, ITEMS>(krow, slot0, slot0 + valid, FULL || (vec_ok && valid == ITEMS), key);
+  __syncthreads();   // histograms are clear
+
+  uint32_t prefix = 0, mask = 0;
+  uint32_t need = static_cast<uint32_t>(k);
+#pragma unroll
+  for (int pass = 0; pass < kPasses; ++pass) {
+    const int shift = 24 - 8 * pass;
+    uint32_t* h = hist + 256 * pass;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      bool in = FULL || i < valid;
+      if (pass > 0) in = in && (key[i] & mask) == prefix;
+      if (in) atomicAdd(&h[(key[i] >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t digit, new_need;
+      pick_digit_all(h, need, lane, digit, new_need);
+      if (lane == 0) {
+        misc[0] = digit;
+        misc[1] = new_need;
+      }
+    }
+    __syncthreads();
+    prefix |= misc[0] << shift;
+    mask |= 255u << shift;
+    need = misc[1];
+  }
+
+  // per-thread counts of entries above / on the threshold value, then the block scan
+  uint32_t mine = 0;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const bool in = FULL || i < valid;
+    const uint32_t v = key[i] & kValMask;
+    mine += (in && v > prefix) ? 1u : 0u;
+    mine += (in && v == prefix) ? 0x10000u : 0u;
+  }
+  uint32_t incl = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += nb;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarps = (nthr + 31) >> 5;
+    const uint32_t w = lane < nwarps ? wsum[lane] : 0u;
+    uint32_t wi = w;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t nb = __shfl_up_sync(0xffffffffu, wi, off);
+      if (lane >= off) wi += nb;
+    }
+    wsum[lane] = wi - w;
+  }
+  __syncthreads();
+  const uint32_t excl = wsum[warp] + incl - mine;
+  uint32_t gt_rank = excl & 0xffffu;
+  uint32_t eq_rank = excl >> 16;
+  const uint32_t n_gt = static_cast<uint32_t>(k) - need;
+  int pos[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    pos[i] = -1;
+    if (FULL || i < valid) {
+      const uint32_t v = key[i] & kValMask;
+      if (v > prefix) {
+        pos[i] = static_cast<int>(gt_rank++);
+      } else if (v == prefix) {
+        if (eq_rank < need) pos[i] = static_cast<int>(n_gt + eq_rank);
+        ++eq_rank;
+      }
+    }
+  }
+  Bits* ovrow = out_vals + row * out_row_stride;
+  long long* oirow = out_idx + row * out_row_stride;
+  const T* xrow = x + row * x_row_stride;
+  // slot s belongs to bucket s / j
+  const int jshift = j == 1 ? 0 : (j == 2 ? 1 : (j == 4 ? 2 : -1));
+  extern __shared__ __align__(16) unsigned char stage_smem[];
+  long long* sidx = reinterpret_cast<long long*>(stage_smem);
+  const int tile = stage_tile(k);
+  Bits* sval = reinterpret_cast<Bits*>(stage_smem + stage_val_offset(tile));
+  const bool vec_out = (reinterpret_cast<uintptr_t>(ovrow) % 16 == 0) && (reinterpret_cast<uintptr_t>(oirow) % 16 == 0);
+  for (int base = 0; base < k; base += tile) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const uint32_t rel = static_cast<uint32_t>(pos[i] - base);
+      if (pos[i] >= 0 && rel < static_cast<uint32_t>(tile)) {
+        const int slot = slot0 + i;
+        const long long bucket = jshift >= 0 ? (slot >> jshift) : slot / 3;
+        const long long at = static_cast<long long>(key[i] & PQ::kStripeMask) * b + bucket;
+        sval[rel] = Img::inverse(key[i] >> PQ::kShift, xrow + at);
+        sidx[rel] = at;
       }
     }
     __syncthreads();
@@ -732,6 +873,55 @@ size_t select_workspace_bytes(int dtype, long long rows, long long k0) {
     case ATK_I8: return workspace_typed<int8_t>(rows, k0);
     case ATK_U8: return workspace_typed<uint8_t>(rows, k0);
     default: return 0;
+  }
+}
+
+namespace {
+template <typename T>
+int select_packed_typed(const SelectPackedLaunch& a) {
+  using Bits = typename ElemTraits<T>::Bits;
+  if (a.k0 > kSmallMaxK0 || a.rows >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+  const int k0 = static_cast<int>(a.k0);
+  const int k = static_cast<int>(a.k);
+  const int vec_ok = (reinterpret_cast<uintptr_t>(a.keys) % 16 == 0) && ((a.k0 * 4) % 16 == 0);
+  const unsigned rows = static_cast<unsigned>(a.rows);
+  auto threads_for = [&](int items) {
+    int t = (k0 + items - 1) / items;
+    return ((t + 31) / 32) * 32;
+  };
+  const T* x = static_cast<const T*>(a.x);
+  Bits* ov = static_cast<Bits*>(a.out_vals);
+#define ATK_LAUNCH_SELECT_PACKED(ITEMS)                                                                   \
+  do {                                                                                                    \
+    if (vec_ok && threads_for(ITEMS) * (ITEMS) == k0)                                                     \
+      select_row_packed_kernel<T, ITEMS, 512, true><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
+          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, vec_ok);           \
+    else                                                                                                  \
+      select_row_packed_kernel<T, ITEMS, 512, false><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
+          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, vec_ok);           \
+  } while (0)
+  // at least 16 bytes of entries per thread, more until the block is at most 512 wide
+  if (threads_for(4) <= kSelectRowThreads) ATK_LAUNCH_SELECT_PACKED(4);
+  else if (threads_for(8) <= kSelectRowThreads) ATK_LAUNCH_SELECT_PACKED(8);
+  else if (threads_for(16) <= kSelectRowThreads) ATK_LAUNCH_SELECT_PACKED(16);
+  else ATK_LAUNCH_SELECT_PACKED(32);
+#undef ATK_LAUNCH_SELECT_PACKED
+  note_launch();
+  return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+}
+}  // namespace
+
+long long select_packed_max_k0() { return kSmallMaxK0; }
+
+int launch_select_packed(const SelectPackedLaunch& a, int dtype) {
+  if (a.rows <= 0 || a.k <= 0) return ATK_OK;
+  switch (dtype) {
+    case ATK_F16: return select_packed_typed<__half>(a);
+    case ATK_BF16: return select_packed_typed<__nv_bfloat16>(a);
+    case ATK_I16: return select_packed_typed<int16_t>(a);
+    case ATK_I8: return select_packed_typed<int8_t>(a);
+    case ATK_U8: return select_packed_typed<uint8_t>(a);
+    default: return ATK_ERR_BAD_DTYPE;
   }
 }
 

@@ -25,4 +25,24 @@ int launch_select(const SelectLaunch& a, int dtype);
 // nothing, when the problem needs more than that array holds.
 int launch_select_static(const SelectLaunch& a, int dtype);
 
+// The select of the two-stage operator when stage 1 handed over its packed queue
+// entries (image of the value << shift | stripe; slot s belongs to bucket s / j)
+// instead of values and positions: values and positions are rebuilt only for the
+// k winners.  `x` is the operator's input (read back for the sign of a zero).
+struct SelectPackedLaunch {
+  const uint32_t* keys;       // rows x k0, dense
+  long long rows, k0, k;
+  const void* x;
+  long long x_row_stride;     // elements
+  long long b;                // buckets per row: position = stripe * b + bucket
+  int j;
+  void* out_vals;
+  long long* out_idx;
+  long long out_row_stride;
+  cudaStream_t stream;
+};
+// Rows this select takes (one block per row); longer rows use the plain hand-off.
+long long select_packed_max_k0();
+int launch_select_packed(const SelectPackedLaunch& a, int dtype);
+
 }  // namespace atk

@@ -38,6 +38,10 @@ struct SweepParams {
   int s;                     // blockDim.y: stripe splits inside the block (power of two)
   int vec_out;               // 16-byte stores are legal for both outputs
   int vec_part;              // ... and for the scratch planes of the stripe split
+  // Packed hand-off to the select (two-stage operator only): instead of values and
+  // positions the kernel writes the queue entries themselves, rows x k0 words.
+  uint32_t* out_keys;
+  int vec_keys;              // 16-byte stores are legal for out_keys
   // Cross-block stripe split: z blocks share one (row, tile); block z walks
   // stripes [z*z_chunk, (z+1)*z_chunk) and writes its partial candidates to
   // plane z of the scratch buffers (dense [z][rows][k0]); a merge kernel
@@ -154,7 +158,7 @@ __device__ __forceinline__ void sweep_merge(Q (&q)[V], uint32_t* smem, int cw, i
 // ---------------------------------------------------------------------------
 // Stage 1 only: every block handles one tile of columns of one row and writes
 // the J candidates of each bucket (slot = bucket*J + q, ascending).
-template <typename T, typename Q, int J, int V, bool SKIP, bool SIMD>
+template <typename T, typename Q, int J, int V, bool SKIP, bool SIMD, bool PACKED_OUT>
 __global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
 sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
@@ -179,6 +183,27 @@ sweep_kernel(const SweepParams p) {
   if (active) sweep_scan<T, Q, V, SKIP, SIMD>(q, p, xrow, c0, ty, S, z);
   if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
   if (!active || ty != 0) return;
+
+  if constexpr (PACKED_OUT) {
+    // The queue entries go to the select as they are: (image of the value, stripe)
+    // words, bucket c in slots c*J .. c*J+J-1, ascending.
+    static_assert(Q::kPacked, "only packed queues have entries to hand over");
+    __align__(16) uint32_t ok[V * J];
+#pragma unroll
+    for (int e = 0; e < V; ++e)
+#pragma unroll
+      for (int j = 0; j < J; ++j) ok[e * J + j] = q[e].k[j];
+    uint32_t* kdst = p.out_keys + row * (p.b * J) + c0 * J;
+    if ((V * J) % 4 == 0 && p.vec_keys) {
+#pragma unroll
+      for (int i = 0; i < V * J / 4; ++i)
+        st_out_16(reinterpret_cast<uint4*>(kdst) + i, reinterpret_cast<const uint4*>(ok)[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < V * J; ++i) kdst[i] = ok[i];
+    }
+    return;
+  }
 
   // Write-out: bucket c owns slots c*J .. c*J+J-1, ascending queue order.
   __align__(16) Bits ov[V * J];
@@ -407,8 +432,13 @@ struct SweepLaunch {
   int sm_count;
   void* workspace;          // optional scratch for splitting stripes over blocks (may be null)
   size_t workspace_bytes;
+  uint32_t* out_keys;       // non-null: hand the packed queue entries to the select instead of out_vals / out_idx
   cudaStream_t stream;
 };
+
+// Returned (nothing launched) when packed entries were asked for and this shape or
+// element type has none to give: the caller uses the plain outputs instead.
+constexpr int kPackedUnavailable = 1;
 
 // Scratch the stripe split over blocks would like for this shape, assuming the
 // widest vector path (0 when the shape fills the GPU without it).  The launch

@@ -40,6 +40,10 @@ int launch_stage1(const SweepLaunch& a) {
 
   SweepPlan pl = plan_sweep(a.rows, a.b, p.l_full, V, a.sm_count);
   const long long k0 = a.b * J;
+  constexpr bool kCanPack = Q::kPacked && !Q::kFirst;
+  if (a.out_keys != nullptr && (!kCanPack || pl.Z > 1)) return kPackedUnavailable;
+  p.out_keys = a.out_keys;
+  p.vec_keys = (reinterpret_cast<uintptr_t>(a.out_keys) % 16 == 0) && ((k0 * 4) % 16 == 0);
   if (pl.Z > 1) {
     // use as many planes as the caller's scratch holds (none: no split over blocks)
     const size_t per_z = static_cast<size_t>(a.rows) * k0 * (sizeof(Bits) + 8);
@@ -70,10 +74,20 @@ int launch_stage1(const SweepLaunch& a) {
   const dim3 block(static_cast<unsigned>(pl.cw), static_cast<unsigned>(pl.S));
   // The head test pays off once a thread walks a long column.
   const bool skip = (pl.z_chunk / pl.S) >= 256;
+  if constexpr (kCanPack) {
+    if (a.out_keys != nullptr) {
+      if (skip)
+        sweep_kernel<T, Q, J, V, true, SIMD, true><<<grid, block, smem, a.stream>>>(p);
+      else
+        sweep_kernel<T, Q, J, V, false, SIMD, true><<<grid, block, smem, a.stream>>>(p);
+      note_launch();
+      return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+    }
+  }
   if (skip)
-    sweep_kernel<T, Q, J, V, true, SIMD><<<grid, block, smem, a.stream>>>(p);
+    sweep_kernel<T, Q, J, V, true, SIMD, false><<<grid, block, smem, a.stream>>>(p);
   else
-    sweep_kernel<T, Q, J, V, false, SIMD><<<grid, block, smem, a.stream>>>(p);
+    sweep_kernel<T, Q, J, V, false, SIMD, false><<<grid, block, smem, a.stream>>>(p);
   note_launch();
   if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   if (pl.Z > 1) {
@@ -104,6 +118,7 @@ int launch_by_queue(const SweepLaunch& a) {
       return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4 && ElemTraits<T>::kHalfFloat)>(a);
     }
   }
+  if (a.out_keys != nullptr) return kPackedUnavailable;
   return launch_stage1<T, FloatQueue<T, J, FIRST>, J, V, false>(a);
 }
 
