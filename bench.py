@@ -93,20 +93,57 @@ def measured_hbm_peak() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons while a region runs.
+
+    Reads them through NVML inside this process (what nvidia-smi itself reads;
+    the library is opened once, before any timing, and a query costs
+    microseconds).  Starting an nvidia-smi process per sample was measured to
+    slow the kernels it was meant to observe by 10-20 % -- each start
+    initialises the driver's management library next to the running work -- so
+    that route is only the fallback when the NVML binding is missing."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    # NVML clocks-event-reason bits, in the order of NAMES
+    BITS = [0x8, 0x40, 0x20, 0x4]
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.samples: list[tuple[float, float, list[str]]] = []
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        self._nvml = None
+        self._handle = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            handle = None
+            try:
+                uuid = str(torch.cuda.get_device_properties(gpu_index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self._nvml, self._handle = pynvml, handle
+            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self._reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self._once()                      # the first query pays the set-up cost, outside any timing
+            self.samples.clear()
+        except Exception:
+            self._nvml = None
 
     def _once(self):
+        if self._nvml is not None:
+            try:
+                mhz = float(self._nvml.nvmlDeviceGetClockInfo(self._handle, self._nvml.NVML_CLOCK_SM))
+                mask = int(self._reasons_fn(self._handle))
+                self.samples.append((mhz, self._max, [n for n, bit in zip(self.NAMES, self.BITS) if mask & bit]))
+            except Exception:
+                pass
+            return
         try:
             out = subprocess.run(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
                                   "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
@@ -119,7 +156,7 @@ class ClockSampler:
     def _run(self):
         while not self._stop.is_set():
             self._once()
-            self._stop.wait(0.1)
+            self._stop.wait(0.02 if self._nvml is not None else 0.1)
 
     def __enter__(self):
         self._thread.start()
@@ -136,6 +173,7 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(s[0] for s in self.samples),
                 "sm_max_mhz": max(s[1] for s in self.samples), "reasons": reasons,
                 "samples": len(self.samples),
+                "source": "NVML in-process" if self._nvml is not None else "nvidia-smi",
                 "window": "timed region plus an untimed continuation of the same step loop"}
 
 
@@ -291,9 +329,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
         # neither the input nor the output of a step is still in the 126 MB L2.
         # The timed step calls the C-ABI entry point the Python operator itself
         # calls (atk_topk) with preallocated buffers: Python's custom-op dispatch
-        # costs about as much host time as a 100 us kernel takes, and a CUDA-graph
-        # replay per step adds ~10 us of launch latency, so either would measure
-        # the host, not the path.
+        # costs about as much host time as a 100 us kernel takes.  The K timed
+        # steps are captured into ONE CUDA graph (the reference's own benchmark
+        # times graph replays of many calls as well) and the replay of that graph
+        # is the timed region: launching step by step from Python puts an event
+        # record and a few microseconds of launch gap between 60-100 us kernels,
+        # which would measure the host, not the path.
         n_sets = 2
         xs = [make_input(w, rows, 1000 * rank + i, dev) for i in range(n_sets)]
         outs = [(torch.empty(rows, k, device=dev, dtype=dtype), torch.empty(rows, k, device=dev, dtype=torch.int64))
@@ -301,10 +342,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
         ws_bytes = lib.atk_topk_workspace_bytes(code, rows, n, k, j, k_mult)
         wss = [torch.empty(max(ws_bytes, 1), device=dev, dtype=torch.uint8) for _ in range(n_sets)]
 
-        def step(i):
+        def step(i, on_stream=None):
             x, (v, ix), ws = xs[i % n_sets], outs[i % n_sets], wss[i % n_sets]
             rc = lib.atk_topk(x.data_ptr(), code, rows, n, n, k, j, k_mult, 1, -1, v.data_ptr(), ix.data_ptr(), k,
-                              ws.data_ptr() if ws_bytes else None, ws_bytes, stream_ptr)
+                              ws.data_ptr() if ws_bytes else None, ws_bytes,
+                              stream_ptr if on_stream is None else on_stream)
             if rc != 0:
                 raise RuntimeError(_native.strerror(rc))
 
@@ -321,35 +363,49 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
     launches_per_step = int(lib.atk_launch_count())
     torch.cuda.synchronize(dev)
 
+    sampler = ClockSampler(local_rank)      # opens NVML now, well before the timed region
     for i in range(max(args.warmup, 3)):
         step(i)
+    graph = None
+    if not long_row:
+        # the K timed steps as one graph (buffer sets alternate inside it)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            capture_ptr = torch.cuda.current_stream(dev).cuda_stream
+            for i in range(args.steps):
+                step(i, capture_ptr)
+        graph.replay()                      # untimed: first replay uploads the graph
+        torch.cuda.synchronize(dev)
     barrier()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    with ClockSampler(local_rank) as clocks:
+    with sampler as clocks:
         barrier()
         t_begin = torch.cuda.Event(enable_timing=True)
         t_end = torch.cuda.Event(enable_timing=True)
         t_begin.record(stream)
-        for i in range(args.steps):
-            starts[i].record(stream)
-            step(i)
-            ends[i].record(stream)
+        if graph is not None:
+            graph.replay()                  # exactly args.steps steps
+        else:
+            for i in range(args.steps):
+                step(i)
         t_end.record(stream)
         barrier()
         # The timed region of a 0.1 ms kernel is shorter than one nvidia-smi
-        # sample; keep the identical step loop running (untimed) until the
-        # sampler has had about a second under this load.
+        # sample; keep the identical work running (untimed) until the sampler
+        # has had about a second under this load.
         t_probe = time.perf_counter()
         i = 0
         while time.perf_counter() - t_probe < args.clock_probe_seconds:
-            for _ in range(16):
-                step(i)
-                i += 1
+            if graph is not None:
+                graph.replay()
+            else:
+                for _ in range(16):
+                    step(i)
+                    i += 1
             torch.cuda.synchronize(dev)
     launches = launches_per_step * args.steps
     total_ms = t_begin.elapsed_time(t_end)
-    kernel_ms = statistics.mean(s.elapsed_time(e) for s, e in zip(starts, ends))
+    kernel_ms = total_ms / args.steps
 
     e2e_ms_local = float("nan")
     e2e_steps = max(3, min(args.steps, 10))
@@ -380,7 +436,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
                                "two input/output buffer sets alternated; what a step reads and writes is not in L2"),
                            timed_call=("approx_topk.distributed.topk_long_row (atk_stage1_slab, NCCL all-gather, "
                                        "atk_select)" if long_row else
-                                       "atk_topk (C ABI) on the current stream, buffers preallocated")),
+                                       "atk_topk (C ABI), buffers preallocated; the K timed steps are one CUDA graph "
+                                       "replayed once inside the timed region")),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload),
                          "alg_bytes_per_step_per_gpu": alg,

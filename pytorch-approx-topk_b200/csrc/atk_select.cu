@@ -28,6 +28,12 @@ constexpr int kLargeThreads = 256;
 // histogram and in the count kernel of the multi-block path (build knobs; more
 // cost registers and with them resident blocks: 2 measured best for 16-bit
 // elements, 4 for 32-bit ones in the count kernel).
+// Resident blocks the compiler must allow for in the packed-entry select with at
+// most eight entries per thread (2 and 3 measured alike on 1024 rows x 4096 entries,
+// 65-66 us for the whole operator; leaving it to the compiler cost 10 us).
+#ifndef ATK_SELECT_PACKED_MINBLOCKS
+#define ATK_SELECT_PACKED_MINBLOCKS 2
+#endif
 #ifndef ATK_HIST_BATCH
 #define ATK_HIST_BATCH 2
 #endif
@@ -338,7 +344,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 // radix digits), the low bits the stripe.  Nothing but the entries is read;
 // value bits and positions are rebuilt for the winners only.
 template <typename T, int ITEMS, int MAXT, bool FULL>
-__global__ void __launch_bounds__(MAXT)
+__global__ void __launch_bounds__(MAXT, ITEMS <= 8 ? ATK_SELECT_PACKED_MINBLOCKS : 1)
 select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const T* __restrict__ x,
                          long long x_row_stride, long long b, int j,
                          typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
