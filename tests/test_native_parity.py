@@ -231,6 +231,33 @@ def test_select_matches_oracle(dtype, rows, k0, k):
         assert torch.equal(v, v2) and torch.equal(i, i2)         # deterministic, order included
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.int16, torch.int8, torch.float32])
+def test_two_stage_odd_candidate_counts_and_views(dtype):
+    # Candidate counts that are not multiples of the vector width, j = 3, a
+    # strided input view: the 8/16-bit types take the packed hand-off between the
+    # stages (entries instead of values + positions), fp32 the plain one.
+    def data(rows, n, seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        if dtype.is_floating_point:
+            return torch.randn(rows, n, generator=g, device="cuda").to(dtype)
+        info = torch.iinfo(dtype)
+        return torch.randint(info.min, info.max + 1, (rows, n), generator=g, device="cuda").to(dtype)
+
+    for seed, (rows, n, k, j, k_mult) in enumerate([(5, 1000, 9, 3, 2), (3, 777, 5, 1, 3), (2, 4099, 14, 2, 5),
+                                                    (4, 50000, 1023, 1, 3), (1, 300, 21, 3, 4)]):
+        x = data(rows, n, 700 + seed)
+        v, i = api.topk(x, k, j, k_mult, True)
+        ov, oi = oracle.topk(x.cpu(), k, j, k_mult, True)
+        assert_valid_selection(x, v, i, ov)
+        if dtype == torch.float32:
+            assert_pairs_identical(v, i, ov, oi)
+    base = data(6, 2100, 710)
+    view = base[:, 50:2050]                      # row stride 2100, 100-byte offset
+    v, i = api.topk(view, 64, 2, 2, True)
+    ov, oi = oracle.topk(view.cpu().contiguous(), 64, 2, 2, True)
+    assert_valid_selection(view, v, i, ov)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("j,k_mult", [(1, 2), (2, 2), (4, 2), (2, 4), (1, 16)])
 def test_topk_two_stage_matches_oracle(dtype, j, k_mult):
