@@ -164,3 +164,17 @@ def test_bucket_matches_reference_fixtures(golden):
 
 def test_topk_protocol_is_exported():
     assert hasattr(Topk, "__call__")
+
+
+def test_bench_clock_sampler_degrades_without_a_gpu():
+    # no driver here: neither NVML nor nvidia-smi answers, the summary says so instead of failing
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("atk_bench_main", Path(__file__).resolve().parents[1] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    with bench.ClockSampler(0) as sampler:
+        pass
+    summary = sampler.summary()
+    assert summary["samples"] == 0 and summary["reasons"] == [] and summary["sm_mhz"] is None
