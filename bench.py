@@ -370,13 +370,19 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
     if not long_row:
         # the K timed steps as one graph (buffer sets alternate inside it)
         torch.cuda.synchronize(dev)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            capture_ptr = torch.cuda.current_stream(dev).cuda_stream
-            for i in range(args.steps):
-                step(i, capture_ptr)
-        graph.replay()                      # untimed: first replay uploads the graph
-        torch.cuda.synchronize(dev)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                capture_ptr = torch.cuda.current_stream(dev).cuda_stream
+                for i in range(args.steps):
+                    step(i, capture_ptr)
+            graph.replay()                  # untimed: first replay uploads the graph
+            torch.cuda.synchronize(dev)
+        except Exception as exc:            # time the plain step loop instead, and say so
+            print(f"bench: graph capture of the timed steps failed ({exc}); timing direct launches",
+                  file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize(dev)
     barrier()
     with sampler as clocks:
         barrier()
@@ -436,8 +442,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
                                "two input/output buffer sets alternated; what a step reads and writes is not in L2"),
                            timed_call=("approx_topk.distributed.topk_long_row (atk_stage1_slab, NCCL all-gather, "
                                        "atk_select)" if long_row else
-                                       "atk_topk (C ABI), buffers preallocated; the K timed steps are one CUDA graph "
-                                       "replayed once inside the timed region")),
+                                       "atk_topk (C ABI), buffers preallocated; " +
+                                       ("the K timed steps are one CUDA graph replayed once inside the timed region"
+                                        if graph is not None else "K direct launches on the current stream"))),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload),
                          "alg_bytes_per_step_per_gpu": alg,
