@@ -41,7 +41,7 @@ struct SelectPackedLaunch {
   long long out_row_stride;
   cudaStream_t stream;
 };
-// Rows this select takes (one block per row); longer rows use the plain hand-off.
+// Longest row this select takes (one block per row); longer rows use the plain hand-off.
 long long select_packed_max_k0();
 int launch_select_packed(const SelectPackedLaunch& a, int dtype);
 
