@@ -178,3 +178,23 @@ def test_bench_clock_sampler_degrades_without_a_gpu():
         pass
     summary = sampler.summary()
     assert summary["samples"] == 0 and summary["reasons"] == [] and summary["sm_mhz"] is None
+
+
+def test_every_element_type_of_the_reference_dispatch_has_a_code():
+    from approx_topk import _native
+
+    want = {torch.float32, torch.float16, torch.bfloat16, torch.float64,
+            torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8}
+    assert set(_native.DTYPE_CODES) == want
+    assert sorted(_native.DTYPE_CODES.values()) == list(range(9))
+    with pytest.raises(RuntimeError, match="not supported"):
+        _native.dtype_code(torch.bool)
+
+
+def test_gather_checks_come_before_any_native_call():
+    from approx_topk.gather import gather_records
+
+    src = torch.ones(2, 10, 4)
+    idx = torch.zeros(2, 3, dtype=torch.int64)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        gather_records(src, idx)            # no CPU path, and it says so
