@@ -7,9 +7,17 @@
  * device (or, where stated, host) pointers and sizes, launches on the stream it
  * is given, never allocates device memory (the caller owns all buffers and the
  * workspace), never synchronises unless stated, never throws and never aborts:
- * it returns ATK_OK (0) or a negative ATK_ERR_* code.  All entry points are
- * re-entrant and may be called concurrently from several host threads on
- * different streams.  The device the pointers live on must be current.
+ * it returns ATK_OK (0) or a negative ATK_ERR_* code.  All entry points except
+ * atk_select_static are re-entrant and may be called concurrently from several
+ * host threads on different streams (atk_select_static shares one built-in
+ * scratch array per device: see its description).  The device the pointers
+ * live on must be current.
+ *
+ * NaN inputs are outside the contract for every element type and every entry
+ * point, as they are in the reference (its insertion loop makes the result
+ * depend on the scan order): nothing crashes or hangs, every returned index is
+ * a position of the row, but which elements are returned next to a NaN is
+ * unspecified and may depend on the launch shape.
  *
  * Reference interfaces replaced (paths inside the reference project):
  *   approx_topk/priority_queue_approx_topk.cu:378-387,523-525  PriorityQueueTopK (pybind)

@@ -72,6 +72,9 @@ def slab_of_row(row: Tensor, total_buckets: int, rank: int, world: int) -> Tenso
 def _native_stage1_slab(slab: Tensor, total_buckets: int, col_offset: int, j: int) -> tuple[Tensor, Tensor]:
     _native.require_cuda(slab)
     _native.require_device(slab.device)
+    # the kernel reads a dense stripes x cols array: a strided view (a column
+    # range cut out of the full row) is copied, never read through its base pointer
+    slab = slab.contiguous()
     stripes, cols = slab.shape
     vals = torch.empty(cols * j, device=slab.device, dtype=slab.dtype)
     idx = torch.empty(cols * j, device=slab.device, dtype=torch.int64)

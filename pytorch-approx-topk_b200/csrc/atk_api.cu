@@ -12,6 +12,23 @@ namespace atk {
 static thread_local long long g_launches = 0;
 void note_launch(int n) { g_launches += n; }
 
+// Lazily cached SM count per device.  Together with the per-device address cache and
+// the built-in scratch array of atk_select_static (atk_select.cu) this is all the
+// global state the library has.
+int sm_count_of_current_device() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < 64) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0 && dev < 64) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
 namespace {
 
 int elem_size(int dtype) {
@@ -30,21 +47,6 @@ int elem_size(int dtype) {
 }
 
 size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
-
-// Lazily cached SM count per device (the only global state of the library).
-int sm_count_of_current_device() {
-  static std::atomic<int> cache[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-  if (dev >= 0 && dev < 64) {
-    const int c = cache[dev].load(std::memory_order_relaxed);
-    if (c > 0) return c;
-  }
-  int n = 0;
-  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  if (dev >= 0 && dev < 64) cache[dev].store(n, std::memory_order_relaxed);
-  return n;
-}
 
 int sweep_dispatch(const SweepLaunch& a, int dtype) {
   switch (dtype) {

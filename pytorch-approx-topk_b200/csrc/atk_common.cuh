@@ -13,6 +13,9 @@ namespace atk {
 // Thread-local launch counter behind atk_launch_count().
 void note_launch(int n = 1);
 
+// Number of SMs of the current device (queried once per device, then cached).
+int sm_count_of_current_device();
+
 // Sentinel stripe numbers of never-filled queue slots.  With the "last wins"
 // tie rule a real element must outrank the sentinel at equal value (-inf), so
 // the sentinel index is below every real index; with "first wins" above.

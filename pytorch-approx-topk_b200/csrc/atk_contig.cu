@@ -354,7 +354,7 @@ int launch_typed(const ContigLaunch& a) {
     note_launch();
     return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
   }
-  if (p.base >= 8192 && a.rows * a.b * 32 < static_cast<long long>(148) * 1024) {
+  if (p.base >= 8192 && a.rows * a.b * 32 < static_cast<long long>(sm_count_of_current_device()) * 1024) {
     // few, very long buckets: a block per bucket
     if (a.rows * a.b >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     contig_block_kernel<T, J, FIRST><<<static_cast<unsigned>(a.rows * a.b), 256, 0, a.stream>>>(p);

@@ -40,7 +40,7 @@ int launch_gather(const void* src, long long rows, long long n, long long record
   const long long total = rows * k;
   const long long per_block = 256 / lanes;
   long long blocks = (total + per_block - 1) / per_block;
-  const long long cap = 148ll * 8 * 4;          // a few waves; the loop covers the rest
+  const long long cap = static_cast<long long>(sm_count_of_current_device()) * 8 * 4;          // a few waves; the loop covers the rest
   if (blocks > cap) blocks = cap;
   gather_records_kernel<P><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       static_cast<const unsigned char*>(src), rows, n, pieces, src_row_stride_bytes, idx, k, idx_row_stride,

@@ -839,7 +839,8 @@ int select_typed(const SelectLaunch& a) {
   // The histogram and count blocks loop over several chunks when there are many
   // more chunks than the GPU holds blocks, so that the per-block epilogue (global
   // flush, fence, ticket) is paid once per group of chunks.
-  long long cpb = (a.rows * chunks + 148ll * 6 - 1) / (148ll * 6);
+  const long long sms = sm_count_of_current_device();
+  long long cpb = (a.rows * chunks + sms * 6 - 1) / (sms * 6);
   if (cpb < 1) cpb = 1;
   if (cpb > 64) cpb = 64;
   const long long groups = (chunks + cpb - 1) / cpb;
@@ -853,7 +854,7 @@ int select_typed(const SelectLaunch& a) {
         cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
   // count: one warp per cpw chunks, about one wave of blocks (every block ends with a fence and a ticket)
   constexpr int kWarps = kLargeThreads / 32;
-  long long cpw = (a.rows * chunks + 148ll * 8 * kWarps - 1) / (148ll * 8 * kWarps);
+  long long cpw = (a.rows * chunks + sms * 8 * kWarps - 1) / (sms * 8 * kWarps);
   if (cpw < 1) cpw = 1;
   if (cpw > 16) cpw = 16;
   const dim3 grid_c(static_cast<unsigned>((chunks + kWarps * cpw - 1) / (kWarps * cpw)), static_cast<unsigned>(a.rows));

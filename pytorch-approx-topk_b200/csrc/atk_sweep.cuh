@@ -362,13 +362,23 @@ struct SweepPlan {
   long long cw, tiles, S, Z, z_chunk;
 };
 
-// Equal stripe ranges for Z blocks, with Z lowered so that no range is empty
-// (the last block must own the ragged last stripe).
+// Most entries a queue holds (J <= kMaxJ); every block of a stripe split must
+// walk at least that many complete stripes per in-block split, so that no
+// never-filled queue slot reaches the scratch planes (a never-filled packed
+// entry would decode to a made-up element there).
+constexpr long long kMaxJ = 4;
+
+// Equal stripe ranges for Z blocks, with Z lowered so that every range holds at
+// least kMaxJ stripes for each of the S in-block splits.  The last block walks
+// to the end of the column (and owns the ragged last stripe), so a short
+// remainder is folded into it instead of getting a block of its own.
 inline void set_chunks(SweepPlan& pl, long long l_full) {
   if (pl.Z < 1) pl.Z = 1;
+  const long long least = kMaxJ * (pl.S > 0 ? pl.S : 1);
   pl.z_chunk = (l_full + pl.Z - 1) / pl.Z;
-  if (pl.z_chunk < 1) pl.z_chunk = 1;
-  const long long used = (l_full + pl.z_chunk - 1) / pl.z_chunk;
+  if (pl.z_chunk < least) pl.z_chunk = least;
+  long long used = (l_full + pl.z_chunk - 1) / pl.z_chunk;
+  while (used > 1 && l_full - (used - 1) * pl.z_chunk < least) --used;
   pl.Z = used >= 1 ? used : 1;
 }
 

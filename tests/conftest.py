@@ -16,10 +16,14 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100); run with -m gpu on a B200")
 
 
-def pytest_collection_modifyitems(config, items):
-    # GPU tests must never be silently skipped on a GPU box: they fail loudly
-    # if CUDA is missing when explicitly selected with -m gpu.
-    pass
+def pytest_runtest_setup(item):
+    # A test marked `gpu` that is run on a machine without a CUDA device fails
+    # (it is never skipped): select with -m "not gpu" where there is no GPU.
+    if item.get_closest_marker("gpu") is not None:
+        import torch
+
+        if not torch.cuda.is_available():
+            pytest.fail("this test is marked `gpu` and needs a CUDA device; run the CPU suite with -m \"not gpu\"")
 
 
 @pytest.fixture(scope="session")

@@ -1,14 +1,18 @@
 """Access to the reference's own CUDA operator for GPU parity tests (test infrastructure).
 
 ``oracle/build_ref.py`` compiles the reference's CUDA file, unmodified and in
-place, into ``oracle/_ref/atk_reference_cuda.so``.  When that file is present
-the GPU tests compare the new kernels with it on the same inputs; when it is
-absent those comparisons are skipped (the C oracle comparisons still run).
+place, into ``oracle/_ref/atk_reference_cuda.so``.  The GPU tests compare the new
+kernels with it on the same inputs.  These comparisons are the strongest parity
+evidence there is, so a missing file FAILS them (:func:`require`); only an
+explicit ``ATK_ALLOW_MISSING_REFERENCE=1`` in the environment turns the failure
+into a skip (for a machine that has neither the reference checkout nor the
+prebuilt module).
 """
 
 from __future__ import annotations
 
 import importlib.util
+import os
 from functools import cache
 from pathlib import Path
 
@@ -29,6 +33,19 @@ def module():
 
 def available() -> bool:
     return module() is not None
+
+
+def require() -> None:
+    """Call first in every test that compares with the reference's CUDA operator."""
+    if available():
+        return
+    import pytest
+
+    msg = (f"{_SO} is missing: build it with `python oracle/build_ref.py --reference-root <reference checkout>` "
+           "(or set ATK_ALLOW_MISSING_REFERENCE=1 to skip the comparisons with the reference's CUDA operator)")
+    if os.environ.get("ATK_ALLOW_MISSING_REFERENCE") == "1":
+        pytest.skip(msg)
+    pytest.fail(msg)
 
 
 def reference_topk(xs, k, dim=-1, j=1, k_mult=1, interleaved=True, multithread_buckets=False):

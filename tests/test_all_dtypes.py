@@ -205,11 +205,11 @@ def test_unsupported_dtype_is_rejected_clearly():
         topk_torch(x, k=4, dim=1, interleaved=True)
 
 
-@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
 @pytest.mark.parametrize("dtype", WIDE)
 @pytest.mark.parametrize("j", [1, 2, 3, 4])
 @pytest.mark.parametrize("interleaved", [True, False])
 def test_stage1_matches_reference_cuda_operator(dtype, j, interleaved):
+    refcuda.require()
     for seed, (rows, n, k0) in enumerate(GEOMETRIES[:10]):
         k0 = (k0 // j) * j
         for dist in ("full", "ties"):
@@ -223,10 +223,10 @@ def test_stage1_matches_reference_cuda_operator(dtype, j, interleaved):
             assert torch.equal(i, ri), (dtype, j, interleaved, rows, n, k0, dist)
 
 
-@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
 @pytest.mark.parametrize("dtype", WIDE)
 @pytest.mark.parametrize("j,k_mult", [(2, 1), (4, 2), (1, 4)])
 def test_topk_matches_reference_cuda_operator(dtype, j, k_mult):
+    refcuda.require()
     for seed, (rows, n, k) in enumerate([(8, 4096, 64), (3, 10007, 32), (2, 65536, 1024)]):
         x = make(rows, n, dtype, 200 + seed)
         if dtype == torch.float64:

@@ -198,3 +198,31 @@ def test_gather_checks_come_before_any_native_call():
     idx = torch.zeros(2, 3, dtype=torch.int64)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         gather_records(src, idx)            # no CPU path, and it says so
+
+
+def test_reference_cpu_tests_pass_unmodified_against_this_package():
+    # Where the reference checkout is present, its own CPU-runnable test files are
+    # collected as they are and run against THIS package (the module paths are the
+    # same).  The reference's GPU tests need both a GPU and the checkout, which are
+    # never on one machine here; tests/test_priority_queue.py restates them.
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    ref = Path(os.environ.get("ATK_REFERENCE_ROOT", root.parent / "reference"))
+    files = [ref / "tests" / "test_autobucket.py", ref / "tests" / "test_bucket_argmax.py"]
+    if not all(f.exists() for f in files):
+        pytest.skip("reference checkout not present on this machine")
+    code = (
+        "import sys, pytest, approx_topk\n"
+        "assert 'pytorch-approx-topk_b200' in approx_topk.__file__, approx_topk.__file__\n"
+        f"sys.exit(pytest.main(['-q', '-p', 'no:cacheprovider', '--rootdir', {str(root)!r}, "
+        f"{str(files[0])!r}, {str(files[1]) + '::test_batch_contiguous'!r}]))\n"
+    )
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(root), str(root / "pytorch-approx-topk_b200")]))
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(root), env=env,
+                         timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert " passed" in res.stdout and "failed" not in res.stdout

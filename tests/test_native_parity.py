@@ -128,6 +128,34 @@ def test_stage1_stripes_split_over_blocks(dtype, j):
             assert torch.equal(bits(v), bits(ov)) and torch.equal(i.cpu(), oi), (rows, n, k0, dist)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32, torch.int16, torch.int8])
+@pytest.mark.parametrize("j", [1, 2, 3, 4])
+def test_stripe_split_with_a_short_remainder_has_no_made_up_candidates(dtype, j):
+    # Stripe counts that leave the last block of a split fewer stripes than a queue
+    # has entries (16385 = 128 * 128 + 1, 129 * 127 + 2, ...) on rows whose values
+    # are all negative (log-probabilities): a never-filled queue slot written to a
+    # scratch plane would outrank every real element.  b = 17 is not a multiple of
+    # the vector width, so 16-bit rows take the scalar packed path.
+    for b, stripes in [(17, 16385), (17, 129 * 127 + 2), (24, 16386), (8, 40001), (17, 16384 + 3)]:
+        n = b * stripes
+        k0 = b * j
+        g = torch.Generator(device="cuda").manual_seed(b + stripes + j)
+        if dtype.is_floating_point:
+            x = (-torch.rand(1, n, device="cuda", generator=g) - 0.5).to(dtype)
+        else:
+            info = torch.iinfo(dtype)
+            x = torch.randint(info.min, min(-1, info.min // 2 + 2), (1, n), device="cuda", generator=g).to(dtype)
+        ov, oi = oracle.stage1(x.cpu(), k0, j, True)
+        for use_workspace in (True, False):
+            v, i = api.stage1(x, k0, j, True, use_workspace=use_workspace)
+            assert torch.equal(v.cpu(), ov) and torch.equal(i.cpu(), oi), (dtype, b, stripes, j, use_workspace)
+        if j == 4:                          # through the operator, which always passes the workspace
+            from approx_topk import topk
+
+            tv, ti = topk(x, k0, -1, j=j)
+            assert torch.equal(tv.cpu(), ov) and torch.equal(ti.cpu(), oi)
+
+
 def test_operator_single_row_small_k_uses_the_split_and_matches_oracle():
     from approx_topk import topk
     from approx_topk.experimental.bucketed_argmax import topk_torch
@@ -169,11 +197,11 @@ def test_stage1_row_stride_and_unaligned_base():
     assert torch.equal(bits(v), bits(ov)) and torch.equal(i.cpu(), oi)
 
 
-@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("j", [1, 2, 3, 4])
 @pytest.mark.parametrize("interleaved", [True, False])
 def test_stage1_matches_reference_cuda_operator(dtype, j, interleaved):
+    refcuda.require()
     for seed, (rows, n, k0) in enumerate(GEOMETRIES):
         k0 = (k0 // j) * j
         if k0 == 0:
@@ -187,10 +215,10 @@ def test_stage1_matches_reference_cuda_operator(dtype, j, interleaved):
             assert torch.equal(i, ri), (dtype, j, interleaved, rows, n, k0, dist)
 
 
-@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("j,k_mult", [(1, 1), (2, 1), (4, 2), (2, 4), (1, 4)])
 def test_topk_matches_reference_cuda_operator(dtype, j, k_mult):
+    refcuda.require()
     for seed, (rows, n, k) in enumerate([(8, 4096, 64), (3, 10007, 32), (2, 65536, 1024)]):
         x = make(rows, n, dtype, 200 + seed)
         v, i = api.topk(x, k, j, k_mult, True)
@@ -202,9 +230,9 @@ def test_topk_matches_reference_cuda_operator(dtype, j, k_mult):
         assert oracle.recall(x.cpu(), v.cpu()) == oracle.recall(x.cpu(), rv.cpu())
 
 
-@pytest.mark.skipif(not refcuda.available(), reason="reference CUDA operator not built (oracle/build_ref.py)")
 @pytest.mark.parametrize("j", [1, 2, 4])
 def test_block_per_bucket_reference_kernel_same_selection(j):
+    refcuda.require()
     # The reference's 64-thread-per-bucket kernel must select the same set on tie-free rows.
     x = make(4, 16384, torch.float32, 77)
     v, i = api.stage1(x, 32 * j, j, True)
@@ -274,9 +302,9 @@ def test_topk_two_stage_matches_oracle(dtype, j, k_mult):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("j,k_mult", [(1, 2), (2, 2), (3, 2), (4, 2), (2, 4), (1, 4)])
-def test_fused_row_kernel_matches_oracle(dtype, j, k_mult):
-    # Enough rows for the one-block-per-row kernel that keeps the candidates in
-    # shared memory: aligned, ragged (b does not divide n), unaligned rows, long
+def test_two_stage_many_rows_matches_oracle_and_two_kernel_path(dtype, j, k_mult):
+    # Many rows, so that stage 1 runs unsplit and (for 16-bit elements) hands packed
+    # entries to the select: aligned, ragged (b does not divide n), unaligned rows, long
     # columns, and the largest candidate count it takes.
     for seed, (rows, n, k) in enumerate([(96, 4096, 96), (80, 10007, 48), (77, 8190, 24), (100, 131072, 12),
                                          (75, 65536, 2040)]):
@@ -290,7 +318,7 @@ def test_fused_row_kernel_matches_oracle(dtype, j, k_mult):
             assert_valid_selection(x, v, i, ov)
             if dtype == torch.float32 and dist == "randn":
                 assert_pairs_identical(v, i, ov, oi)
-            # the fused kernel and the two-kernel path agree bit for bit (same tie choices)
+            # the operator and stage 1 + select called separately agree bit for bit (same tie choices)
             cv, ci = api.stage1(x, k * k_mult, j, True)
             sv, si = api.select(cv, ci, k)
             if not (dtype != torch.float32 and dist == "ties"):

@@ -183,3 +183,37 @@ def test_sentinel_modes():
     assert i.tolist() == [[-1, 1]]                        # -inf never enters the reference queue
     v, i = oracle.stage1(x, 2, 2, interleaved=True)       # -inf start: every slot is a real element
     assert i.tolist() == [[3, 1]]
+
+
+def test_timed_cpu_path_matches_reference_fixtures(golden, golden_all_dtypes):
+    # oracle/torch_cpu_path.py is what bench.py times as the reference's CPU path
+    # (the denominator of the speed-up); it must return what the reference's own
+    # Python returned on the same inputs.
+    from oracle.torch_cpu_path import bucketed_argmax_cpu, bucketed_topk_cpu
+
+    checked = 0
+    for (data, meta), widened in ((golden, True), (golden_all_dtypes, False)):
+        for i, m in enumerate(meta):
+            x = torch.from_numpy(data[f"c{i}_x"])
+            if widened:
+                x = x.to(DTYPES[m["dtype"]])
+            ev = torch.from_numpy(data[f"c{i}_values"])
+            ei = torch.from_numpy(data[f"c{i}_indices"])
+            if m["kind"] == "bucketed_torch_topk":
+                v, idx = bucketed_topk_cpu(x, m["k"], m["j"], m["k_mult"], m["interleaved"])
+                got = v.float() if widened else v
+                assert torch.equal(got.sort(dim=-1).values, ev), m
+                # the reference pads with the type's lowest value; a row that holds that
+                # value itself can have a padded position returned for it
+                collides = not x.dtype.is_floating_point and bool((x == torch.iinfo(x.dtype).min).any())
+                if not collides:
+                    assert torch.equal(x.gather(-1, idx), v), m
+                if not _rows_have_ties(x):
+                    assert torch.equal(idx.sort(dim=-1).values, ei), m
+            else:
+                v, idx = bucketed_argmax_cpu(x, m["k"], m["interleaved"])
+                assert torch.equal(v.float() if widened else v, ev), m
+                if not _rows_have_ties(x):
+                    assert torch.equal(idx, ei), m
+            checked += 1
+    assert checked >= 120
