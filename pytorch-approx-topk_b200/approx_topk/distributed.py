@@ -52,11 +52,21 @@ def topk_row_sharded(xs_local: Tensor, k: int, j: int = 1, k_mult: int = 1,
 
 def bucket_group(total_buckets: int, rank: int, world: int) -> tuple[int, int]:
     """Columns ``[start, stop)`` of the ``stripes x total_buckets`` view owned by ``rank``.
-    Equal groups are required so that the gathered candidate buffer is dense."""
-    if total_buckets % world:
-        raise ValueError(f"the number of buckets ({total_buckets}) must be a multiple of the world size ({world})")
-    cols = total_buckets // world
-    return rank * cols, (rank + 1) * cols
+
+    Every rank gets ``ceil(total_buckets / world)`` columns until the columns run
+    out, so when the world size does not divide the bucket count the last groups
+    are short (possibly empty).  All real columns therefore precede all padding,
+    and after an all-gather of equal-sized candidate blocks the first ``k0`` slots
+    of the gathered buffer are exactly the single-GPU candidate buffer."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    cols = group_width(total_buckets, world)
+    return min(total_buckets, rank * cols), min(total_buckets, (rank + 1) * cols)
+
+
+def group_width(total_buckets: int, world: int) -> int:
+    """Columns of a full bucket group: ``ceil(total_buckets / world)``."""
+    return -(-total_buckets // world)
 
 
 def slab_of_row(row: Tensor, total_buckets: int, rank: int, world: int) -> Tensor:
@@ -69,44 +79,139 @@ def slab_of_row(row: Tensor, total_buckets: int, rank: int, world: int) -> Tenso
     return row.view(n // total_buckets, total_buckets)[:, start:stop].contiguous()
 
 
-def _native_stage1_slab(slab: Tensor, total_buckets: int, col_offset: int, j: int) -> tuple[Tensor, Tensor]:
+def _native_stage1_slab(slab: Tensor, total_buckets: int, col_offset: int, j: int,
+                        out: tuple[Tensor, Tensor] | None = None,
+                        workspace: Tensor | None = None) -> tuple[Tensor, Tensor]:
     _native.require_cuda(slab)
     _native.require_device(slab.device)
     # the kernel reads a dense stripes x cols array: a strided view (a column
     # range cut out of the full row) is copied, never read through its base pointer
     slab = slab.contiguous()
     stripes, cols = slab.shape
-    vals = torch.empty(cols * j, device=slab.device, dtype=slab.dtype)
-    idx = torch.empty(cols * j, device=slab.device, dtype=torch.int64)
+    if out is None:
+        vals = torch.empty(cols * j, device=slab.device, dtype=slab.dtype)
+        idx = torch.empty(cols * j, device=slab.device, dtype=torch.int64)
+    else:
+        vals, idx = out
     lib = _native.lib()
     code = _native.dtype_code(slab.dtype)
     with torch.cuda.device(slab.device):
-        ws_bytes = lib.atk_stage1_slab_workspace_bytes(code, stripes, cols, j)
-        ws = torch.empty(ws_bytes, device=slab.device, dtype=torch.uint8) if ws_bytes else None
+        if workspace is None:
+            ws_bytes = lib.atk_stage1_slab_workspace_bytes(code, stripes, cols, j)
+            workspace = torch.empty(ws_bytes, device=slab.device, dtype=torch.uint8) if ws_bytes else None
+        ws_bytes = workspace.numel() if workspace is not None else 0
         status = lib.atk_stage1_slab(
             slab.data_ptr(), code, stripes, cols, total_buckets, col_offset, j,
-            vals.data_ptr(), idx.data_ptr(), ws.data_ptr() if ws is not None else None, ws_bytes,
+            vals.data_ptr(), idx.data_ptr(), workspace.data_ptr() if ws_bytes else None, ws_bytes,
             _native.current_stream_ptr(slab.device))
     _native.check(status)
     return vals, idx
 
 
-def _native_select(cand_vals: Tensor, cand_idx: Tensor, k: int) -> tuple[Tensor, Tensor]:
+def _native_select(cand_vals: Tensor, cand_idx: Tensor, k: int,
+                   out: tuple[Tensor, Tensor] | None = None,
+                   workspace: Tensor | None = None) -> tuple[Tensor, Tensor]:
     _native.require_cuda(cand_vals)
     k0 = cand_vals.numel()
     code = _native.dtype_code(cand_vals.dtype)
     lib = _native.lib()
-    vals = torch.empty(k, device=cand_vals.device, dtype=cand_vals.dtype)
-    idx = torch.empty(k, device=cand_vals.device, dtype=torch.int64)
+    if out is None:
+        vals = torch.empty(k, device=cand_vals.device, dtype=cand_vals.dtype)
+        idx = torch.empty(k, device=cand_vals.device, dtype=torch.int64)
+    else:
+        vals, idx = out
     with torch.cuda.device(cand_vals.device):
-        ws_bytes = lib.atk_select_workspace_bytes(code, 1, k0, k)
-        ws = torch.empty(ws_bytes, device=cand_vals.device, dtype=torch.uint8) if ws_bytes else None
+        if workspace is None:
+            ws_bytes = lib.atk_select_workspace_bytes(code, 1, k0, k)
+            workspace = torch.empty(ws_bytes, device=cand_vals.device, dtype=torch.uint8) if ws_bytes else None
+        ws_bytes = workspace.numel() if workspace is not None else 0
         status = lib.atk_select(cand_vals.data_ptr(), cand_idx.data_ptr(), code, 1, k0, k0, k,
                                 vals.data_ptr(), idx.data_ptr(), k,
-                                ws.data_ptr() if ws is not None else None, ws_bytes,
+                                workspace.data_ptr() if ws_bytes else None, ws_bytes,
                                 _native.current_stream_ptr(cand_vals.device))
     _native.check(status)
     return vals, idx
+
+
+class LongRowTopK:
+    """The long-row operator with every buffer allocated once.
+
+    A step (:meth:`__call__`) launches stage 1 on this rank's slab, the all-gather
+    of the candidates and the exact select, all on the current stream and without
+    allocating or synchronising, so a step can be captured in a CUDA graph
+    together with its NCCL collective.  Results are written to ``self.values`` /
+    ``self.indices`` (overwritten by the next step).
+
+    ``events``, when given to a step, receives one recorded CUDA event after each
+    phase (stage 1, exchange, select) for a per-phase breakdown.
+    """
+
+    def __init__(self, stripes: int, k: int, j: int, k_mult: int, dtype: torch.dtype,
+                 device: torch.device, group: dist.ProcessGroup | None = None):
+        if k_mult < 1:
+            raise ValueError(f"k_mult must be >=1, was {k_mult}")
+        self.k, self.j, self.k_mult = k, j, k_mult
+        self.k0 = k * k_mult
+        if self.k0 % j:
+            raise RuntimeError("topk: j must divide k")
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.total_buckets = self.k0 // j
+        self.start, self.stop = bucket_group(self.total_buckets, self.rank, self.world)
+        self.cols = self.stop - self.start
+        self.stripes = stripes
+        self.dtype, self.device = dtype, torch.device(device)
+        block = group_width(self.total_buckets, self.world) * j      # candidates per rank, padded groups included
+        lib = _native.lib()
+        code = _native.dtype_code(dtype)
+        dev = self.device
+        with torch.cuda.device(dev):
+            self.local_vals = torch.empty(block, device=dev, dtype=dtype)
+            self.local_idx = torch.empty(block, device=dev, dtype=torch.int64)
+            if self.world > 1:
+                self.cand_vals = torch.empty(block * self.world, device=dev, dtype=dtype)
+                self.cand_idx = torch.empty(block * self.world, device=dev, dtype=torch.int64)
+            else:
+                self.cand_vals, self.cand_idx = self.local_vals, self.local_idx
+            ws1 = lib.atk_stage1_slab_workspace_bytes(code, stripes, self.cols, j) if self.cols else 0
+            self.stage1_ws = torch.empty(ws1, device=dev, dtype=torch.uint8) if ws1 else None
+            if self.k0 > k:
+                ws2 = lib.atk_select_workspace_bytes(code, 1, self.k0, k)
+                self.select_ws = torch.empty(ws2, device=dev, dtype=torch.uint8) if ws2 else None
+                self.values = torch.empty(k, device=dev, dtype=dtype)
+                self.indices = torch.empty(k, device=dev, dtype=torch.int64)
+            else:
+                self.select_ws = None
+                self.values, self.indices = self.cand_vals[:k], self.cand_idx[:k]
+
+    def __call__(self, slab: Tensor, events: list | None = None) -> tuple[Tensor, Tensor]:
+        if slab.ndim != 2 or tuple(slab.shape) != (self.stripes, self.cols) or slab.dtype != self.dtype:
+            raise ValueError(f"slab must be {self.stripes} x {self.cols} of {self.dtype}, got "
+                             f"{tuple(slab.shape)} of {slab.dtype}")
+
+        def mark():
+            if events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(torch.cuda.current_stream(self.device))
+                events.append(ev)
+
+        if self.cols:
+            _native_stage1_slab(slab, self.total_buckets, self.start, self.j,
+                                out=(self.local_vals[:self.cols * self.j], self.local_idx[:self.cols * self.j]),
+                                workspace=self.stage1_ws)
+        mark()
+        if self.world > 1:
+            # rank g's block is slots [g*block, (g+1)*block); real columns fill the
+            # gathered buffer from the front, so its first k0 slots are the candidates
+            dist.all_gather_into_tensor(self.cand_vals, self.local_vals, group=self.group)
+            dist.all_gather_into_tensor(self.cand_idx, self.local_idx, group=self.group)
+        mark()
+        if self.k0 > self.k:
+            _native_select(self.cand_vals[:self.k0], self.cand_idx[:self.k0], self.k,
+                           out=(self.values, self.indices), workspace=self.select_ws)
+        mark()
+        return self.values, self.indices
 
 
 def topk_long_row(
@@ -121,13 +226,15 @@ def topk_long_row(
     """Approximate top-k of one long interleaved row sharded by bucket groups.
 
     :param slab: this rank's dense ``stripes x cols`` slab (columns
-        ``[rank*cols, (rank+1)*cols)`` of the ``stripes x b`` view, ``b = k*k_mult/j``).
+        :func:`bucket_group` of the ``stripes x b`` view, ``b = k*k_mult/j``).
     :returns: the ``k`` selected ``(values, indices)``, identical on every rank
         and identical to the single-GPU result; indices are positions in the
         full row.
 
     ``stage1`` / ``select`` default to the native kernels; they are parameters so
-    that the partitioning and the exchange can be exercised on CPU ranks.
+    that the partitioning and the exchange can be exercised on CPU ranks.  For a
+    step that is repeated (or captured in a CUDA graph) use :class:`LongRowTopK`,
+    which allocates its buffers once.
     """
     if k_mult < 1:
         raise ValueError(f"k_mult must be >=1, was {k_mult}")
@@ -143,13 +250,24 @@ def topk_long_row(
     stage1 = stage1 or _native_stage1_slab
     select = select or _native_select
 
-    local_vals, local_idx = stage1(slab, total_buckets, start, j)
+    block = group_width(total_buckets, world) * j
+    if stop > start:
+        local_vals, local_idx = stage1(slab, total_buckets, start, j)
+    else:
+        local_vals = torch.empty(0, device=slab.device, dtype=slab.dtype)
+        local_idx = torch.empty(0, device=slab.device, dtype=torch.int64)
     if world > 1:
-        cand_vals = torch.empty(k0, device=slab.device, dtype=slab.dtype)
-        cand_idx = torch.empty(k0, device=slab.device, dtype=torch.int64)
-        # rank g's candidates are slots [g*k0/G, (g+1)*k0/G): a plain all-gather
+        if local_vals.numel() < block:           # a short (or empty) last group: pad its block
+            pad = block - local_vals.numel()
+            local_vals = torch.cat([local_vals, local_vals.new_zeros(pad)])
+            local_idx = torch.cat([local_idx, local_idx.new_full((pad,), -1)])
+        cand_vals = torch.empty(block * world, device=slab.device, dtype=slab.dtype)
+        cand_idx = torch.empty(block * world, device=slab.device, dtype=torch.int64)
+        # rank g's candidates are slots [g*block, (g+1)*block): a plain all-gather;
+        # the padding of short groups lands behind the k0 real candidates
         dist.all_gather_into_tensor(cand_vals, local_vals, group=group)
         dist.all_gather_into_tensor(cand_idx, local_idx, group=group)
+        cand_vals, cand_idx = cand_vals[:k0], cand_idx[:k0]
     else:
         cand_vals, cand_idx = local_vals, local_idx
     if k0 == k:

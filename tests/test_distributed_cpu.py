@@ -28,10 +28,32 @@ def test_row_shard_covers_all_rows_once():
         atd.row_shard(10, 2, 2)
 
 
-def test_bucket_group_requires_equal_groups():
+def test_bucket_groups_pad_the_last_groups():
     assert atd.bucket_group(1024, 3, 4) == (768, 1024)
+    # the world size does not divide the bucket count: full groups first, then short or empty ones
+    assert [atd.bucket_group(10, r, 4) for r in range(4)] == [(0, 3), (3, 6), (6, 9), (9, 10)]
+    assert [atd.bucket_group(5, r, 4) for r in range(4)] == [(0, 2), (2, 4), (4, 5), (5, 5)]
+    for b in (1, 5, 10, 17, 1024):
+        for world in (1, 2, 3, 4, 8):
+            spans = [atd.bucket_group(b, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == b
+            assert all(x[1] == y[0] for x, y in zip(spans, spans[1:]))
+            assert all(x[1] - x[0] <= atd.group_width(b, world) for x in spans)
     with pytest.raises(ValueError):
-        atd.bucket_group(10, 0, 4)
+        atd.bucket_group(10, 4, 4)
+
+
+def test_slab_cut_from_a_row_view_gives_the_dense_slabs_candidates():
+    # a column range of the stripes x buckets view is strided; its candidates must be
+    # those of the dense copy (the native entry point copies such a view before reading it,
+    # which tests/test_native_parity.py checks on the GPU)
+    row = torch.randn(64 * 16, generator=torch.Generator().manual_seed(3))
+    view = row.view(64, 16)[:, 4:12]
+    assert not view.is_contiguous()
+    v, i = oracle_stage1_slab(view, 16, 4, 2)
+    dv, di = oracle_stage1_slab(view.contiguous(), 16, 4, 2)
+    assert torch.equal(v, dv) and torch.equal(i, di)
+    assert torch.equal(row[i], v)
 
 
 def oracle_stage1_slab(slab, total_buckets, col_offset, j):
@@ -69,9 +91,11 @@ def _worker(rank, world, port, k, j, k_mult, n, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("k,j,k_mult", [(64, 2, 1), (64, 4, 2), (32, 1, 4)])
-def test_long_row_two_ranks_equals_single_process(tmp_path, k, j, k_mult):
-    world, n = 2, 1 << 14
+@pytest.mark.parametrize("k,j,k_mult,world,n", [(64, 2, 1, 2, 1 << 14), (64, 4, 2, 2, 1 << 14), (32, 1, 4, 2, 1 << 14),
+                                                 (30, 2, 1, 2, 15 * 700),      # 15 buckets over 2 ranks: 8 + 7
+                                                 (10, 2, 1, 3, 5 * 512),       # 5 buckets over 3 ranks: 2 + 2 + 1
+                                                 (4, 2, 2, 3, 4 * 300)])       # 4 buckets over 3 ranks: 2 + 2 + 0
+def test_long_row_ranks_equal_single_process(tmp_path, k, j, k_mult, world, n):
     port = _free_port()
     mp.spawn(_worker, args=(world, port, k, j, k_mult, n, str(tmp_path)), nprocs=world, join=True)
     row = torch.randn(n, generator=torch.Generator().manual_seed(1234))
@@ -81,9 +105,10 @@ def test_long_row_two_ranks_equals_single_process(tmp_path, k, j, k_mult):
         assert torch.equal(v.sort().values, ev.reshape(-1).sort().values)
         assert torch.equal(i.sort().values, ei.reshape(-1).sort().values)
         assert torch.equal(row[i], v)
-    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    for v, i in results[1:]:
+        assert torch.equal(results[0][0], v) and torch.equal(results[0][1], i)
     spans = [torch.load(tmp_path / f"span{r}.pt") for r in range(world)]
-    assert spans == [(0, 5), (5, 10)]
+    assert spans == [atd.row_shard(10, r, world) for r in range(world)]
 
 
 def test_long_row_single_process_matches_oracle():

@@ -373,3 +373,34 @@ def test_long_row_entry_point_single_rank_equals_operator():
     v, i = atd.topk_long_row(slab, k, j, k_mult)
     ev, ei = api.topk(row, k, j, k_mult, True)
     assert_pairs_identical(v.view(1, -1), i.view(1, -1), ev, ei)
+
+
+def test_long_row_plan_with_preallocated_buffers_and_strided_slab():
+    # LongRowTopK (buffers allocated once, graph-capturable step) equals topk_long_row, step after
+    # step; a strided column range passed as the slab is copied, not read through its base pointer
+    from approx_topk import distributed as atd
+
+    n, k, j, k_mult = 1 << 21, 1 << 14, 4, 2      # 2^15 candidates: the multi-block select with its workspace
+    b = k * k_mult // j
+    row = make(1, n, torch.float32, 901)
+    plan = atd.LongRowTopK(n // b, k, j, k_mult, torch.float32, row.device)
+    ev, ei = api.topk(row, k, j, k_mult, True)
+    for _ in range(2):
+        v, i = plan(row.view(n // b, b))
+        assert_pairs_identical(v.view(1, -1), i.view(1, -1), ev, ei)
+    # a strided slab: columns [64, 192) of the view as one "rank" of a wider row
+    view = row.view(n // b, b)[:, 64:192]
+    assert not view.is_contiguous()
+    sv, si = atd._native_stage1_slab(view, b, 64, j)
+    dv, di = api.stage1_slab(view.contiguous(), b, 64, j)
+    assert torch.equal(bits(sv), bits(dv)) and torch.equal(si, di)
+    # CUDA-graph capture of a step (what the benchmark times)
+    g = torch.cuda.CUDAGraph()
+    slab = row.view(n // b, b)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(g):
+        plan(slab)
+    plan.values.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert_pairs_identical(plan.values.view(1, -1), plan.indices.view(1, -1), ev, ei)
