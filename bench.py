@@ -1,6 +1,7 @@
 """Benchmark of the bucketed approximate top-k hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4j1|c4j2|c5b]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--replays R] [--impl ours|reference]
+                    [--workload c2|c3|c4j1|c4j2|c5b] [--no-extra] [--no-long-row] [--no-e2e]
 
 Default workload "c2" (synthetic, seeded) is the configuration the headline
 metric is quoted on — fp32 rows of 2^20 elements ~N(0,1), k = 2^16, j = 2,
@@ -12,13 +13,25 @@ so there is no data-path collective and scaling is weak; at N = 8 the job is the
 are sharded over the GPUs (strong scaling; one all-gather of candidates).
 
 One JSON line is printed by rank 0:
-  value      rows/s of the whole job, inputs resident in HBM, timed with CUDA
-             events on the launching stream, max over ranks
+  value      rows/s of the whole job, inputs resident in HBM.  The K steps are one
+             CUDA graph; the timed region is R replays of it, each between two
+             CUDA events on the launching stream; per replay the max over ranks
+             is taken, and value / ms_per_step are the mean over the R replays
+             (min, standard error and the list are printed too)
   roofline   the step against the measured HBM copy bandwidth
   e2e        the same metric through the host-buffer API: pinned host rows in,
-             pinned host results out, copies inside the timed region
+             pinned host results out, copies inside the timed region; with the
+             time the same bytes take as bare pinned copies on every rank at once
   cpu_baseline  the reference's CPU path (torch ops on the host's cores) on a
              bounded sample of the same workload (N = 1, rank 0 only)
+  reference_cuda  the reference's own CUDA operator (compiled unmodified into
+             oracle/_ref) timed with the same graph method on the same inputs
+             (N = 1; a baseline, outside the timed region of `value`)
+  extra      short records of the other single-GPU reference configurations
+             (default workload, N = 1)
+  long_row   the one-long-row configuration (bucket groups sharded over the
+             GPUs, NCCL all-gather of candidates, exact select) at this N, with
+             CUDA-event times of its three phases
 
 --impl reference times that CPU path alone (rank 0; other ranks exit).
 """
@@ -190,6 +203,16 @@ def make_input(w: dict, rows: int, seed: int, device) -> torch.Tensor:
             end = min(off + (1 << 28), flat.numel())
             flat[off:end] = torch.randn(end - off, device=device, generator=g).to(dtype)
         return x
+    if w["data"] == "attention" and torch.device(device).type == "cpu":
+        # On the host the keys are not materialised: given q, the scores q.K_i/sqrt(128) of
+        # i.i.d. N(0,1) keys are independent N(0, |q|^2/128), so that is what is drawn.
+        q = torch.randn(rows, 1, 128, generator=g)
+        scale = q.norm(dim=-1) / 128 ** 0.5
+        x = torch.empty(rows, n, dtype=dtype)
+        for r0 in range(0, rows, 64):
+            nr = min(64, rows - r0)
+            x[r0:r0 + nr] = (torch.randn(nr, n, generator=g) * scale[r0:r0 + nr]).to(dtype)
+        return x
     if w["data"] == "attention":
         # scores of one query against n keys, head_dim 128, built 32 rows at a time
         x = torch.empty(rows, n, device=device, dtype=dtype)
@@ -211,16 +234,23 @@ def make_input(w: dict, rows: int, seed: int, device) -> torch.Tensor:
     raise ValueError(w["data"])
 
 
+def cpu_sample(w: dict, rows: int) -> tuple[torch.Tensor, int, int]:
+    """Host rows of the workload's own distribution for the CPU path: (x, k, scale).
+    The long row is sampled by a 2^26-element slice with the same bucket length;
+    `scale` is how many such slices make the row."""
+    n = min(w["n"], 1 << 26)
+    scale = w["n"] // n
+    k = max(w["k"] // scale, w["j"])
+    return make_input(dict(w, n=n), rows, 0, "cpu"), k, scale
+
+
 def cpu_path_rate(w: dict, target_seconds: float, threads: int) -> dict:
     """The reference's CPU path (oracle/torch_cpu_path.py) on a bounded sample."""
     from oracle.torch_cpu_path import bucketed_topk_cpu
 
     torch.set_num_threads(threads)
     rows = min(w["rows"], 128)
-    n = min(w["n"], 1 << 26)            # the long row is sampled by a 2^26-element slice
-    scale = w["n"] // n
-    k = max(w["k"] // scale, w["j"])
-    x = make_input(dict(w, n=n, data="randn" if w["data"] != "spikes" else "randn"), rows, 0, "cpu")
+    x, k, scale = cpu_sample(w, rows)
     bucketed_topk_cpu(x[: max(1, rows // 16)], k, w["j"], w["k_mult"], True)  # warm the thread pool
     reps, t0 = 0, time.perf_counter()
     while True:
@@ -229,8 +259,8 @@ def cpu_path_rate(w: dict, target_seconds: float, threads: int) -> dict:
         dt = time.perf_counter() - t0
         if dt >= target_seconds or reps >= 500:
             break
-    sample = (f"{reps} passes over {rows}x{n} {w['dtype']} rows (k={k}) in {dt:.1f} s, torch CPU ops restating "
-              f"the reference's autobucket path, {threads} threads")
+    sample = (f"{reps} passes over {rows}x{x.shape[-1]} {w['dtype']} rows of the workload's distribution (k={k}) in "
+              f"{dt:.1f} s, torch CPU ops restating the reference's autobucket path, {threads} threads")
     if scale > 1:
         sample += f"; a 1/{scale} slice of the row with the same bucket length, rate scaled to full rows"
     return {"value": reps * rows / dt / scale, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample}
@@ -240,11 +270,16 @@ def config_of(w: dict, name: str) -> dict:
     return {"workload": w["text"], "name": name, "rows_per_gpu": w["rows"], "n": w["n"], "k": w["k"],
             "j": w["j"], "k_mult": w["k_mult"],
             "sharding": "bucket groups of the row + all-gather of candidates" if w.get("long_row")
-            else "rows, no collective"}
+            else "rows, no collective",
+            # identical in both arms (the driver compares the two configs); it describes the GPU-timed arm
+            "l2": ("input far larger than the 126 MB L2" if w.get("long_row") else
+                   "GPU-timed arm: two input/output buffer sets alternated, what a step reads and writes is not "
+                   "in L2; CPU reference arm: every step streams the rows through the host caches")}
 
 
 def run_reference(args, rank: int) -> int:
-    """Reference arm: the reference's own CPU path on the host cores (rank 0 only)."""
+    """Reference arm: the reference's own CPU path on the host cores (rank 0 only).
+    A step is one pass over the configuration's rows (one GPU's share)."""
     if rank != 0:
         return 0
     w = WORKLOADS[args.workload]
@@ -252,27 +287,24 @@ def run_reference(args, rank: int) -> int:
     from oracle.torch_cpu_path import bucketed_topk_cpu
 
     torch.set_num_threads(threads)
-    sample_rows = min(w["rows"], 32)     # one step = a bounded sample of the batch
-    n = min(w["n"], 1 << 26)
-    scale = w["n"] // n
-    k = max(w["k"] // scale, w["j"])
-    x = make_input(dict(w, n=n, data="randn"), sample_rows, 0, "cpu")
+    x, k, scale = cpu_sample(w, w["rows"])
     for _ in range(args.warmup):
         bucketed_topk_cpu(x, k, w["j"], w["k_mult"], True)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         bucketed_topk_cpu(x, k, w["j"], w["k_mult"], True)
     dt = time.perf_counter() - t0
-    value = args.steps * sample_rows / dt / scale
-    sample = (f"{sample_rows}x{n} {w['dtype']} rows per step (k={k}), torch CPU ops restating the reference's "
-              f"autobucket path, {threads} threads")
+    value = args.steps * w["rows"] / dt / scale
+    sample = (f"{w['rows']}x{x.shape[-1]} {w['dtype']} rows per step (k={k}), torch CPU ops restating the "
+              f"reference's autobucket path, {threads} threads, GPUs unused")
+    if scale > 1:
+        sample += f"; a 1/{scale} slice of the row with the same bucket length, rate scaled to full rows"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong" if w.get("long_row") else "weak", "vs_baseline": None,
         "dtype": DTYPE_TAG[w["dtype"]], "data": "synthetic",
-        "config": dict(config_of(w, args.workload), rows_per_step=sample_rows,
-                       note="reference CPU path on host cores, each step a bounded sample; GPUs unused"),
+        "config": config_of(w, args.workload),
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -281,12 +313,192 @@ def run_reference(args, rank: int) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------
+# timing helpers (GPU)
+
+def capture_steps(step, steps: int, dev, capture_error_mode: str = "global"):
+    """The `steps` steps as one CUDA graph (None if capture is not possible)."""
+    torch.cuda.synchronize(dev)
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode=capture_error_mode):
+            ptr = torch.cuda.current_stream(dev).cuda_stream
+            for i in range(steps):
+                step(i, ptr)
+        graph.replay()                  # untimed: the first replay uploads the graph
+        torch.cuda.synchronize(dev)
+        return graph
+    except Exception as exc:            # time the plain step loop instead, and say so
+        print(f"bench: graph capture of the timed steps failed ({exc}); timing direct launches", file=sys.stderr)
+        torch.cuda.synchronize(dev)
+        return None
+
+
+def timed_replays(graph, step, steps: int, replays: int, dev, stream, barrier) -> list[float]:
+    """Milliseconds of each of `replays` passes over the `steps` steps, each pass
+    between two CUDA events on `stream`; barrier + synchronize on both sides."""
+    begins = [torch.cuda.Event(enable_timing=True) for _ in range(replays)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(replays)]
+    barrier()
+    for r in range(replays):
+        begins[r].record(stream)
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(steps):
+                step(i, None)
+        ends[r].record(stream)
+    barrier()
+    return [b.elapsed_time(e) for b, e in zip(begins, ends)]
+
+
+def spread(per_step_ms: list[float]) -> dict:
+    mean = statistics.fmean(per_step_ms)
+    sd = statistics.stdev(per_step_ms) if len(per_step_ms) > 1 else 0.0
+    return {"mean": mean, "min": min(per_step_ms), "stderr": sd / len(per_step_ms) ** 0.5}
+
+
+class RowsWorkload:
+    """Buffers and the step of a row-sharded workload on one GPU: two (input,
+    output, workspace) sets alternate so that neither the input nor the output of
+    a step is still in the 126 MB L2.  The step is the C-ABI call the Python
+    operator itself makes (atk_topk) on preallocated buffers."""
+
+    def __init__(self, w: dict, lib, native, dev, seed_base: int, stream_ptr: int):
+        self.w, self.lib, self.native, self.dev = w, lib, native, dev
+        self.dtype = DTYPES[w["dtype"]]
+        self.code = native.dtype_code(self.dtype)
+        self.rows, self.n, self.k, self.j, self.k_mult = w["rows"], w["n"], w["k"], w["j"], w["k_mult"]
+        self.stream_ptr = stream_ptr
+        self.xs = [make_input(w, self.rows, seed_base + i, dev) for i in range(2)]
+        self.outs = [(torch.empty(self.rows, self.k, device=dev, dtype=self.dtype),
+                      torch.empty(self.rows, self.k, device=dev, dtype=torch.int64)) for _ in range(2)]
+        self.ws_bytes = lib.atk_topk_workspace_bytes(self.code, self.rows, self.n, self.k, self.j, self.k_mult)
+        self.wss = [torch.empty(max(self.ws_bytes, 1), device=dev, dtype=torch.uint8) for _ in range(2)]
+
+    def step(self, i: int, on_stream=None) -> None:
+        x, (v, ix), ws = self.xs[i % 2], self.outs[i % 2], self.wss[i % 2]
+        rc = self.lib.atk_topk(x.data_ptr(), self.code, self.rows, self.n, self.n, self.k, self.j, self.k_mult, 1, -1,
+                               v.data_ptr(), ix.data_ptr(), self.k, ws.data_ptr() if self.ws_bytes else None,
+                               self.ws_bytes, self.stream_ptr if on_stream is None else on_stream)
+        if rc != 0:
+            raise RuntimeError(self.native.strerror(rc))
+
+    def launches_per_step(self) -> int:
+        self.lib.atk_reset_launch_count()
+        self.step(0)
+        return int(self.lib.atk_launch_count())
+
+
+def reference_cuda_record(wl: RowsWorkload, ours_ms: float, steps: int, replays: int, dev, stream) -> dict:
+    """The reference's CUDA operator on the same inputs, timed like `value`: its own
+    output allocation and its torch.topk + gather second stage included, as its
+    users get it.  A baseline; outside the timed region of `value`."""
+    try:
+        from oracle import reference_cuda as refcuda
+
+        if not refcuda.available():
+            return {"ms_per_step": None, "speedup": None, "unavailable": f"{refcuda.SO_PATH.name} not built"}
+        w = wl.w
+
+        def step(i, _ptr=None):
+            refcuda.reference_topk(wl.xs[i % 2], w["k"], -1, w["j"], w["k_mult"], True, False)
+
+        for i in range(3):
+            step(i)
+        graph = capture_steps(step, steps, dev)
+        ms = timed_replays(graph, step, steps, replays, dev, stream, lambda: torch.cuda.synchronize(dev))
+        sp = spread([m / steps for m in ms])
+        return {"ms_per_step": sp["mean"], "ms_per_step_min": sp["min"], "speedup": sp["mean"] / ours_ms,
+                "replays": replays, "graph": graph is not None,
+                "what": "reference priority_queue_approx_topk.cu compiled unmodified for sm_100 (thread-per-bucket "
+                        "kernel, its torch.empty outputs and torch.topk + gather second stage), same inputs"}
+    except Exception as exc:  # a baseline must never take the benchmark down
+        return {"ms_per_step": None, "speedup": None, "unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+
+
+def extra_record(name: str, lib, native, dev, stream, steps: int, replays: int, peak: float, with_reference: bool) -> dict:
+    """A short record of another single-GPU reference configuration."""
+    w = WORKLOADS[name]
+    wl = RowsWorkload(w, lib, native, dev, 5000, stream.cuda_stream)
+    launches = wl.launches_per_step()
+    for i in range(3):
+        wl.step(i)
+    graph = capture_steps(wl.step, steps, dev)
+    ms = timed_replays(graph, wl.step, steps, replays, dev, stream, lambda: torch.cuda.synchronize(dev))
+    sp = spread([m / steps for m in ms])
+    alg = alg_bytes(w, wl.rows)
+    rec = {"workload": w["text"], "ms_per_step": sp["mean"], "ms_per_step_min": sp["min"],
+           "ms_per_step_stderr": sp["stderr"], "rows_s": wl.rows / (sp["mean"] * 1e-3),
+           "frac": alg / (sp["mean"] * 1e-3) / 1e9 / peak, "alg_bytes_per_step": alg, "kernels_per_step": launches,
+           "steps": steps, "replays": replays, "graph": graph is not None,
+           "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(name)}
+    if with_reference:
+        rec["reference_cuda"] = reference_cuda_record(wl, sp["mean"], max(2, steps // 4), max(3, replays // 2), dev, stream)
+    return rec
+
+
+def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, replays: int, peak: float) -> dict | None:
+    """The one-long-row configuration at this world size (all ranks take part)."""
+    import torch.distributed as dist
+
+    from approx_topk import distributed as atd
+
+    w = WORKLOADS["c5b"]
+    n, k, j, k_mult = w["n"], w["k"], w["j"], w["k_mult"]
+    dtype = DTYPES[w["dtype"]]
+    b = k * k_mult // j
+    stripes = n // b
+    c0, c1 = atd.bucket_group(b, rank, world)
+    # This rank's bucket group as a dense stripes x cols slab, generated directly in
+    # that layout (the values are i.i.d., so the slab of a random row is a random slab).
+    slab = make_input(dict(w, n=stripes * (c1 - c0)), 1, 77 + rank, dev).view(stripes, c1 - c0)
+    plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev)
+
+    def step(i, _ptr=None):
+        plan(slab)
+
+    for i in range(3):
+        step(i)
+    # phases, from events between them on plain launches
+    phase_ms = [0.0, 0.0, 0.0]
+    for _ in range(3):
+        evs: list = []
+        torch.cuda.synchronize(dev)
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        plan(slab, events=evs)
+        torch.cuda.synchronize(dev)
+        marks = [t0] + evs
+        for p in range(3):
+            phase_ms[p] += marks[p].elapsed_time(marks[p + 1]) / 3
+    graph = capture_steps(step, steps, dev, capture_error_mode="thread_local")
+    ms = timed_replays(graph, step, steps, replays, dev, stream, barrier)
+    t = torch.tensor(ms + phase_ms, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    vals = t.tolist()
+    ms, phase_ms = vals[:replays], vals[replays:]
+    if rank != 0:
+        return None
+    sp = spread([m / steps for m in ms])
+    s = torch.empty(0, dtype=dtype).element_size()
+    alg = (n // world) * s + k * (s + 8)
+    return {"workload": w["text"], "ms_per_step": sp["mean"], "ms_per_step_min": sp["min"],
+            "ms_per_step_stderr": sp["stderr"], "rows_s": 1.0 / (sp["mean"] * 1e-3), "scaling": "strong",
+            "frac_per_gpu": alg / (sp["mean"] * 1e-3) / 1e9 / peak, "alg_bytes_per_step_per_gpu": alg,
+            "phase_ms": {"stage1": phase_ms[0], "all_gather": phase_ms[1], "select": phase_ms[2],
+                         "how": "CUDA events between the phases of plain launches, max over ranks, mean of 3 steps"},
+            "steps": steps, "replays": replays, "graph": graph is not None,
+            "timed_call": "approx_topk.distributed.LongRowTopK step (atk_stage1_slab, NCCL all-gather, atk_select)"}
+
+
 def run_ours(args, rank: int, local_rank: int, world: int) -> int:
     import torch.distributed as dist
 
     import approx_topk
     from approx_topk import _native
-    from approx_topk import distributed as atd
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path)")
@@ -302,103 +514,58 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
         torch.cuda.synchronize(dev)
 
     lib = _native.lib()
-    dtype = DTYPES[w["dtype"]]
-    code = _native.dtype_code(dtype)
-    rows, n, k, j, k_mult = w["rows"], w["n"], w["k"], w["j"], w["k_mult"]
     stream = torch.cuda.current_stream(dev)
-    stream_ptr = stream.cuda_stream
-    long_row = bool(w.get("long_row"))
+    peak, peak_src = measured_hbm_peak()
+    replays = max(1, args.replays)
 
-    if long_row:
-        # One row for the whole job; this rank holds its bucket group as a dense
-        # stripes x cols slab, generated directly in that layout (the values are
-        # i.i.d., so the slab of a random row is a random slab).
-        b = k * k_mult // j
-        c0, c1 = atd.bucket_group(b, rank, world)
-        slab = make_input(dict(w, n=(n // b) * (c1 - c0)), 1, 77 + rank, dev).view(n // b, c1 - c0)
-        result = {}
+    if w.get("long_row"):
+        # --workload c5b: the long row alone is the line
+        rec = long_row_record(rank, world, dev, stream, barrier, args.steps, replays, peak)
+        if rank == 0:
+            line = {"metric": METRIC, "value": rec["rows_s"], "unit": "rows/s", "n_gpus": world, "steps": args.steps,
+                    "warmup": 3, "ms_per_step": rec["ms_per_step"], "replays": replays,
+                    "ms_per_step_min": rec["ms_per_step_min"], "ms_per_step_stderr": rec["ms_per_step_stderr"],
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                    "dtype": DTYPE_TAG[w["dtype"]], "data": "synthetic",
+                    "config": config_of(w, args.workload), "timed_call": rec["timed_call"],
+                    "roofline": {"bound": "hbm", "achieved": rec["frac_per_gpu"] * peak, "peak": peak, "unit": "GB/s",
+                                 "frac": rec["frac_per_gpu"], "traffic": None,
+                                 "alg_bytes_per_step_per_gpu": rec["alg_bytes_per_step_per_gpu"],
+                                 "peak_source": peak_src},
+                    "e2e": None, "gpu_launches": None, "long_row": rec}
+            if world == 1 and not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_path_rate(w, args.cpu_seconds, os.cpu_count() or 1)
+            args.out.emit(json.dumps(line))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
 
-        def step(i):
-            result["out"] = atd.topk_long_row(slab, k, j, k_mult)
-
-        check = None
-        n_sets = 1
-        rows_per_rank_step = 1.0 / world
-    else:
-        # Two (input, output, workspace) buffer sets are alternated so that
-        # neither the input nor the output of a step is still in the 126 MB L2.
-        # The timed step calls the C-ABI entry point the Python operator itself
-        # calls (atk_topk) with preallocated buffers: Python's custom-op dispatch
-        # costs about as much host time as a 100 us kernel takes.  The K timed
-        # steps are captured into ONE CUDA graph (the reference's own benchmark
-        # times graph replays of many calls as well) and the replay of that graph
-        # is the timed region: launching step by step from Python puts an event
-        # record and a few microseconds of launch gap between 60-100 us kernels,
-        # which would measure the host, not the path.
-        n_sets = 2
-        xs = [make_input(w, rows, 1000 * rank + i, dev) for i in range(n_sets)]
-        outs = [(torch.empty(rows, k, device=dev, dtype=dtype), torch.empty(rows, k, device=dev, dtype=torch.int64))
-                for _ in range(n_sets)]
-        ws_bytes = lib.atk_topk_workspace_bytes(code, rows, n, k, j, k_mult)
-        wss = [torch.empty(max(ws_bytes, 1), device=dev, dtype=torch.uint8) for _ in range(n_sets)]
-
-        def step(i, on_stream=None):
-            x, (v, ix), ws = xs[i % n_sets], outs[i % n_sets], wss[i % n_sets]
-            rc = lib.atk_topk(x.data_ptr(), code, rows, n, n, k, j, k_mult, 1, -1, v.data_ptr(), ix.data_ptr(), k,
-                              ws.data_ptr() if ws_bytes else None, ws_bytes,
-                              stream_ptr if on_stream is None else on_stream)
-            if rc != 0:
-                raise RuntimeError(_native.strerror(rc))
-
-        # the public operator gives the same bits as the direct call
-        pv, pi = approx_topk.topk(xs[0], k, -1, j=j, k_mult=k_mult)
-        step(0)
-        torch.cuda.synchronize(dev)
-        assert torch.equal(pv, outs[0][0]) and torch.equal(pi, outs[0][1])
-        del pv, pi
-        rows_per_rank_step = float(rows)
-
-    lib.atk_reset_launch_count()
-    step(0)
-    launches_per_step = int(lib.atk_launch_count())
+    wl = RowsWorkload(w, lib, _native, dev, 1000 * rank, stream.cuda_stream)
+    rows, n, k, j, k_mult, dtype = wl.rows, wl.n, wl.k, wl.j, wl.k_mult, wl.dtype
+    # the public operator gives the same bits as the direct call
+    pv, pi = approx_topk.topk(wl.xs[0], k, -1, j=j, k_mult=k_mult)
+    wl.step(0)
+    torch.cuda.synchronize(dev)
+    assert torch.equal(pv, wl.outs[0][0]) and torch.equal(pi, wl.outs[0][1])
+    del pv, pi
+    launches_per_step = wl.launches_per_step()
     torch.cuda.synchronize(dev)
 
     sampler = ClockSampler(local_rank)      # opens NVML now, well before the timed region
     for i in range(max(args.warmup, 3)):
-        step(i)
-    graph = None
-    if not long_row:
-        # the K timed steps as one graph (buffer sets alternate inside it)
-        torch.cuda.synchronize(dev)
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                capture_ptr = torch.cuda.current_stream(dev).cuda_stream
-                for i in range(args.steps):
-                    step(i, capture_ptr)
-            graph.replay()                  # untimed: first replay uploads the graph
-            torch.cuda.synchronize(dev)
-        except Exception as exc:            # time the plain step loop instead, and say so
-            print(f"bench: graph capture of the timed steps failed ({exc}); timing direct launches",
-                  file=sys.stderr)
-            graph = None
-            torch.cuda.synchronize(dev)
+        wl.step(i)
+    # The K steps are captured into ONE CUDA graph (the reference's own benchmark
+    # times graph replays of many calls as well): launching step by step from
+    # Python puts an event record and a few microseconds of launch gap between
+    # 60-100 us kernels, which would measure the host, not the path.
+    graph = capture_steps(wl.step, args.steps, dev)
     barrier()
     with sampler as clocks:
-        barrier()
-        t_begin = torch.cuda.Event(enable_timing=True)
-        t_end = torch.cuda.Event(enable_timing=True)
-        t_begin.record(stream)
-        if graph is not None:
-            graph.replay()                  # exactly args.steps steps
-        else:
-            for i in range(args.steps):
-                step(i)
-        t_end.record(stream)
-        barrier()
-        # The timed region of a 0.1 ms kernel is shorter than one nvidia-smi
-        # sample; keep the identical work running (untimed) until the sampler
-        # has had about a second under this load.
+        replay_ms = timed_replays(graph, wl.step, args.steps, replays, dev, stream, barrier)
+        # The timed region of a 0.1 ms kernel is shorter than one clock sample;
+        # keep the identical work running (untimed) until the sampler has had
+        # about a second under this load.
         t_probe = time.perf_counter()
         i = 0
         while time.perf_counter() - t_probe < args.clock_probe_seconds:
@@ -406,59 +573,84 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
                 graph.replay()
             else:
                 for _ in range(16):
-                    step(i)
+                    wl.step(i)
                     i += 1
             torch.cuda.synchronize(dev)
-    launches = launches_per_step * args.steps
-    total_ms = t_begin.elapsed_time(t_end)
-    kernel_ms = total_ms / args.steps
 
-    e2e_ms_local = float("nan")
     e2e_steps = max(3, min(args.steps, 10))
-    do_e2e = not args.no_e2e and not long_row
+    do_e2e = not args.no_e2e
+    e2e_ms_local, floor_ms_local = float("nan"), float("nan")
     if do_e2e:
-        e2e_ms_local = run_e2e(w, dev, xs[0], e2e_steps, barrier)
+        e2e_ms_local, floor_ms_local = run_e2e(w, dev, wl.xs[0], e2e_steps, barrier)
 
-    times = torch.tensor([total_ms, kernel_ms, e2e_ms_local], device=dev, dtype=torch.float64)
+    times = torch.tensor(replay_ms + [e2e_ms_local, floor_ms_local], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, kernel_ms, e2e_ms = times.tolist()
+    vals = times.tolist()
+    replay_ms, e2e_ms, floor_ms = vals[:replays], vals[replays], vals[replays + 1]
 
+    line = None
     if rank == 0:
-        rows_total = rows_per_rank_step * world
-        peak, peak_src = measured_hbm_peak()
+        sp = spread([m / args.steps for m in replay_ms])
+        kernel_ms = sp["mean"]
+        rows_total = float(rows) * world
         s = torch.empty(0, dtype=dtype).element_size()
-        # bytes one GPU moves per step (the roofline is per GPU)
-        alg = alg_bytes(w, rows) if not long_row else (n // world) * s + k * (s + 8)
+        alg = alg_bytes(w, rows)            # bytes one GPU moves per step (the roofline is per GPU)
         achieved = alg / (kernel_ms * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": rows_total * args.steps / (total_ms * 1e-3), "unit": "rows/s",
+            "metric": METRIC, "value": rows_total / (kernel_ms * 1e-3), "unit": "rows/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong" if long_row else "weak",
+            "ms_per_step": kernel_ms, "replays": replays, "ms_per_step_min": sp["min"],
+            "ms_per_step_stderr": sp["stderr"], "replay_ms": replay_ms,
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": DTYPE_TAG[w["dtype"]], "data": "synthetic",
-            "config": dict(config_of(w, args.workload),
-                           l2=("input far larger than the 126 MB L2" if long_row else
-                               "two input/output buffer sets alternated; what a step reads and writes is not in L2"),
-                           timed_call=("approx_topk.distributed.topk_long_row (atk_stage1_slab, NCCL all-gather, "
-                                       "atk_select)" if long_row else
-                                       "atk_topk (C ABI), buffers preallocated; " +
-                                       ("the K timed steps are one CUDA graph replayed once inside the timed region"
-                                        if graph is not None else "K direct launches on the current stream"))),
+            "config": config_of(w, args.workload),
+            "timed_call": "atk_topk (C ABI), buffers preallocated; " +
+                          (f"the K steps are one CUDA graph, replayed {replays} times inside the timed "
+                           "region, every replay between its own pair of CUDA events"
+                           if graph is not None else "K direct launches on the current stream per replay"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload),
                          "alg_bytes_per_step_per_gpu": alg,
-                         "read_only_gbs": ((n // world) * s if long_row else rows * n * s) / (kernel_ms * 1e-3) / 1e9,
+                         "read_only_gbs": rows * n * s / (kernel_ms * 1e-3) / 1e9,
+                         "frac_of_nominal_8tbs": achieved / 8000.0,
                          "step_ms": kernel_ms, "kernels_per_step": launches_per_step,
                          "peak_source": peak_src},
             "e2e": None if not do_e2e else {
                 "value": rows_total * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s",
                 "h2d_bytes_per_step": rows * n * s, "d2h_bytes_per_step": rows * k * (s + 8),
                 "ms_per_step": e2e_ms / e2e_steps,
+                "copy_floor_ms": floor_ms / e2e_steps, "e2e_frac": floor_ms / e2e_ms,
+                "copy_floor": "the same bytes per step as bare pinned cudaMemcpyAsync copies, upload and download "
+                              "on two streams, on every rank at once (max over ranks)",
                 "api": "approx_topk.host_buffers.topk_host (atk_topk_host), pinned host buffers"},
-            "gpu_launches": launches,
+            "gpu_launches": launches_per_step * args.steps * replays,
             "clocks": clocks.summary(),
         }
+        if world == 1:
+            line["reference_cuda"] = reference_cuda_record(wl, kernel_ms, max(2, args.steps // 4),
+                                                           max(3, replays // 2), dev, stream)
+    del wl, graph
+    torch.cuda.empty_cache()
+
+    if world == 1 and args.workload == "c2" and not args.no_extra:
+        extra = {}
+        for name in ("c3", "c4j1", "c4j2"):
+            try:
+                extra[name] = extra_record(name, lib, _native, dev, stream, max(2, args.steps // 2),
+                                           max(3, replays // 2), peak, True)
+            except Exception as exc:
+                extra[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+            torch.cuda.empty_cache()
+        line["extra"] = extra
+    if args.workload == "c2" and not args.no_long_row:
+        try:
+            rec = long_row_record(rank, world, dev, stream, barrier, 5, 5, peak)
+        except Exception as exc:
+            rec = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        if rank == 0:
+            line["long_row"] = rec
+    if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_path_rate(w, args.cpu_seconds, os.cpu_count() or 1)
         args.out.emit(json.dumps(line))
@@ -468,8 +660,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
     return 0
 
 
-def run_e2e(w, dev, x_dev, e2e_steps, barrier) -> float:
-    """End to end through the host-buffer API: pinned host rows -> pinned host results."""
+def run_e2e(w, dev, x_dev, e2e_steps, barrier) -> tuple[float, float]:
+    """End to end through the host-buffer API: pinned host rows -> pinned host
+    results (milliseconds for e2e_steps steps), and the time the same bytes take
+    as bare pinned copies (upload and download on two streams at once)."""
     from approx_topk.host_buffers import topk_host
 
     xh = torch.empty(x_dev.shape, dtype=x_dev.dtype).pin_memory()
@@ -483,7 +677,31 @@ def run_e2e(w, dev, x_dev, e2e_steps, barrier) -> float:
     for _ in range(e2e_steps):
         topk_host(xh, w["k"], w["j"], w["k_mult"], device=dev, out=out)
     torch.cuda.synchronize(dev)
-    return (time.perf_counter() - t0) * 1e3
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    # copy floor: what the host link gives for the same bytes, no kernels
+    dv = torch.empty_like(out[0], device=dev)
+    di = torch.empty_like(out[1], device=dev)
+    up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def copies():
+        with torch.cuda.stream(up):
+            x_dev.copy_(xh, non_blocking=True)
+        with torch.cuda.stream(down):
+            out[0].copy_(dv, non_blocking=True)
+            out[1].copy_(di, non_blocking=True)
+
+    x_keep = x_dev.clone()
+    copies()
+    torch.cuda.synchronize(dev)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        copies()
+    torch.cuda.synchronize(dev)
+    floor_ms = (time.perf_counter() - t0) * 1e3
+    x_dev.copy_(x_keep)
+    return e2e_ms, floor_ms
 
 
 class StdoutToStderr:
@@ -504,8 +722,9 @@ class StdoutToStderr:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=50, help="K: steps per graph replay")
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--replays", type=int, default=10, help="R: timed replays of the K-step graph")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="length of the CPU-baseline sample")
@@ -513,6 +732,8 @@ def main() -> int:
     ap.add_argument("--clock-probe-seconds", type=float, default=1.0,
                     help="untimed continuation of the step loop while GPU clocks are sampled")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the records of the other configurations")
+    ap.add_argument("--no-long-row", action="store_true", help="skip the long-row record")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

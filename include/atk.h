@@ -208,8 +208,11 @@ int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64
  * memory gives full PCIe speed, pageable memory works).  Rows are processed in
  * chunks so that the upload of chunk i+1, the kernels of chunk i and the
  * download of chunk i-1 overlap.  `device_scratch` is caller-allocated device
- * memory of atk_topk_host_scratch_bytes() bytes.  Creates two internal streams
- * per call, synchronises before returning.  chunk_rows <= 0 picks a default.
+ * memory of atk_topk_host_scratch_bytes() bytes.  Works on two internal streams
+ * (created on the first call on a device and kept), synchronises before
+ * returning.  Calls that overlap on one device from several host threads are
+ * correct (each has its own scratch) but share those streams, so their work
+ * is serialised.  chunk_rows <= 0 picks a default.
  */
 size_t atk_topk_host_scratch_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j,
                                    int64_t k_mult, int64_t chunk_rows);

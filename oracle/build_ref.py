@@ -10,9 +10,9 @@ use (``approx_topk/cuda_extensions.py:12-27``).  This script compiles that file
 command (no copy of the source is made, the reference's own loader is not run)
 and writes only the resulting extension module
 ``oracle/_ref/atk_reference_cuda.so``.  The module needs a GPU to execute, so it
-is only ever called from ``-m gpu`` parity tests and from the optional
-"reference CUDA kernel" timing leg of ``bench.py``; both skip it when the file
-is absent.
+is only ever called from ``-m gpu`` parity tests (which fail when the file is
+absent) and from the "reference_cuda" baseline leg of ``bench.py`` (which
+reports the absence instead of a time).
 
 Usage:  python oracle/build_ref.py [--reference-root DIR] [--force]
 The compile takes several minutes (hundreds of template instantiations).

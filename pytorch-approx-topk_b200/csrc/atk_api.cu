@@ -2,6 +2,7 @@
 // the host-buffer pipeline.  See include/atk.h for the contract of every entry
 // point and the reference interface each one replaces.
 #include <atomic>
+#include <mutex>
 
 #include "atk_contig.cuh"
 #include "atk_select.cuh"
@@ -13,8 +14,8 @@ static thread_local long long g_launches = 0;
 void note_launch(int n) { g_launches += n; }
 
 // Lazily cached SM count per device.  Together with the per-device address cache and
-// the built-in scratch array of atk_select_static (atk_select.cu) this is all the
-// global state the library has.
+// the built-in scratch array of atk_select_static (atk_select.cu) and the two cached
+// pipeline streams per device of atk_topk_host this is all the global state the library has.
 int sm_count_of_current_device() {
   static std::atomic<int> cache[64];
   int dev = 0;
@@ -391,6 +392,32 @@ int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64
 
 // ---- host-buffer pipeline ---------------------------------------------------
 namespace {
+// The two pipeline streams of atk_topk_host, created on the first call on a
+// device and kept for the life of the process (creating and destroying two
+// streams per call cost tens of microseconds of every step).
+bool host_streams_of_current_device(cudaStream_t (&out)[2]) {
+  static std::mutex mu;
+  static cudaStream_t cache[64][2];
+  static bool ready[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ready[dev]) {
+    cudaStream_t a = nullptr, b = nullptr;
+    if (cudaStreamCreateWithFlags(&a, cudaStreamNonBlocking) != cudaSuccess) return false;
+    if (cudaStreamCreateWithFlags(&b, cudaStreamNonBlocking) != cudaSuccess) {
+      cudaStreamDestroy(a);
+      return false;
+    }
+    cache[dev][0] = a;
+    cache[dev][1] = b;
+    ready[dev] = true;
+  }
+  out[0] = cache[dev][0];
+  out[1] = cache[dev][1];
+  return true;
+}
+
 struct HostPlan {
   int64_t chunk_rows;
   size_t x_bytes, v_bytes, i_bytes, ws_bytes, slot_bytes;
@@ -435,11 +462,7 @@ int atk_topk_host(const void* x_host, int dtype, int64_t rows, int64_t n, int64_
   if (device_scratch == nullptr || scratch_bytes < 2 * p.slot_bytes) return ATK_ERR_WORKSPACE;
 
   cudaStream_t st[2] = {nullptr, nullptr};
-  if (cudaStreamCreateWithFlags(&st[0], cudaStreamNonBlocking) != cudaSuccess) return ATK_ERR_CUDA;
-  if (cudaStreamCreateWithFlags(&st[1], cudaStreamNonBlocking) != cudaSuccess) {
-    cudaStreamDestroy(st[0]);
-    return ATK_ERR_CUDA;
-  }
+  if (!host_streams_of_current_device(st)) return ATK_ERR_CUDA;
   int rc = ATK_OK;
   int64_t chunk = 0;
   for (int64_t r0 = 0; r0 < rows && rc == ATK_OK; r0 += p.chunk_rows, ++chunk) {
@@ -452,10 +475,14 @@ int atk_topk_host(const void* x_host, int dtype, int64_t rows, int64_t n, int64_
     void* dws = p.ws_bytes ? base + p.x_bytes + p.v_bytes + p.i_bytes : nullptr;
     const unsigned char* hx = static_cast<const unsigned char*>(x_host) + static_cast<size_t>(r0) * row_stride * s;
     // Work queued on a stream runs in order, so a slot is reused only after
-    // its previous download has been issued on the same stream.
-    cudaError_t e = cudaMemcpy2DAsync(dx, static_cast<size_t>(n) * s, hx, static_cast<size_t>(row_stride) * s,
-                                      static_cast<size_t>(n) * s, static_cast<size_t>(nr),
-                                      cudaMemcpyHostToDevice, st[slot]);
+    // its previous download has been issued on the same stream.  Dense rows
+    // go up as one linear copy, strided rows as a pitched one.
+    cudaError_t e;
+    if (row_stride == n)
+      e = cudaMemcpyAsync(dx, hx, static_cast<size_t>(nr) * n * s, cudaMemcpyHostToDevice, st[slot]);
+    else
+      e = cudaMemcpy2DAsync(dx, static_cast<size_t>(n) * s, hx, static_cast<size_t>(row_stride) * s,
+                            static_cast<size_t>(n) * s, static_cast<size_t>(nr), cudaMemcpyHostToDevice, st[slot]);
     if (e != cudaSuccess) { rc = ATK_ERR_CUDA; break; }
     rc = atk_topk(dx, dtype, nr, n, n, k, j, k_mult, interleaved, -1, dv, di, k, dws, p.ws_bytes, st[slot]);
     if (rc != ATK_OK) break;
@@ -466,10 +493,8 @@ int atk_topk_host(const void* x_host, int dtype, int64_t rows, int64_t n, int64_
                           st[slot]);
     if (e != cudaSuccess) rc = ATK_ERR_CUDA;
   }
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < 2; ++i)
     if (cudaStreamSynchronize(st[i]) != cudaSuccess && rc == ATK_OK) rc = ATK_ERR_CUDA;
-    cudaStreamDestroy(st[i]);
-  }
   return rc;
 }
 

@@ -47,6 +47,32 @@ def main() -> int:
             assert torch.equal(v.view(torch.int16 if v.element_size() == 2 else torch.int32),
                                ev.view(torch.int16 if ev.element_size() == 2 else torch.int32)), \
                 f"rank {rank}: values differ ({dtype}, n={n})"
+        # a bucket count the world size does not divide (padded last group), and the plan
+        # with preallocated buffers, stepped directly and as a CUDA graph holding the collective
+        for dtype, stripes, k, j, k_mult in [(torch.float32, 4096, 45, 3, 1), (torch.float16, 2048, 4098, 2, 2),
+                                             (torch.float32, 1024, 1 << 15, 4, 2)]:
+            b = k * k_mult // j
+            g = torch.Generator(device=dev).manual_seed(777)
+            row = torch.randn(stripes * b, device=dev, generator=g).to(dtype)
+            slab = atd.slab_of_row(row, b, rank, world)
+            ev, ei = approx_topk.topk(row.view(1, -1), k, -1, j=j, k_mult=k_mult)
+            ev, ei = canonical(ev.view(-1), ei.view(-1))
+            v, i = canonical(*atd.topk_long_row(slab, k, j, k_mult))
+            assert torch.equal(i, ei) and torch.equal(v, ev), f"rank {rank}: padded groups differ ({dtype}, b={b})"
+            plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev)
+            for _ in range(2):
+                v, i = canonical(*plan(slab))
+                assert torch.equal(i, ei) and torch.equal(v, ev), f"rank {rank}: plan differs ({dtype}, b={b})"
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                plan(slab)
+            plan.values.zero_()
+            for _ in range(2):
+                graph.replay()
+            torch.cuda.synchronize(dev)
+            v, i = canonical(plan.values.clone(), plan.indices.clone())
+            assert torch.equal(i, ei) and torch.equal(v, ev), f"rank {rank}: graph replay differs ({dtype}, b={b})"
         # rows: each rank computes its span; together they equal the full batch
         g = torch.Generator(device=dev).manual_seed(99)
         x = torch.randn(37, 1 << 14, device=dev, generator=g)

@@ -1,38 +1,18 @@
-"""Access to the reference's own CUDA operator for GPU parity tests (test infrastructure).
+"""The reference's own CUDA operator in the GPU parity tests (test infrastructure).
 
-``oracle/build_ref.py`` compiles the reference's CUDA file, unmodified and in
-place, into ``oracle/_ref/atk_reference_cuda.so``.  The GPU tests compare the new
-kernels with it on the same inputs.  These comparisons are the strongest parity
-evidence there is, so a missing file FAILS them (:func:`require`); only an
-explicit ``ATK_ALLOW_MISSING_REFERENCE=1`` in the environment turns the failure
-into a skip (for a machine that has neither the reference checkout nor the
-prebuilt module).
+The loader lives in ``oracle/reference_cuda.py``.  The comparisons with the
+reference's CUDA operator are the strongest parity evidence there is, so a
+missing module FAILS them (:func:`require`); only an explicit
+``ATK_ALLOW_MISSING_REFERENCE=1`` in the environment turns the failure into a
+skip (for a machine that has neither the reference checkout nor the prebuilt
+module).
 """
 
 from __future__ import annotations
 
-import importlib.util
 import os
-from functools import cache
-from pathlib import Path
 
-import torch
-
-_SO = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "atk_reference_cuda.so"
-
-
-@cache
-def module():
-    if not _SO.exists():
-        return None
-    spec = importlib.util.spec_from_file_location("atk_reference_cuda", _SO)
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    return mod
-
-
-def available() -> bool:
-    return module() is not None
+from oracle.reference_cuda import SO_PATH, available, module, reference_stage1, reference_topk  # noqa: F401
 
 
 def require() -> None:
@@ -41,30 +21,8 @@ def require() -> None:
         return
     import pytest
 
-    msg = (f"{_SO} is missing: build it with `python oracle/build_ref.py --reference-root <reference checkout>` "
+    msg = (f"{SO_PATH} is missing: build it with `python oracle/build_ref.py --reference-root <reference checkout>` "
            "(or set ATK_ALLOW_MISSING_REFERENCE=1 to skip the comparisons with the reference's CUDA operator)")
     if os.environ.get("ATK_ALLOW_MISSING_REFERENCE") == "1":
         pytest.skip(msg)
     pytest.fail(msg)
-
-
-def reference_topk(xs, k, dim=-1, j=1, k_mult=1, interleaved=True, multithread_buckets=False):
-    """What the reference's Python wrapper does around its kernel
-    (approx_topk/priority_queue.py:51-88): allocate k*k_mult candidates, run the
-    kernel, then torch.topk(sorted=False) + gather when k_mult > 1."""
-    mod = module()
-    dim = dim % xs.ndim
-    k0 = k * k_mult
-    shape = list(xs.shape)
-    shape[dim] = k0
-    vals = torch.empty(shape, device=xs.device, dtype=xs.dtype)
-    idx = torch.empty(shape, device=xs.device, dtype=torch.int64)
-    mod.PriorityQueueTopK(xs, k0, j, dim, True, interleaved, multithread_buckets, vals, idx)
-    if k0 == k:
-        return vals, idx
-    v2, i2 = torch.topk(vals, k, dim, True, sorted=False)
-    return v2, idx.gather(dim, i2)
-
-
-def reference_stage1(xs, k0, j, interleaved=True, multithread_buckets=False):
-    return reference_topk(xs, k0, -1, j, 1, interleaved, multithread_buckets)
