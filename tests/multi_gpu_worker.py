@@ -49,7 +49,7 @@ def main() -> int:
                 f"rank {rank}: values differ ({dtype}, n={n})"
         # a bucket count the world size does not divide (padded last group), and the plan
         # with preallocated buffers, stepped directly and as a CUDA graph holding the collective
-        for dtype, stripes, k, j, k_mult in [(torch.float32, 4096, 45, 3, 1), (torch.float16, 2048, 4098, 2, 2),
+        for dtype, stripes, k, j, k_mult in [(torch.float32, 4096, 45, 3, 1), (torch.float16, 2048, 4099, 2, 2),
                                              (torch.float32, 1024, 1 << 15, 4, 2)]:
             b = k * k_mult // j
             g = torch.Generator(device=dev).manual_seed(777)
