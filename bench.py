@@ -475,6 +475,9 @@ def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, rep
             phase_ms[p] += marks[p].elapsed_time(marks[p + 1]) / 3
     graph = capture_steps(step, steps, dev, capture_error_mode="thread_local")
     ms = timed_replays(graph, step, steps, replays, dev, stream, barrier)
+    used_graph = graph is not None
+    del graph                     # a graph that holds a collective must be gone before the process group is torn down
+    torch.cuda.synchronize(dev)
     t = torch.tensor(ms + phase_ms, device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -490,7 +493,7 @@ def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, rep
             "frac_per_gpu": alg / (sp["mean"] * 1e-3) / 1e9 / peak, "alg_bytes_per_step_per_gpu": alg,
             "phase_ms": {"stage1": phase_ms[0], "all_gather": phase_ms[1], "select": phase_ms[2],
                          "how": "CUDA events between the phases of plain launches, max over ranks, mean of 3 steps"},
-            "steps": steps, "replays": replays, "graph": graph is not None,
+            "steps": steps, "replays": replays, "graph": used_graph,
             "timed_call": "approx_topk.distributed.LongRowTopK step (atk_stage1_slab, NCCL all-gather, atk_select)"}
 
 

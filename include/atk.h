@@ -60,6 +60,18 @@ enum {
   ATK_ERR_SCRATCH_LIMIT = -9 /* atk_select_static: the problem needs more than the built-in scratch */
 };
 
+/* Formats of the operator's final output (atk_topk_ex).  The reference fixes
+ * int64 indices (approx_topk/priority_queue.py:65-67); the narrower ones are
+ * opt-in for consumers that do not need 64-bit positions: on the headline
+ * workload the int64 indices are two thirds of all bytes written. */
+enum {
+  ATK_OUT_I64 = 0,   /* out_vals: rows x k of dtype; out_idx: rows x k int64 (the default) */
+  ATK_OUT_I32 = 1,   /* out_vals: rows x k of dtype; out_idx: rows x k int32; needs n < 2^31 */
+  ATK_OUT_REC32 = 2  /* out_vals: rows x k records of 8 bytes {uint32 value bits (the element's
+                        bits zero-extended), int32 position}; out_idx unused (may be NULL);
+                        element types of at most 32 bits, n < 2^31 */
+};
+
 /* Library version, major*10000 + minor*100 + patch. */
 int atk_version(void);
 
@@ -187,6 +199,19 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
              int64_t k, int j, int64_t k_mult, int interleaved, int mode,
              void* out_vals, int64_t* out_idx, int64_t out_row_stride,
              void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * atk_topk with a choice of output format (ATK_OUT_*); no counterpart in the
+ * reference, whose indices are always int64.  Everything else is atk_topk:
+ * the same selection, the same order of the k pairs inside a row, the same
+ * workspace (atk_topk_workspace_bytes).  out_row_stride counts pairs (records
+ * for ATK_OUT_REC32).  Interleaved buckets only (the layout the narrow formats
+ * are meant for); ATK_OUT_I64 is accepted for every layout and is atk_topk.
+ */
+int atk_topk_ex(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
+                int64_t k, int j, int64_t k_mult, int interleaved, int mode, int out_format,
+                void* out_vals, void* out_idx, int64_t out_row_stride,
+                void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * k_b = 1 bucketed arg-max with the conventions of

@@ -28,6 +28,11 @@ ATK_ERR_TOO_LARGE = -7
 ATK_ERR_CUDA = -8
 ATK_ERR_SCRATCH_LIMIT = -9
 
+# output formats of atk_topk_ex
+ATK_OUT_I64 = 0
+ATK_OUT_I32 = 1
+ATK_OUT_REC32 = 2
+
 # Codes of include/atk.h; the nine element types of the reference's native
 # dispatch (approx_topk/priority_queue_approx_topk.cu:449-453).
 DTYPE_CODES = {
@@ -54,6 +59,8 @@ SIGNATURES = {
     "atk_select_static": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
     "atk_topk_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64]),
     "atk_topk": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
+    "atk_topk_ex": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _int, _int, _vp, _vp, _i64, _vp, _sz,
+                           _vp]),
     "atk_bucketed_argmax": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_topk_host_scratch_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64, _i64]),
     "atk_topk_host": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _vp, _vp, _vp, _sz, _i64]),

@@ -13,6 +13,10 @@ namespace atk {
 static thread_local long long g_launches = 0;
 void note_launch(int n) { g_launches += n; }
 
+int stage1_formatted(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k0, int j,
+                     int interleaved, int mode, int out_format, void* out_vals, void* out_idx,
+                     int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream);
+
 // Lazily cached SM count per device.  Together with the per-device address cache and
 // the built-in scratch array of atk_select_static (atk_select.cu) and the two cached
 // pipeline streams per device of atk_topk_host this is all the global state the library has.
@@ -114,8 +118,21 @@ size_t atk_stage1_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k0
 int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k0,
                int j, int interleaved, int mode, void* out_vals, int64_t* out_idx,
                int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  return stage1_formatted(x, dtype, rows, n, row_stride, k0, j, interleaved, mode, ATK_OUT_I64, out_vals, out_idx,
+                          out_row_stride, workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"
+
+namespace atk {
+// atk_stage1 with the output format of the final pairs as a parameter (the C ABI
+// offers the formats through atk_topk_ex only).
+int stage1_formatted(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k0, int j,
+                     int interleaved, int mode, int out_format, void* out_vals, void* out_idx,
+                     int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
   (void)mode;
-  int rc = check_common(x, dtype, rows, n, row_stride, out_vals, out_idx, out_row_stride);
+  int rc = check_common(x, dtype, rows, n, row_stride, out_vals,
+                        out_format == ATK_OUT_REC32 ? out_vals : out_idx, out_row_stride);
   if (rc != ATK_OK) return rc;
   if (k0 < 0) return ATK_ERR_BAD_ARG;
   if (k0 == 0 || rows == 0) return ATK_OK;
@@ -139,12 +156,14 @@ int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_st
     a.j = j;
     a.first_wins = false;
     a.sm_count = sm_count_of_current_device();
+    a.out_format = out_format;
     a.workspace = workspace;
     a.workspace_bytes = workspace_bytes;
     a.out_keys = nullptr;
     a.stream = static_cast<cudaStream_t>(stream);
     return sweep_dispatch(a, dtype);
   }
+  if (out_format != ATK_OUT_I64) return ATK_ERR_BAD_ARG;   // narrow formats: interleaved buckets only
   ContigLaunch c;
   c.x = x;
   c.out_vals = out_vals;
@@ -160,6 +179,9 @@ int atk_stage1(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_st
   c.stream = static_cast<cudaStream_t>(stream);
   return launch_contig(c, dtype);
 }
+}  // namespace atk
+
+extern "C" {
 
 size_t atk_stage1_slab_workspace_bytes(int dtype, int64_t stripes, int64_t cols, int j) {
   const int s = elem_size(dtype);
@@ -219,7 +241,7 @@ int atk_select(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_
   a.cand_row_stride = cand_row_stride;
   a.k = k;
   a.out_vals = out_vals;
-  a.out_idx = reinterpret_cast<long long*>(out_idx);
+  a.out_idx = out_idx;
   a.out_row_stride = out_row_stride;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
@@ -242,7 +264,7 @@ int atk_select_static(const void* cand_vals, const int64_t* cand_idx, int dtype,
   a.cand_row_stride = cand_row_stride;
   a.k = k;
   a.out_vals = out_vals;
-  a.out_idx = reinterpret_cast<long long*>(out_idx);
+  a.out_idx = out_idx;
   a.out_row_stride = out_row_stride;
   a.workspace = nullptr;
   a.workspace_bytes = 0;
@@ -265,9 +287,22 @@ size_t atk_topk_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k, i
 int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k, int j,
              int64_t k_mult, int interleaved, int mode, void* out_vals, int64_t* out_idx,
              int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  return atk_topk_ex(x, dtype, rows, n, row_stride, k, j, k_mult, interleaved, mode, ATK_OUT_I64, out_vals, out_idx,
+                     out_row_stride, workspace, workspace_bytes, stream);
+}
+
+int atk_topk_ex(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k, int j,
+                int64_t k_mult, int interleaved, int mode, int out_format, void* out_vals, void* out_idx,
+                int64_t out_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
   if (k_mult < 1 || k < 0) return ATK_ERR_BAD_ARG;
   const int s = elem_size(dtype);
   if (s == 0) return ATK_ERR_BAD_DTYPE;
+  if (out_format != ATK_OUT_I64 && out_format != ATK_OUT_I32 && out_format != ATK_OUT_REC32) return ATK_ERR_BAD_ARG;
+  if (out_format != ATK_OUT_I64) {
+    if (!interleaved) return ATK_ERR_BAD_ARG;
+    if (out_format == ATK_OUT_REC32 && s > 4) return ATK_ERR_BAD_DTYPE;
+    if (n >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+  }
   if (k == 0 || rows == 0) return ATK_OK;
   const int64_t k0 = k * k_mult;
   // Workspace layout: [stage-1 stripe-split planes][candidate values][candidate positions][select state].
@@ -277,8 +312,8 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
   size_t split_bytes = align256(atk_stage1_workspace_bytes(dtype, rows, n, k0, j, interleaved));
   if (k_mult == 1) {
     if (ws == nullptr || workspace_bytes < split_bytes) split_bytes = ws == nullptr ? 0 : workspace_bytes;
-    return atk_stage1(x, dtype, rows, n, row_stride, k, j, interleaved, mode, out_vals, out_idx, out_row_stride,
-                      ws, split_bytes, stream);
+    return stage1_formatted(x, dtype, rows, n, row_stride, k, j, interleaved, mode, out_format, out_vals, out_idx,
+                            out_row_stride, ws, split_bytes, stream);
   }
   const size_t cand_v = align256(static_cast<size_t>(rows) * k0 * s);
   const size_t cand_i = align256(static_cast<size_t>(rows) * k0 * 8);
@@ -297,7 +332,8 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
   // positions are rebuilt for the k winners only.  Shapes without packed entries
   // (too many stripes, stripes split over blocks) fall through to the plain form.
   if (interleaved && s <= 2 && k0 <= select_packed_max_k0() && j >= 1 && j <= 4 && k0 % j == 0 && k0 <= n &&
-      rows > 0 && n > 0 && x != nullptr && out_vals != nullptr && out_idx != nullptr && row_stride >= 0 &&
+      rows > 0 && n > 0 && x != nullptr && out_vals != nullptr &&
+      (out_idx != nullptr || out_format == ATK_OUT_REC32) && row_stride >= 0 &&
       out_row_stride >= 0 && static_cast<size_t>(rows) * k0 * 4 <= cand_v + cand_i) {
     SweepLaunch a;
     a.x = x;
@@ -330,8 +366,9 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
       sp.b = a.b;
       sp.j = j;
       sp.out_vals = out_vals;
-      sp.out_idx = reinterpret_cast<long long*>(out_idx);
+      sp.out_idx = out_idx;
       sp.out_row_stride = out_row_stride;
+      sp.out_format = out_format;
       sp.stream = a.stream;
       return launch_select_packed(sp, dtype);
     }
@@ -340,8 +377,23 @@ int atk_topk(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stri
   int rc = atk_stage1(x, dtype, rows, n, row_stride, k0, j, interleaved, mode, cand_vals, cand_idx, k0,
                       split_ws, split_bytes, stream);
   if (rc != ATK_OK) return rc;
-  return atk_select(cand_vals, cand_idx, dtype, rows, k0, k0, k, out_vals, out_idx, out_row_stride,
-                    sel_ws ? ws : nullptr, sel_ws, stream);
+  if (out_vals == nullptr || (out_idx == nullptr && out_format != ATK_OUT_REC32) || out_row_stride < 0)
+    return ATK_ERR_BAD_ARG;
+  SelectLaunch sel;
+  sel.cand_vals = cand_vals;
+  sel.cand_idx = reinterpret_cast<const long long*>(cand_idx);
+  sel.rows = rows;
+  sel.k0 = k0;
+  sel.cand_row_stride = k0;
+  sel.k = k;
+  sel.out_vals = out_vals;
+  sel.out_idx = out_idx;
+  sel.out_row_stride = out_row_stride;
+  sel.out_format = out_format;
+  sel.workspace = sel_ws ? ws : nullptr;
+  sel.workspace_bytes = sel_ws;
+  sel.stream = static_cast<cudaStream_t>(stream);
+  return launch_select(sel, dtype);
 }
 
 int atk_bucketed_argmax(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int64_t k,

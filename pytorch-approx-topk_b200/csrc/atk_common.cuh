@@ -16,6 +16,54 @@ void note_launch(int n = 1);
 // Number of SMs of the current device (queried once per device, then cached).
 int sm_count_of_current_device();
 
+// Where the final (value, position) pairs of a row go, in one of the output
+// formats of include/atk.h: values + int64 positions (the reference's layout),
+// values + int32 positions, or 8-byte records {value bits zero-extended to 32
+// bits, int32 position}.  `at(offset)` is the same row advanced by `offset` pairs.
+template <typename B>
+struct OutRow {
+  B* v;
+  void* i;      // long long* (ATK_OUT_I64) or int* (ATK_OUT_I32); unused for records
+  uint2* rec;   // ATK_OUT_REC32
+  int fmt;
+  __device__ __forceinline__ OutRow(void* out_vals, void* out_idx, long long row, long long row_stride, int format)
+      : v(nullptr), i(nullptr), rec(nullptr), fmt(format) {
+    const long long off = row * row_stride;
+    if (format == ATK_OUT_REC32) {
+      rec = static_cast<uint2*>(out_vals) + off;
+    } else {
+      v = static_cast<B*>(out_vals) + off;
+      i = format == ATK_OUT_I32 ? static_cast<void*>(static_cast<int*>(out_idx) + off)
+                                : static_cast<void*>(static_cast<long long*>(out_idx) + off);
+    }
+  }
+  __device__ __forceinline__ OutRow at(long long offset) const {
+    OutRow r = *this;
+    if (fmt == ATK_OUT_REC32) {
+      r.rec += offset;
+    } else {
+      r.v += offset;
+      r.i = fmt == ATK_OUT_I32 ? static_cast<void*>(static_cast<int*>(i) + offset)
+                               : static_cast<void*>(static_cast<long long*>(i) + offset);
+    }
+    return r;
+  }
+  // both destinations (or the record array) start on a 16-byte boundary
+  __device__ __forceinline__ bool aligned16() const {
+    if (fmt == ATK_OUT_REC32) return reinterpret_cast<uintptr_t>(rec) % 16 == 0;
+    return reinterpret_cast<uintptr_t>(v) % 16 == 0 && reinterpret_cast<uintptr_t>(i) % 16 == 0;
+  }
+  __device__ __forceinline__ void put(long long slot, B value, long long position) const {
+    if (fmt == ATK_OUT_REC32) {
+      rec[slot] = make_uint2(static_cast<uint32_t>(value), static_cast<uint32_t>(static_cast<int>(position)));
+    } else {
+      v[slot] = value;
+      if (fmt == ATK_OUT_I32) static_cast<int*>(i)[slot] = static_cast<int>(position);
+      else static_cast<long long*>(i)[slot] = position;
+    }
+  }
+};
+
 // Sentinel stripe numbers of never-filled queue slots.  With the "last wins"
 // tie rule a real element must outrank the sentinel at equal value (-inf), so
 // the sentinel index is below every real index; with "first wins" above.

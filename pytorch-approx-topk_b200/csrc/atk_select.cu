@@ -161,11 +161,20 @@ template <typename B> size_t stage_bytes(long long k) {
   return stage_val_offset(stage_tile(k)) + static_cast<size_t>(stage_tile(k)) * sizeof(B);
 }
 
-// Copies staged entries [0, cnt) to out_vals/out_idx[dst ...]; all threads of
-// the block take part.  `vec`: both destinations are 16-byte aligned at dst.
+// Copies staged entries [0, cnt) to the output row `o` (already advanced to the
+// first destination slot); all threads of the block take part.  `vec`: the
+// destinations start on a 16-byte boundary (used by the int64 layout, whose
+// positions are 2/3 of the bytes; the narrow formats store element-wise, which
+// is just as coalesced).
 template <typename B>
-__device__ __forceinline__ void stage_copy_out(const long long* sidx, const B* sval, int cnt, B* __restrict__ ov,
-                                               long long* __restrict__ oi, int tid, int nthr, bool vec) {
+__device__ __forceinline__ void stage_copy_out(const long long* sidx, const B* sval, int cnt, const OutRow<B>& o,
+                                               int tid, int nthr, bool vec) {
+  if (o.fmt != ATK_OUT_I64) {
+    for (int p = tid; p < cnt; p += nthr) o.put(p, sval[p], sidx[p]);
+    return;
+  }
+  B* __restrict__ ov = o.v;
+  long long* __restrict__ oi = static_cast<long long*>(o.i);
   if (vec) {
     const int ni = cnt / 2;                                   // 16-byte pieces of positions
     for (int q = tid; q < ni; q += nthr) reinterpret_cast<uint4*>(oi)[q] = reinterpret_cast<const uint4*>(sidx)[q];
@@ -194,8 +203,8 @@ template <typename T, int ITEMS, int MAXT, bool FULL>
 __global__ void __launch_bounds__(MAXT, (ITEMS <= 8 && MAXT == 512) ? ATK_SELECT_ROW_MINBLOCKS : 1)
 select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                   const long long* __restrict__ cand_idx, int k0, long long cand_row_stride, int k,
-                  typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
-                  long long out_row_stride, int vec_ok) {
+                  void* __restrict__ out_vals, void* __restrict__ out_idx, long long out_row_stride, int out_fmt,
+                  int vec_ok) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
   using Bits = typename ElemTraits<T>::Bits;
@@ -298,8 +307,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   uint32_t gt_rank = excl & 0xffffu;
   uint32_t eq_rank = excl >> 16;
   const uint32_t n_gt = static_cast<uint32_t>(k) - need;
-  Bits* ovrow = out_vals + row * out_row_stride;
-  long long* oirow = out_idx + row * out_row_stride;
+  const OutRow<Bits> orow(out_vals, out_idx, row, out_row_stride, out_fmt);
   // output position of every item (-1: not selected)
   int pos[ITEMS];
 #pragma unroll
@@ -320,7 +328,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   long long* sidx = reinterpret_cast<long long*>(stage_smem);
   const int tile = stage_tile(k);
   Bits* sval = reinterpret_cast<Bits*>(stage_smem + stage_val_offset(tile));
-  const bool vec_out = (reinterpret_cast<uintptr_t>(ovrow) % 16 == 0) && (reinterpret_cast<uintptr_t>(oirow) % 16 == 0);
+  const bool vec_out = orow.aligned16();
   for (int base = 0; base < k; base += tile) {
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
@@ -333,7 +341,7 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
     }
     __syncthreads();
     const int cnt = k - base < tile ? k - base : tile;
-    stage_copy_out<Bits>(sidx, sval, cnt, ovrow + base, oirow + base, tid, nthr, vec_out);
+    stage_copy_out<Bits>(sidx, sval, cnt, orow.at(base), tid, nthr, vec_out);
     if (base + tile < k) __syncthreads();
   }
 }
@@ -347,8 +355,8 @@ template <typename T, int ITEMS, int MAXT, bool FULL>
 __global__ void __launch_bounds__(MAXT, ITEMS <= 8 ? ATK_SELECT_PACKED_MINBLOCKS : 1)
 select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const T* __restrict__ x,
                          long long x_row_stride, long long b, int j,
-                         typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
-                         long long out_row_stride, int vec_ok) {
+                         void* __restrict__ out_vals, void* __restrict__ out_idx, long long out_row_stride,
+                         int out_fmt, int vec_ok) {
   using Bits = typename ElemTraits<T>::Bits;
   using PQ = PackedQueue<T, 1, false>;
   using Img = PackedImage<T>;
@@ -449,8 +457,7 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
       }
     }
   }
-  Bits* ovrow = out_vals + row * out_row_stride;
-  long long* oirow = out_idx + row * out_row_stride;
+  const OutRow<Bits> orow(out_vals, out_idx, row, out_row_stride, out_fmt);
   const T* xrow = x + row * x_row_stride;
   // slot s belongs to bucket s / j
   const int jshift = j == 1 ? 0 : (j == 2 ? 1 : (j == 4 ? 2 : -1));
@@ -458,7 +465,7 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
   long long* sidx = reinterpret_cast<long long*>(stage_smem);
   const int tile = stage_tile(k);
   Bits* sval = reinterpret_cast<Bits*>(stage_smem + stage_val_offset(tile));
-  const bool vec_out = (reinterpret_cast<uintptr_t>(ovrow) % 16 == 0) && (reinterpret_cast<uintptr_t>(oirow) % 16 == 0);
+  const bool vec_out = orow.aligned16();
   for (int base = 0; base < k; base += tile) {
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
@@ -473,7 +480,7 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
     }
     __syncthreads();
     const int cnt = k - base < tile ? k - base : tile;
-    stage_copy_out<Bits>(sidx, sval, cnt, ovrow + base, oirow + base, tid, nthr, vec_out);
+    stage_copy_out<Bits>(sidx, sval, cnt, orow.at(base), tid, nthr, vec_out);
     if (base + tile < k) __syncthreads();
   }
 }
@@ -659,8 +666,8 @@ __global__ void __launch_bounds__(kLargeThreads)
 select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                     const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride,
                     long long k, const RowState<typename KeyOf<T>::Key>* __restrict__ state,
-                    const uint2* __restrict__ bases, typename ElemTraits<T>::Bits* __restrict__ out_vals,
-                    long long* __restrict__ out_idx, long long out_row_stride, int vec) {
+                    const uint2* __restrict__ bases, void* __restrict__ out_vals, void* __restrict__ out_idx,
+                    long long out_row_stride, int out_fmt, int vec) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
   __shared__ uint32_t wsum[32];
@@ -678,8 +685,7 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   if (end > k0) end = k0;
   const auto* vrow = cand_vals + row * cand_row_stride;
   const long long* irow = cand_idx + row * cand_row_stride;
-  auto* ovrow = out_vals + row * out_row_stride;
-  long long* oirow = out_idx + row * out_row_stride;
+  const OutRow<typename ElemTraits<T>::Bits> orow(out_vals, out_idx, row, out_row_stride, out_fmt);
   // Thread t owns the ITEMS consecutive slots begin + t*ITEMS ...:
   // per-thread counts, one block-wide scan, then every winner knows its place.
   const int lane = threadIdx.x & 31;
@@ -748,14 +754,11 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
     }
   }
   __syncthreads();
-  auto* gv = ovrow + gt_base;
-  long long* gi = oirow + gt_base;
-  const bool vec_gt = (reinterpret_cast<uintptr_t>(gv) % 16 == 0) && (reinterpret_cast<uintptr_t>(gi) % 16 == 0);
-  stage_copy_out<typename ElemTraits<T>::Bits>(sidx, sval, static_cast<int>(tot_gt), gv, gi, threadIdx.x,
-                                               kLargeThreads, vec_gt);
+  const auto gt_row = orow.at(gt_base);
+  stage_copy_out<typename ElemTraits<T>::Bits>(sidx, sval, static_cast<int>(tot_gt), gt_row, threadIdx.x,
+                                               kLargeThreads, gt_row.aligned16());
   stage_copy_out<typename ElemTraits<T>::Bits>(sidx + tot_gt, sval + tot_gt, static_cast<int>(sel_eq),
-                                               ovrow + n_gt + eq_base, oirow + n_gt + eq_base, threadIdx.x,
-                                               kLargeThreads, false);
+                                               orow.at(n_gt + eq_base), threadIdx.x, kLargeThreads, false);
 }
 
 inline long long chunks_of(long long k0) { return (k0 + kChunk - 1) / kChunk; }
@@ -780,7 +783,7 @@ int select_typed(const SelectLaunch& a) {
   using Bits = typename ElemTraits<T>::Bits;
   using K = KeyOf<T>;
   const Bits* cv = static_cast<const Bits*>(a.cand_vals);
-  Bits* ov = static_cast<Bits*>(a.out_vals);
+  void* ov = a.out_vals;
   using State = RowState<typename K::Key>;
   if (a.k0 <= small_max_k0<T>()) {
     if (a.rows >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
@@ -804,10 +807,10 @@ int select_typed(const SelectLaunch& a) {
     do {                                                                                                 \
       if (vec_ok && threads_for(ITEMS) * (ITEMS) == k0)                                                  \
         select_row_kernel<T, ITEMS, MAXT, true><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
-            cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);          \
+            cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, a.out_format, vec_ok); \
       else                                                                                               \
         select_row_kernel<T, ITEMS, MAXT, false><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
-            cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, vec_ok);          \
+            cv, a.cand_idx, k0, a.cand_row_stride, k, ov, a.out_idx, a.out_row_stride, a.out_format, vec_ok); \
     } while (0)
     if (threads_for(kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(kBase, kSelectRowThreads);
     else if (threads_for(2 * kBase) <= kSelectRowThreads) ATK_LAUNCH_SELECT_ROW(2 * kBase, kSelectRowThreads);
@@ -861,7 +864,7 @@ int select_typed(const SelectLaunch& a) {
   select_count_kernel<T, kItems><<<grid_c, kLargeThreads, 0, a.stream>>>(
       cv, a.k0, a.cand_row_stride, state, counts, tickets, static_cast<int>(chunks), static_cast<int>(cpw), vec);
   select_write_kernel<T, kItems><<<grid, kLargeThreads, 0, a.stream>>>(
-      cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, counts, ov, a.out_idx, a.out_row_stride, vec);
+      cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, counts, ov, a.out_idx, a.out_row_stride, a.out_format, vec);
   note_launch(K::kPasses + 2);
   return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
 }
@@ -901,15 +904,15 @@ int select_packed_typed(const SelectPackedLaunch& a) {
     return ((t + 31) / 32) * 32;
   };
   const T* x = static_cast<const T*>(a.x);
-  Bits* ov = static_cast<Bits*>(a.out_vals);
+  void* ov = a.out_vals;
 #define ATK_LAUNCH_SELECT_PACKED(ITEMS)                                                                   \
   do {                                                                                                    \
     if (vec_ok && threads_for(ITEMS) * (ITEMS) == k0)                                                     \
       select_row_packed_kernel<T, ITEMS, 512, true><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
-          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, vec_ok);           \
+          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, a.out_format, vec_ok); \
     else                                                                                                  \
       select_row_packed_kernel<T, ITEMS, 512, false><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
-          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, vec_ok);           \
+          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, a.out_format, vec_ok); \
   } while (0)
   // at least 16 bytes of entries per thread, more until the block is at most 512 wide
   if (threads_for(4) <= kSelectRowThreads) ATK_LAUNCH_SELECT_PACKED(4);

@@ -10,8 +10,9 @@ struct SelectLaunch {
   const long long* cand_idx;
   long long rows, k0, cand_row_stride, k;
   void* out_vals;
-  long long* out_idx;
+  void* out_idx;             // int64 or int32 positions by out_format (unused for records)
   long long out_row_stride;
+  int out_format = ATK_OUT_I64;
   void* workspace;
   size_t workspace_bytes;
   cudaStream_t stream;
@@ -37,8 +38,9 @@ struct SelectPackedLaunch {
   long long b;                // buckets per row: position = stripe * b + bucket
   int j;
   void* out_vals;
-  long long* out_idx;
+  void* out_idx;
   long long out_row_stride;
+  int out_format = ATK_OUT_I64;
   cudaStream_t stream;
 };
 // Longest row this select takes (one block per row); longer rows use the plain hand-off.

@@ -17,6 +17,7 @@
 #pragma once
 
 #include "atk_queue.cuh"
+#include "atk_tile.cuh"
 
 namespace atk {
 
@@ -36,7 +37,8 @@ struct SweepParams {
   long long idx_offset;
   int cw;                    // blockDim.x: threads across columns
   int s;                     // blockDim.y: stripe splits inside the block (power of two)
-  int vec_out;               // 16-byte stores are legal for both outputs
+  int vec_out;               // 16-byte stores are legal for the outputs (in their format)
+  int out_format;            // ATK_OUT_*: how the final pairs are stored (the scratch planes are always int64)
   int vec_part;              // ... and for the scratch planes of the stripe split
   // Packed hand-off to the select (two-stage operator only): instead of values and
   // positions the kernel writes the queue entries themselves, rows x k0 words.
@@ -100,9 +102,18 @@ __device__ __forceinline__ long long sweep_walk(QS (&qs)[V / QS::kCols], const S
   return l;
 }
 
-// Scan into q[V].  With SIMD (16-bit inputs on the vector path) the walk runs
-// on two-column SIMD queues that are then converted to packed entries.
-template <typename T, typename Q, int V, bool SKIP, bool SIMD>
+// How a thread scans its columns (template argument MODE of the kernel):
+//   kScanQueues   insertion into the queues of Q, element by element;
+//   kScanSimd     16-bit float inputs on the vector path: two-column SIMD queues
+//                 that are converted to packed entries after the walk;
+//   16 / 32 / 64  16-bit float inputs, two columns per thread, short columns: the
+//                 two-pass tile of atk_tile.cuh with chunks of that many stripes.
+constexpr int kScanQueues = 0;
+constexpr int kScanSimd = 1;
+constexpr int kScanTile = -1;   // launcher-side tag: pick the chunk length from the launch shape
+
+// Scan into q[V].
+template <typename T, typename Q, int V, bool SKIP, int MODE>
 __device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, const T* xrow, long long c0,
                                            int ty, int S, int z) {
   // stripe range of this block (the whole column unless stripes are split over blocks)
@@ -110,7 +121,10 @@ __device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, cons
   long long l_end = l_begin + p.z_chunk;
   if (l_end > p.l_full || z == p.z - 1) l_end = p.l_full;
   long long l;
-  if constexpr (SIMD) {
+  if constexpr (MODE >= 16) {
+    static_assert(V == 2 && Q::kPacked && !Q::kFirst, "the tile scan works on two columns of packed queues");
+    l = tile_walk<T, Q::kJ, MODE>(q, xrow + c0, p.stripe_stride, ty, S, l_begin, l_end);
+  } else if constexpr (MODE == kScanSimd) {
     using QS = Simd16Queue<T, Q::kJ, Q::kFirst>;
     QS qs[V / 2];
 #pragma unroll
@@ -155,10 +169,31 @@ __device__ __forceinline__ void sweep_merge(Q (&q)[V], uint32_t* smem, int cw, i
   }
 }
 
+// Stores BYTES bytes from a 16-byte aligned local array to `dst`.  With `vec` the
+// destination is known to be aligned to the widest power-of-two store (16, 8 or 4
+// bytes) that divides BYTES; otherwise, and for odd sizes, element by element.
+template <int BYTES, typename E>
+__device__ __forceinline__ void store_run(E* dst, const E* src, bool vec) {
+  constexpr int kStore = BYTES % 16 == 0 ? 16 : (BYTES % 8 == 0 ? 8 : (BYTES % 4 == 0 ? 4 : 0));
+  if (kStore == 16 && vec) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 16; ++i) st_out_16(reinterpret_cast<uint4*>(dst) + i, reinterpret_cast<const uint4*>(src)[i]);
+  } else if (kStore == 8 && vec) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 8; ++i) reinterpret_cast<uint2*>(dst)[i] = reinterpret_cast<const uint2*>(src)[i];
+  } else if (kStore == 4 && vec) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 4; ++i) reinterpret_cast<uint32_t*>(dst)[i] = reinterpret_cast<const uint32_t*>(src)[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < BYTES / static_cast<int>(sizeof(E)); ++i) dst[i] = src[i];
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Stage 1 only: every block handles one tile of columns of one row and writes
 // the J candidates of each bucket (slot = bucket*J + q, ascending).
-template <typename T, typename Q, int J, int V, bool SKIP, bool SIMD, bool PACKED_OUT>
+template <typename T, typename Q, int J, int V, bool SKIP, int MODE, bool PACKED_OUT>
 __global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
 sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
@@ -180,7 +215,7 @@ sweep_kernel(const SweepParams p) {
 #pragma unroll
   for (int e = 0; e < V; ++e) q[e].init();
 
-  if (active) sweep_scan<T, Q, V, SKIP, SIMD>(q, p, xrow, c0, ty, S, z);
+  if (active) sweep_scan<T, Q, V, SKIP, MODE>(q, p, xrow, c0, ty, S, z);
   if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
   if (!active || ty != 0) return;
 
@@ -224,25 +259,34 @@ sweep_kernel(const SweepParams p) {
     }
   // direct to the outputs, or to plane z of the scratch when stripes are split over blocks
   const long long k0 = p.b * J;
+  // The thread's V*J entries are contiguous in every output array and start at a
+  // multiple of their total size there, so the widest store that divides that size
+  // is aligned whenever the buffers and their row strides are 16-byte aligned.
+  if (p.z == 1 && p.out_format != ATK_OUT_I64) {
+    const long long out_base = row * p.out_row_stride + c0 * J;
+    if (p.out_format == ATK_OUT_REC32) {
+      // records {value bits zero-extended to 32 bits, int32 position}
+      __align__(16) uint2 rec[V * J];
+#pragma unroll
+      for (int i = 0; i < V * J; ++i)
+        rec[i] = make_uint2(static_cast<uint32_t>(ov[i]), static_cast<uint32_t>(static_cast<int>(oi[i])));
+      store_run<V * J * 8>(static_cast<uint2*>(p.out_vals) + out_base, rec, p.vec_out);
+    } else {
+      __align__(16) int oi32[V * J];
+#pragma unroll
+      for (int i = 0; i < V * J; ++i) oi32[i] = static_cast<int>(oi[i]);
+      store_run<V * J * static_cast<int>(sizeof(Bits))>(static_cast<Bits*>(p.out_vals) + out_base, ov, p.vec_out);
+      store_run<V * J * 4>(reinterpret_cast<int*>(p.out_idx) + out_base, oi32, p.vec_out);
+    }
+    return;
+  }
   const long long out_base = p.z > 1 ? (static_cast<long long>(z) * p.rows + row) * k0 + c0 * J
                                      : row * p.out_row_stride + c0 * J;
   Bits* vdst = static_cast<Bits*>(p.z > 1 ? p.part_vals : p.out_vals) + out_base;
   long long* idst = (p.z > 1 ? p.part_idx : p.out_idx) + out_base;
-  constexpr int kValBytes = V * J * static_cast<int>(sizeof(Bits));
-  if (kValBytes % 16 == 0 && (p.z > 1 ? p.vec_part : p.vec_out)) {
-    const uint4* src = reinterpret_cast<const uint4*>(ov);
-#pragma unroll
-    for (int i = 0; i < kValBytes / 16; ++i) st_out_16(reinterpret_cast<uint4*>(vdst) + i, src[i]);
-    const uint4* isrc = reinterpret_cast<const uint4*>(oi);
-#pragma unroll
-    for (int i = 0; i < V * J / 2; ++i) st_out_16(reinterpret_cast<uint4*>(idst) + i, isrc[i]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < V * J; ++i) {
-      vdst[i] = ov[i];
-      idst[i] = oi[i];
-    }
-  }
+  const bool vec = p.z > 1 ? p.vec_part : p.vec_out;
+  store_run<V * J * static_cast<int>(sizeof(Bits))>(vdst, ov, vec);
+  store_run<V * J * 8>(idst, oi, vec);
 }
 
 // Combine the z partial candidate planes written by a stripe-split sweep: a
@@ -297,9 +341,8 @@ template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(256)
 sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_vals,
                           const long long* __restrict__ part_idx, int z, int g /* lanes per bucket */,
-                          long long rows, long long b,
-                          typename ElemTraits<T>::Bits* __restrict__ out_vals, long long* __restrict__ out_idx,
-                          long long out_row_stride) {
+                          long long rows, long long b, void* __restrict__ out_vals, void* __restrict__ out_idx,
+                          long long out_row_stride, int out_format) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
   const int lane = threadIdx.x % g;            // g is a power of two <= 32, groups never straddle warps
@@ -334,13 +377,9 @@ sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_
     for (int j = 0; j < J; ++j) q.push(ov[j], oi[j], ob[j]);
   }
   if (!valid || lane != 0) return;
-  Bits* vdst = out_vals + row * out_row_stride + c * J;
-  long long* idst = out_idx + row * out_row_stride + c * J;
+  const OutRow<Bits> orow(out_vals, out_idx, row, out_row_stride, out_format);
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    vdst[j] = q.b[j];
-    idst[j] = q.i[j];
-  }
+  for (int j = 0; j < J; ++j) orow.put(c * J + j, q.b[j], q.i[j]);
 }
 
 // ---- launch shape (host) -------------------------------------------------------
@@ -440,6 +479,7 @@ struct SweepLaunch {
   int j;
   bool first_wins;          // k_b = 1 arg-max conventions (J must be 1)
   int sm_count;
+  int out_format = ATK_OUT_I64;   // format of out_vals / out_idx (out_idx is then an int* for ATK_OUT_I32)
   void* workspace;          // optional scratch for splitting stripes over blocks (may be null)
   size_t workspace_bytes;
   uint32_t* out_keys;       // non-null: hand the packed queue entries to the select instead of out_vals / out_idx

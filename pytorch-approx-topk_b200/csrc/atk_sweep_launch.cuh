@@ -11,6 +11,10 @@ namespace atk {
 
 namespace sweep_detail {
 
+// Stripes per thread from which the head test (skip the insertion when nothing
+// enters) pays off; below it 16-bit float inputs take the tile scan.
+constexpr long long kSkipStripes = 256;
+
 inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
   p.x = a.x;
   p.out_vals = a.out_vals;
@@ -24,14 +28,50 @@ inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
   p.stripe_stride = a.stripe_stride;
   p.idx_stride = a.idx_stride;
   p.idx_offset = a.idx_offset;
+  p.out_format = a.out_format;
   const uintptr_t ov = reinterpret_cast<uintptr_t>(a.out_vals);
   const uintptr_t oi = reinterpret_cast<uintptr_t>(a.out_idx);
-  p.vec_out = (ov % 16 == 0) && (oi % 16 == 0) && ((a.out_row_stride * elem_size) % 16 == 0) &&
-              ((a.out_row_stride * 8) % 16 == 0);
+  if (a.out_format == ATK_OUT_REC32)
+    p.vec_out = (ov % 16 == 0) && ((a.out_row_stride * 8) % 16 == 0);
+  else
+    p.vec_out = (ov % 16 == 0) && (oi % 16 == 0) && ((a.out_row_stride * elem_size) % 16 == 0) &&
+                ((a.out_row_stride * (a.out_format == ATK_OUT_I32 ? 4 : 8)) % 16 == 0);
 }
 
 // ---- stage 1 -----------------------------------------------------------------
-template <typename T, typename Q, int J, int V, bool SIMD>
+// One launch of the sweep kernel for a scan mode (head-test variant by `skip`).
+template <typename T, typename Q, int J, int V, int MODE, bool PACKED_OUT>
+void launch_sweep_kernel(const dim3& grid, const dim3& block, size_t smem, cudaStream_t stream, const SweepParams& p,
+                         bool skip) {
+  if constexpr (MODE >= 16) {
+    // the tile scan has no head-test variant (it is chosen for short columns)
+    sweep_kernel<T, Q, J, V, false, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
+  } else {
+    if (skip)
+      sweep_kernel<T, Q, J, V, true, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
+    else
+      sweep_kernel<T, Q, J, V, false, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
+  }
+}
+
+// MODE: kScanQueues, kScanSimd, or kScanTile (chunk length picked from the launch shape).
+template <typename T, typename Q, int J, int V, int MODE, bool PACKED_OUT>
+void launch_sweep_mode(const dim3& grid, const dim3& block, size_t smem, cudaStream_t stream, const SweepParams& p,
+                       bool skip, long long stripes_per_thread) {
+  if constexpr (MODE == kScanTile) {
+    // the shortest chunk that holds a thread's stripes (a longer walk loops over chunks of 64)
+    if (stripes_per_thread <= 16)
+      launch_sweep_kernel<T, Q, J, V, 16, PACKED_OUT>(grid, block, smem, stream, p, false);
+    else if (stripes_per_thread <= 32)
+      launch_sweep_kernel<T, Q, J, V, 32, PACKED_OUT>(grid, block, smem, stream, p, false);
+    else
+      launch_sweep_kernel<T, Q, J, V, 64, PACKED_OUT>(grid, block, smem, stream, p, false);
+  } else {
+    launch_sweep_kernel<T, Q, J, V, MODE, PACKED_OUT>(grid, block, smem, stream, p, skip);
+  }
+}
+
+template <typename T, typename Q, int J, int V, int MODE>
 int launch_stage1(const SweepLaunch& a) {
   using Bits = typename ElemTraits<T>::Bits;
   SweepParams p;
@@ -73,21 +113,16 @@ int launch_stage1(const SweepLaunch& a) {
   const dim3 grid(static_cast<unsigned>(a.rows * pl.tiles * pl.Z));
   const dim3 block(static_cast<unsigned>(pl.cw), static_cast<unsigned>(pl.S));
   // The head test pays off once a thread walks a long column.
-  const bool skip = (pl.z_chunk / pl.S) >= 256;
+  const bool skip = (pl.z_chunk / pl.S) >= kSkipStripes;
+  const long long stripes_per_thread = (pl.z_chunk + pl.S - 1) / pl.S;
   if constexpr (kCanPack) {
     if (a.out_keys != nullptr) {
-      if (skip)
-        sweep_kernel<T, Q, J, V, true, SIMD, true><<<grid, block, smem, a.stream>>>(p);
-      else
-        sweep_kernel<T, Q, J, V, false, SIMD, true><<<grid, block, smem, a.stream>>>(p);
+      launch_sweep_mode<T, Q, J, V, MODE, true>(grid, block, smem, a.stream, p, skip, stripes_per_thread);
       note_launch();
       return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
     }
   }
-  if (skip)
-    sweep_kernel<T, Q, J, V, true, SIMD, false><<<grid, block, smem, a.stream>>>(p);
-  else
-    sweep_kernel<T, Q, J, V, false, SIMD, false><<<grid, block, smem, a.stream>>>(p);
+  launch_sweep_mode<T, Q, J, V, MODE, false>(grid, block, smem, a.stream, p, skip, stripes_per_thread);
   note_launch();
   if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   if (pl.Z > 1) {
@@ -96,8 +131,8 @@ int launch_stage1(const SweepLaunch& a) {
     const long long blocks = (a.rows * a.b * g + 255) / 256;
     if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     sweep_merge_planes_kernel<T, J, Q::kFirst><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
-        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, static_cast<Bits*>(a.out_vals),
-        a.out_idx, a.out_row_stride);
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, a.out_vals, a.out_idx,
+        a.out_row_stride, a.out_format);
     note_launch();
     if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   }
@@ -115,11 +150,12 @@ int launch_by_queue(const SweepLaunch& a) {
     const long long stripes = a.n / a.b + (a.n % a.b != 0 ? 1 : 0);
     if (stripes <= PackedQueue<T, J, FIRST>::kMaxStripes) {
       // the two-column SIMD scan exists for the float formats only
-      return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V, (V >= 4 && ElemTraits<T>::kHalfFloat)>(a);
+      return launch_stage1<T, PackedQueue<T, J, FIRST>, J, V,
+                           (V >= 4 && ElemTraits<T>::kHalfFloat) ? kScanSimd : kScanQueues>(a);
     }
   }
   if (a.out_keys != nullptr) return kPackedUnavailable;
-  return launch_stage1<T, FloatQueue<T, J, FIRST>, J, V, false>(a);
+  return launch_stage1<T, FloatQueue<T, J, FIRST>, J, V, kScanQueues>(a);
 }
 
 template <typename T, int V>
@@ -133,6 +169,18 @@ int launch_by_j(const SweepLaunch& a) {
     case 2: return launch_by_queue<T, 2, V, false>(a);
     case 3: return launch_by_queue<T, 3, V, false>(a);
     case 4: return launch_by_queue<T, 4, V, false>(a);
+    default: return ATK_ERR_BAD_J;
+  }
+}
+
+// 16-bit float inputs, queues of two to four entries, columns short enough that no
+// head test would skip insertions: the two-pass tile scan (two columns per thread).
+template <typename T>
+int launch_tile(const SweepLaunch& a) {
+  switch (a.j) {
+    case 2: return launch_stage1<T, PackedQueue<T, 2, false>, 2, 2, kScanTile>(a);
+    case 3: return launch_stage1<T, PackedQueue<T, 3, false>, 3, 2, kScanTile>(a);
+    case 4: return launch_stage1<T, PackedQueue<T, 4, false>, 4, 2, kScanTile>(a);
     default: return ATK_ERR_BAD_J;
   }
 }
@@ -153,6 +201,15 @@ int launch_sweep(const SweepLaunch& a) {
     return (reinterpret_cast<uintptr_t>(a.x) % bytes == 0) && ((a.row_stride * s) % bytes == 0) &&
            ((a.stripe_stride * s) % bytes == 0) && (a.b % v == 0);
   };
+  if constexpr (ElemTraits<T>::kHalfFloat) {
+#ifdef ATK_TILE_SCAN   // build knob: measured slower than the two-column SIMD queues so far (latency-bound)
+    const long long l_full = a.n / a.b;
+    if (a.j >= 2 && !a.first_wins && fits(2) && l_full + 1 <= PackedQueue<T, 1, false>::kMaxStripes) {
+      const SweepPlan pl = plan_sweep(a.rows, a.b, l_full, 2, a.sm_count);
+      if (pl.z_chunk / pl.S < kSkipStripes) return launch_tile<T>(a);
+    }
+#endif
+  }
   if constexpr (sizeof(T) <= 2) {
     constexpr int kHalfVec = kVec / 2;
     if (a.j >= 3 && fits(kHalfVec)) return launch_by_j<T, kHalfVec>(a);

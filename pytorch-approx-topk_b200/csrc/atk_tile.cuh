@@ -1,0 +1,187 @@
+// Stage 1 scan for 16-bit float inputs with short columns: the "two-pass tile".
+//
+// The insertion queues of atk_queue.cuh cost about nine ALU-pipe operations per
+// element at four entries per queue (compares, min/max and the selects that carry
+// the stripe numbers), and that pipe issues 64 lanes per clock and SM: short
+// columns (no head test to skip insertions) are bound by it, not by memory.
+// Here a thread owns two adjacent columns (one 32-bit word per stripe) and holds
+// a chunk of CH stripes of them in registers, then
+//   pass 1  finds the J-th largest VALUE of either column in the chunk with a
+//           values-only network of packed fp16x2 / bf16x2 min/max (sorted batches
+//           merged into a running sorted top-J: no stripe numbers are carried);
+//   pass 2  compares every word of the chunk with that threshold pair and gathers
+//           the outcome as one bit per (column, stripe);
+//   then    only the elements at or above the threshold (J of CH unless values
+//           tie) are turned into packed queue entries (value image, stripe) and
+//           pushed into the exact per-column queues, which rank them by (value,
+//           position) like every other path.
+// Every element of the true top-J by (value, later position wins) is at or above
+// the J-th largest value, so the exact queue receives a superset of the winners
+// and the result is identical to the serial scan of the reference
+// (approx_topk/priority_queue_approx_topk.cu:58-107), ties included.  NaNs never
+// pass the threshold compare (the reference leaves them unspecified).
+#pragma once
+
+#include "atk_queue.cuh"
+
+namespace atk {
+
+template <typename Ops>
+__device__ __forceinline__ void tile_ce(uint32_t& a, uint32_t& b) {
+  const uint32_t lo = Ops::min2(a, b);
+  const uint32_t hi = Ops::max2(a, b);
+  a = lo;
+  b = hi;
+}
+
+// Sorted (ascending per half) top-J of a running list and a new batch, J = 2 or 4.
+template <typename Ops, int J> struct TileNet;
+
+template <typename Ops> struct TileNet<Ops, 4> {
+  static constexpr int kBatch = 4;
+  static __device__ __forceinline__ void sort(uint32_t (&a)[4]) {
+    tile_ce<Ops>(a[0], a[1]);
+    tile_ce<Ops>(a[2], a[3]);
+    tile_ce<Ops>(a[0], a[2]);
+    tile_ce<Ops>(a[1], a[3]);
+    tile_ce<Ops>(a[1], a[2]);
+  }
+  // t ascending, s ascending: the four largest of the eight form a bitonic list
+  static __device__ __forceinline__ void upper(const uint32_t (&t)[4], const uint32_t (&s)[4], uint32_t (&u)[4]) {
+    u[0] = Ops::max2(t[0], s[3]);
+    u[1] = Ops::max2(t[1], s[2]);
+    u[2] = Ops::max2(t[2], s[1]);
+    u[3] = Ops::max2(t[3], s[0]);
+  }
+  static __device__ __forceinline__ void merge(uint32_t (&t)[4], const uint32_t (&s)[4]) {
+    uint32_t u[4];
+    upper(t, s, u);
+    tile_ce<Ops>(u[0], u[2]);
+    tile_ce<Ops>(u[1], u[3]);
+    tile_ce<Ops>(u[0], u[1]);
+    tile_ce<Ops>(u[2], u[3]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) t[i] = u[i];
+  }
+  // smallest of the merged top four = the 4th largest of both lists
+  static __device__ __forceinline__ uint32_t merged_min(const uint32_t (&t)[4], const uint32_t (&s)[4]) {
+    uint32_t u[4];
+    upper(t, s, u);
+    return Ops::min2(Ops::min2(u[0], u[1]), Ops::min2(u[2], u[3]));
+  }
+};
+
+template <typename Ops> struct TileNet<Ops, 2> {
+  static constexpr int kBatch = 2;
+  static __device__ __forceinline__ void sort(uint32_t (&a)[2]) { tile_ce<Ops>(a[0], a[1]); }
+  static __device__ __forceinline__ void merge(uint32_t (&t)[2], const uint32_t (&s)[2]) {
+    uint32_t u0 = Ops::max2(t[0], s[1]);
+    uint32_t u1 = Ops::max2(t[1], s[0]);
+    tile_ce<Ops>(u0, u1);
+    t[0] = u0;
+    t[1] = u1;
+  }
+  static __device__ __forceinline__ uint32_t merged_min(const uint32_t (&t)[2], const uint32_t (&s)[2]) {
+    return Ops::min2(Ops::max2(t[0], s[1]), Ops::max2(t[1], s[0]));
+  }
+};
+
+// J-th largest value per half among the CH words of d (values only).  Two
+// independent running lists (even and odd batches) give the scheduler two chains
+// to interleave; they are combined at the end.
+template <typename Ops, int J, int CH>
+__device__ __forceinline__ uint32_t tile_threshold(const uint32_t (&d)[CH]) {
+  constexpr int N = (J == 3) ? 4 : J;          // three entries: the four-entry network, third largest
+  using Net = TileNet<Ops, N>;
+  constexpr int B = Net::kBatch;
+  constexpr int NB = CH / B;
+  static_assert(CH % (2 * B) == 0 && NB >= 2, "a chunk holds an even number of batches");
+  uint32_t ta[N], tb[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    ta[i] = d[i];
+    tb[i] = d[B + i];
+  }
+  Net::sort(ta);
+  Net::sort(tb);
+#pragma unroll
+  for (int k = 2; k < NB; k += 2) {
+    uint32_t sa[N], sb[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      sa[i] = d[k * B + i];
+      sb[i] = d[(k + 1) * B + i];
+    }
+    Net::sort(sa);
+    Net::sort(sb);
+    Net::merge(ta, sa);
+    Net::merge(tb, sb);
+  }
+  if constexpr (J == 3) {
+    Net::merge(ta, tb);
+    return ta[1];
+  } else {
+    return Net::merged_min(ta, tb);
+  }
+}
+
+// Walks this thread's complete stripes (l_begin + ty, + S, ... < lf) of the two
+// columns at c0 in chunks of CH and leaves their top-J in q[0], q[1] (packed
+// entries).  Returns the first stripe number not visited, like sweep_walk.
+template <typename T, int J, int CH>
+__device__ __forceinline__ long long tile_walk(PackedQueue<T, J, false> (&q)[2], const T* col, long long stripe_stride,
+                                               int ty, int S, long long l_begin, long long lf) {
+  using Ops = Half2Ops<T>;
+  using PQ = PackedQueue<T, J, false>;
+  using Img = PackedImage<T>;
+  const long long l0 = l_begin + ty;
+  const long long total = l0 < lf ? (lf - l0 + S - 1) / S : 0;
+  const long long step = static_cast<long long>(S) * stripe_stride;
+  for (long long i0 = 0; i0 < total; i0 += CH) {
+    const T* ptr = col + (l0 + i0 * S) * stripe_stride;
+    const int cnt = total - i0 < CH ? static_cast<int>(total - i0) : CH;
+    uint32_t d[CH];
+    if (cnt == CH) {
+#pragma unroll
+      for (int i = 0; i < CH; ++i) d[i] = *reinterpret_cast<const uint32_t*>(ptr + i * step);
+    } else {
+      // a short last chunk: the missing stripes read as -inf and are masked out below
+#pragma unroll
+      for (int i = 0; i < CH; ++i) d[i] = i < cnt ? *reinterpret_cast<const uint32_t*>(ptr + i * step) : Ops::kNegInf2;
+    }
+    const uint32_t thr = tile_threshold<Ops, J, CH>(d);
+    // one bit per (column, stripe): 16 stripes per accumulator, low half = even column
+    constexpr int NA = CH / 16;
+    uint32_t acc[NA];
+#pragma unroll
+    for (int a = 0; a < NA; ++a) acc[a] = 0u;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) acc[i / 16] |= Ops::ge(d[i], thr) & (0x00010001u << (i % 16));
+    constexpr int NW = CH >= 32 ? CH / 32 : 1;   // 32-bit mask words per column
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        uint32_t m;
+        if constexpr (CH >= 32) m = __byte_perm(acc[2 * w], acc[2 * w + 1], h ? 0x7632 : 0x5410);
+        else m = h ? (acc[0] >> 16) : (acc[0] & 0xffffu);
+        if (cnt < CH) {
+          const int live = cnt - 32 * w;             // stripes of this word that exist
+          m = live >= 32 ? m : (live <= 0 ? 0u : (m & ((1u << live) - 1u)));
+        }
+        while (m != 0u) {
+          const int bit = 31 - __clz(m);
+          m ^= 1u << bit;
+          const long long i = i0 + 32 * w + bit;
+          const int l = static_cast<int>(l0 + i * S);
+          const uint16_t vb = *reinterpret_cast<const uint16_t*>(col + static_cast<long long>(l) * stripe_stride + h);
+          const uint32_t key = PQ::key_of(Img::word(vb), 0, PQ::low(l));
+          if (key > q[h].k[0]) q[h].push(key);
+        }
+      }
+    }
+  }
+  return l0 + total * S;
+}
+
+}  // namespace atk

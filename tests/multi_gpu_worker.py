@@ -73,6 +73,9 @@ def main() -> int:
             torch.cuda.synchronize(dev)
             v, i = canonical(plan.values.clone(), plan.indices.clone())
             assert torch.equal(i, ei) and torch.equal(v, ev), f"rank {rank}: graph replay differs ({dtype}, b={b})"
+            # a graph that holds a collective must be gone before the process group is torn down
+            del graph
+            torch.cuda.synchronize(dev)
         # rows: each rank computes its span; together they equal the full batch
         g = torch.Generator(device=dev).manual_seed(99)
         x = torch.randn(37, 1 << 14, device=dev, generator=g)
@@ -80,9 +83,10 @@ def main() -> int:
         lo, hi = atd.row_shard(x.shape[0], rank, world)
         v, i = atd.topk_row_sharded(x[lo:hi], 256, j=2)
         assert torch.equal(v, full_v[lo:hi]) and torch.equal(i, full_i[lo:hi])
+        torch.cuda.synchronize(dev)
         dist.barrier()
         if rank == 0:
-            print("MULTI_GPU_OK", world)
+            print("MULTI_GPU_OK", world, flush=True)
     finally:
         dist.destroy_process_group()
     return 0

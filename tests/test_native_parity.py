@@ -404,3 +404,37 @@ def test_long_row_plan_with_preallocated_buffers_and_strided_slab():
     g.replay()
     torch.cuda.synchronize()
     assert_pairs_identical(plan.values.view(1, -1), plan.indices.view(1, -1), ev, ei)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("j", [2, 3, 4])
+def test_stage1_short_columns_two_pass_scan(dtype, j):
+    # 16-bit floats, an even number of buckets and fewer than 256 stripes per thread take the
+    # two-pass scan (threshold from a values-only network, then only the elements at or above it
+    # enter the exact queues): every chunk length (16 / 32 / 64 stripes, several chunks, short last
+    # chunks), a ragged last stripe, stripes split inside the block, tie-heavy rows, rows full of
+    # one value and rows holding -inf must all agree with the serial scan slot for slot.
+    shapes = []
+    for stripes in (j, 5, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 128, 129, 200, 255):
+        if stripes < j:
+            continue
+        for b, rem, rows in ((2, 0, 3), (6, 3, 5), (64, 0, 40), (1026, 17, 2), (4096, 0, 9)):
+            shapes.append((rows, stripes * b + rem, b * j))
+    for seed, (rows, n, k0) in enumerate(shapes):
+        for dist in ("randn", "ties"):
+            check_stage1_exact(make(rows, n, dtype, 3000 + seed, dist), k0, j, True)
+    x = make(4, 64 * 130, dtype, 1)
+    x[0] = 1.5                                    # one value everywhere: the latest stripes win
+    x[1, ::3] = float("-inf")
+    x[2] = float("-inf")
+    x[2, 77] = 0.25
+    x[3, : 64 * 100] = -0.0                       # both zeros tie; the sign of the input is returned
+    x[3, 64 * 100:] = 0.0
+    check_stage1_exact(x, 64 * j, j, True)
+    # the packed hand-off to the select on such shapes (k_mult > 1)
+    for rows, n, k, k_mult in ((70, 65536, 512 * j, 2), (33, 12 * 1000 + 5, 6 * j, 2), (300, 4096, 32 * j, 4)):
+        for dist in ("randn", "ties"):
+            xx = make(rows, n, dtype, 3100 + rows, dist)
+            v, i = api.topk(xx, k, j, k_mult, True)
+            ov, oi = oracle.topk(xx.cpu(), k, j, k_mult, True)
+            assert_valid_selection(xx, v, i, ov)
