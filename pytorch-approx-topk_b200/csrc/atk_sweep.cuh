@@ -190,35 +190,15 @@ __device__ __forceinline__ void store_run(E* dst, const E* src, bool vec) {
   }
 }
 
-// ---------------------------------------------------------------------------
-// Stage 1 only: every block handles one tile of columns of one row and writes
-// the J candidates of each bucket (slot = bucket*J + q, ascending).
-template <typename T, typename Q, int J, int V, bool SKIP, int MODE, bool PACKED_OUT>
-__global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
-sweep_kernel(const SweepParams p) {
+// Write-out of a thread's V queues: the J candidates of bucket c go to slots
+// c*J .. c*J+J-1 in ascending queue order -- as packed entries for the select, as
+// partial candidates of plane z (stripes split over blocks), or as final pairs in
+// the output format of the call.
+template <typename T, typename Q, int J, int V, bool PACKED_OUT>
+__device__ __forceinline__ void sweep_write_out(const SweepParams& p, Q (&q)[V], const T* xrow, long long row,
+                                                long long c0, int z) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
-  extern __shared__ __align__(16) uint32_t sweep_smem[];
-
-  const int tx = threadIdx.x;
-  const int ty = threadIdx.y;
-  const int S = p.s;
-  const long long unit = static_cast<long long>(blockIdx.x) / p.z;        // (row, tile)
-  const int z = static_cast<int>(static_cast<long long>(blockIdx.x) - unit * p.z);
-  const long long row = unit / p.tiles;
-  const long long tile = unit - row * p.tiles;
-  const long long c0 = (tile * p.cw + tx) * V;
-  const bool active = c0 < p.b;
-  const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
-
-  Q q[V];
-#pragma unroll
-  for (int e = 0; e < V; ++e) q[e].init();
-
-  if (active) sweep_scan<T, Q, V, SKIP, MODE>(q, p, xrow, c0, ty, S, z);
-  if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
-  if (!active || ty != 0) return;
-
   if constexpr (PACKED_OUT) {
     // The queue entries go to the select as they are: (image of the value, stripe)
     // words, bucket c in slots c*J .. c*J+J-1, ascending.
@@ -287,6 +267,119 @@ sweep_kernel(const SweepParams p) {
   const bool vec = p.z > 1 ? p.vec_part : p.vec_out;
   store_run<V * J * static_cast<int>(sizeof(Bits))>(vdst, ov, vec);
   store_run<V * J * 8>(idst, oi, vec);
+}
+
+// ---------------------------------------------------------------------------
+// Stage 1 only: every block handles one tile of columns of one row and writes
+// the J candidates of each bucket (slot = bucket*J + q, ascending).
+template <typename T, typename Q, int J, int V, bool SKIP, int MODE, bool PACKED_OUT>
+__global__ void __launch_bounds__(kSweepMaxThreads, ATK_SWEEP_MINBLOCKS)
+sweep_kernel(const SweepParams p) {
+  using Tr = ElemTraits<T>;
+  using Bits = typename Tr::Bits;
+  extern __shared__ __align__(16) uint32_t sweep_smem[];
+
+  const int tx = threadIdx.x;
+  const int ty = threadIdx.y;
+  const int S = p.s;
+  const long long unit = static_cast<long long>(blockIdx.x) / p.z;        // (row, tile)
+  const int z = static_cast<int>(static_cast<long long>(blockIdx.x) - unit * p.z);
+  const long long row = unit / p.tiles;
+  const long long tile = unit - row * p.tiles;
+  const long long c0 = (tile * p.cw + tx) * V;
+  const bool active = c0 < p.b;
+  const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
+
+  Q q[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) q[e].init();
+
+  if (active) sweep_scan<T, Q, V, SKIP, MODE>(q, p, xrow, c0, ty, S, z);
+  if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
+  if (!active || ty != 0) return;
+  sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
+}
+
+// ---------------------------------------------------------------------------
+// Stage 1 for 16-bit float inputs with short columns: a block of 128 threads
+// stages a tile of 256 columns x CH stripes in shared memory with asynchronous
+// 16-byte copies (cp.async, global -> shared without passing through registers)
+// and every thread runs the two-pass scan of atk_tile.cuh on its two columns.
+// Longer columns take several chunks of CH stripes.  Needs: buckets a multiple of
+// 8, rows and stripes 16-byte aligned, no stripe split (p.s == p.z == 1).
+constexpr int kTileThreads = 128;
+constexpr int kTileCols = 2 * kTileThreads;
+// Resident blocks the compiler must allow for (a build knob for measurements).
+#ifndef ATK_TILE_MINBLOCKS
+#define ATK_TILE_MINBLOCKS 6
+#endif
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <typename T, int J, int CH, bool PACKED_OUT>
+__global__ void __launch_bounds__(kTileThreads, ATK_TILE_MINBLOCKS)
+tile_kernel(const SweepParams p) {
+  using Q = PackedQueue<T, J, false>;
+  extern __shared__ __align__(16) uint32_t tile_smem[];     // CH x kTileThreads words
+  const int tx = threadIdx.x;
+  const long long row = static_cast<long long>(blockIdx.x) / p.tiles;
+  const long long tile = static_cast<long long>(blockIdx.x) - row * p.tiles;
+  const long long tile_c0 = tile * kTileCols;
+  const long long c0 = tile_c0 + 2 * tx;
+  const bool active = c0 < p.b;
+  const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
+  long long wcols = p.b - tile_c0;                           // columns of this tile (a multiple of 8)
+  if (wcols > kTileCols) wcols = kTileCols;
+  const int pieces_per_stripe = static_cast<int>(wcols / 8); // 16-byte pieces
+
+  Q q[2];
+  q[0].init();
+  q[1].init();
+  for (long long l0 = 0; l0 < p.l_full; l0 += CH) {
+    const int cnt = p.l_full - l0 < CH ? static_cast<int>(p.l_full - l0) : CH;
+    if (l0 > 0) __syncthreads();                             // the previous chunk has been read
+    const int pieces = cnt * pieces_per_stripe;
+    const T* src = xrow + l0 * p.stripe_stride + tile_c0;
+    if (pieces_per_stripe == kTileCols / 8) {
+      for (int piece = tx; piece < pieces; piece += kTileThreads)
+        cp_async_16(tile_smem + (piece >> 5) * kTileThreads + (piece & 31) * 4,
+                    src + static_cast<long long>(piece >> 5) * p.stripe_stride + (piece & 31) * 8);
+    } else {
+      for (int piece = tx; piece < pieces; piece += kTileThreads) {
+        const int i = piece / pieces_per_stripe;
+        const int c = piece - i * pieces_per_stripe;
+        cp_async_16(tile_smem + i * kTileThreads + c * 4, src + static_cast<long long>(i) * p.stripe_stride + c * 8);
+      }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    if (active) {
+      const uint32_t* words = tile_smem + tx;
+      const int lf = static_cast<int>(l0);
+      if (l0 == 0) {
+        if (cnt == CH) tile_chunk_shared<T, J, CH, kTileThreads, true, true>(q, words, cnt, lf);
+        else tile_chunk_shared<T, J, CH, kTileThreads, false, true>(q, words, cnt, lf);
+      } else {
+        if (cnt == CH) tile_chunk_shared<T, J, CH, kTileThreads, true, false>(q, words, cnt, lf);
+        else tile_chunk_shared<T, J, CH, kTileThreads, false, false>(q, words, cnt, lf);
+      }
+    }
+  }
+  if (!active) return;
+  // ragged last stripe (b does not divide n): only columns < rem exist
+  if (p.rem > 0) {
+    const T* last = xrow + p.l_full * p.stripe_stride + c0;
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+      if (c0 + e < p.rem) q[e].push_tail(load_elem_bits<T>(last + e), static_cast<int>(p.l_full));
+  }
+  sweep_write_out<T, Q, J, 2, PACKED_OUT>(p, q, xrow, row, c0, 0);
 }
 
 // Combine the z partial candidate planes written by a stripe-split sweep: a

@@ -14,6 +14,11 @@ namespace sweep_detail {
 // Stripes per thread from which the head test (skip the insertion when nothing
 // enters) pays off; below it 16-bit float inputs take the tile scan.
 constexpr long long kSkipStripes = 256;
+// Longest columns the shared-memory tile kernel takes (a build knob for measurements).
+#ifndef ATK_TILE_MAX_STRIPES
+#define ATK_TILE_MAX_STRIPES 65535
+#endif
+constexpr long long kTileMaxStripes = ATK_TILE_MAX_STRIPES;
 
 inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
   p.x = a.x;
@@ -173,6 +178,51 @@ int launch_by_j(const SweepLaunch& a) {
   }
 }
 
+// The shared-memory tile kernel: 16-bit float inputs, 2 <= J <= 4, short columns,
+// enough columns that no stripe split is wanted.
+template <typename T, int J>
+int launch_tile_shared_j(const SweepLaunch& a) {
+  using Q = PackedQueue<T, J, false>;
+  SweepParams p;
+  fill_common(p, a, static_cast<int>(sizeof(T)));
+  const long long k0 = a.b * J;
+  p.out_keys = a.out_keys;
+  p.vec_keys = (reinterpret_cast<uintptr_t>(a.out_keys) % 16 == 0) && ((k0 * 4) % 16 == 0);
+  p.tiles = (a.b + kTileCols - 1) / kTileCols;
+  p.cw = kTileThreads;
+  p.s = 1;
+  p.z = 1;
+  p.z_chunk = p.l_full;
+  p.part_vals = nullptr;
+  p.part_idx = nullptr;
+  p.vec_part = 0;
+  if (a.rows * p.tiles >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+  const dim3 grid(static_cast<unsigned>(a.rows * p.tiles));
+  const bool packed = a.out_keys != nullptr;
+#define ATK_LAUNCH_TILE(CH)                                                                          \
+  do {                                                                                               \
+    const size_t smem = static_cast<size_t>(CH) * kTileThreads * 4;                                  \
+    if (packed) tile_kernel<T, J, CH, true><<<grid, kTileThreads, smem, a.stream>>>(p);              \
+    else tile_kernel<T, J, CH, false><<<grid, kTileThreads, smem, a.stream>>>(p);                    \
+  } while (0)
+  if (p.l_full <= 16) ATK_LAUNCH_TILE(16);
+  else if (p.l_full <= 32) ATK_LAUNCH_TILE(32);
+  else ATK_LAUNCH_TILE(64);
+#undef ATK_LAUNCH_TILE
+  note_launch();
+  return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+}
+
+template <typename T>
+int launch_tile_shared(const SweepLaunch& a) {
+  switch (a.j) {
+    case 2: return launch_tile_shared_j<T, 2>(a);
+    case 3: return launch_tile_shared_j<T, 3>(a);
+    case 4: return launch_tile_shared_j<T, 4>(a);
+    default: return ATK_ERR_BAD_J;
+  }
+}
+
 // 16-bit float inputs, queues of two to four entries, columns short enough that no
 // head test would skip insertions: the two-pass tile scan (two columns per thread).
 template <typename T>
@@ -202,6 +252,21 @@ int launch_sweep(const SweepLaunch& a) {
            ((a.stripe_stride * s) % bytes == 0) && (a.b % v == 0);
   };
   if constexpr (ElemTraits<T>::kHalfFloat) {
+#ifndef ATK_NO_TILE_KERNEL
+    {
+      // The shared-memory tile kernel: copies of 16 bytes need 16-byte aligned rows
+      // and stripes; stripe numbers must fit the packed entries; and there must be
+      // enough tiles of 256 columns to occupy the GPU without splitting stripes
+      // (half a wave of its blocks; below that the sweep with its splits takes over).
+      // Measured faster than the insertion queues at every column length from 16 to
+      // 1024 stripes for two to four entries per queue.
+      const long long l_full = a.n / a.b;
+      const long long tiles = (a.b + kTileCols - 1) / kTileCols;
+      if (a.j >= 2 && !a.first_wins && fits(8) && l_full + 1 <= PackedQueue<T, 1, false>::kMaxStripes &&
+          l_full <= kTileMaxStripes && a.b >= kTileCols && a.rows * tiles >= 3ll * a.sm_count)
+        return launch_tile_shared<T>(a);
+    }
+#endif
 #ifdef ATK_TILE_SCAN   // build knob: measured slower than the two-column SIMD queues so far (latency-bound)
     const long long l_full = a.n / a.b;
     if (a.j >= 2 && !a.first_wins && fits(2) && l_full + 1 <= PackedQueue<T, 1, false>::kMaxStripes) {

@@ -4,8 +4,9 @@
 // element at four entries per queue (compares, min/max and the selects that carry
 // the stripe numbers), and that pipe issues 64 lanes per clock and SM: short
 // columns (no head test to skip insertions) are bound by it, not by memory.
-// Here a thread owns two adjacent columns (one 32-bit word per stripe) and holds
-// a chunk of CH stripes of them in registers, then
+// Here a thread owns two adjacent columns (one 32-bit word per stripe) and sees
+// a chunk of CH stripes of them twice (held in registers, tile_walk; or staged in
+// shared memory by asynchronous copies, tile_chunk_shared):
 //   pass 1  finds the J-th largest VALUE of either column in the chunk with a
 //           values-only network of packed fp16x2 / bf16x2 min/max (sorted batches
 //           merged into a running sorted top-J: no stripe numbers are carried);
@@ -95,12 +96,19 @@ __device__ __forceinline__ uint32_t tile_threshold(const uint32_t (&d)[CH]) {
   using Net = TileNet<Ops, N>;
   constexpr int B = Net::kBatch;
   constexpr int NB = CH / B;
-  static_assert(CH % (2 * B) == 0 && NB >= 2, "a chunk holds an even number of batches");
+  static_assert(CH == B || (CH % (2 * B) == 0 && NB >= 2), "one batch, or an even number of batches");
+  if constexpr (NB == 1) {
+    uint32_t t[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) t[i] = d[i];
+    Net::sort(t);
+    return t[N - J];
+  }
   uint32_t ta[N], tb[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) {
     ta[i] = d[i];
-    tb[i] = d[B + i];
+    tb[i] = d[(NB > 1 ? B : 0) + i];
   }
   Net::sort(ta);
   Net::sort(tb);
@@ -182,6 +190,93 @@ __device__ __forceinline__ long long tile_walk(PackedQueue<T, J, false> (&q)[2],
     }
   }
   return l0 + total * S;
+}
+
+// The same two passes over a chunk that asynchronous copies staged in shared
+// memory: `words` points at this thread's word of the chunk's first stripe,
+// consecutive stripes are PITCH words apart (a warp reads consecutive words of a
+// stripe: no bank conflicts).  `cnt` <= CH stripes exist (FULL: cnt == CH); stripe
+// i of the chunk is stripe l_first + i of the column.  Few registers are live (the
+// running lists of the network, the bit accumulators, the queues), so many blocks
+// fit an SM and their copy, network and extraction phases overlap.
+//
+// Pass 1 here is cheaper than the full network: the stripes are cut into groups
+// of kTileGroup, only the group maxima go through the network, and the J-th
+// largest group maximum is the threshold.  It is at most the J-th largest value
+// (J different groups each hold an element at or above it), so the elements at or
+// above it are still a superset of the winners -- about 4.4 instead of 4 of 64 for
+// independent values -- and the exact queues sort it out.
+//
+// Chunks after the first need no network at all: the queues are full by then and
+// the value of their weakest entry -- the J-th largest of everything seen so far
+// -- is a tighter threshold than anything local to the chunk.
+template <int CH> struct TileGroup {
+  // stripes per group: short chunks would let too many elements through with wide groups
+  static constexpr int kSize = CH >= 64 ? 4 : (CH >= 32 ? 2 : 1);
+};
+
+template <typename T, int J, int CH, int PITCH, bool FULL, bool FIRST_CHUNK>
+__device__ __forceinline__ void tile_chunk_shared(PackedQueue<T, J, false> (&q)[2], const uint32_t* words, int cnt,
+                                                  int l_first) {
+  using Ops = Half2Ops<T>;
+  using PQ = PackedQueue<T, J, false>;
+  using Img = PackedImage<T>;
+  auto word = [&](int i) -> uint32_t { return (FULL || i < cnt) ? words[i * PITCH] : Ops::kNegInf2; };
+  uint32_t thr;
+  if constexpr (FIRST_CHUNK) {
+    // pass 1: maxima of groups of stripes, then the J-th largest of them
+    constexpr int kGroup = TileGroup<CH>::kSize;
+    constexpr int G = CH / kGroup;
+    uint32_t gmax[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      uint32_t m = word(g * kGroup);
+#pragma unroll
+      for (int e = 1; e < kGroup; ++e) m = Ops::max2(m, word(g * kGroup + e));
+      gmax[g] = m;
+    }
+    thr = tile_threshold<Ops, J, G>(gmax);
+  } else {
+    // the weakest entries of the two queues, as a value pair (-inf while a queue
+    // is not full, which only NaNs in the first chunk can cause)
+    uint32_t v[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t k0 = q[h].k[0];
+      v[h] = k0 != 0u ? static_cast<uint32_t>(ord16_inverse(k0 >> PQ::kShift)) : (Ops::kNegInf2 & 0xffffu);
+    }
+    thr = v[0] | (v[1] << 16);
+  }
+  // pass 2: one bit per (column, stripe)
+  constexpr int NA = CH / 16;
+  uint32_t acc[NA];
+#pragma unroll
+  for (int a = 0; a < NA; ++a) acc[a] = 0u;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) acc[i / 16] |= Ops::ge(word(i), thr) & (0x00010001u << (i % 16));
+  constexpr int NW = CH >= 32 ? CH / 32 : 1;
+  const uint16_t* halves = reinterpret_cast<const uint16_t*>(words);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      uint32_t m;
+      if constexpr (CH >= 32) m = __byte_perm(acc[2 * w], acc[2 * w + 1], h ? 0x7632 : 0x5410);
+      else m = h ? (acc[0] >> 16) : (acc[0] & 0xffffu);
+      if (!FULL) {
+        const int live = cnt - 32 * w;
+        m = live >= 32 ? m : (live <= 0 ? 0u : (m & ((1u << live) - 1u)));
+      }
+      while (m != 0u) {
+        const int bit = 31 - __clz(m);
+        m ^= 1u << bit;
+        const int i = 32 * w + bit;
+        const uint32_t vb = halves[2 * i * PITCH + h];
+        const uint32_t key = PQ::key_of(Img::word(vb), 0, PQ::low(l_first + i));
+        if (key > q[h].k[0]) q[h].push(key);
+      }
+    }
+  }
 }
 
 }  // namespace atk

@@ -420,6 +420,12 @@ def test_stage1_short_columns_two_pass_scan(dtype, j):
             continue
         for b, rem, rows in ((2, 0, 3), (6, 3, 5), (64, 0, 40), (1026, 17, 2), (4096, 0, 9)):
             shapes.append((rows, stripes * b + rem, b * j))
+    # enough 256-column tiles to occupy the GPU: the shared-memory tile kernel, one chunk, several
+    # chunks (later chunks use the queues' weakest entries as the threshold), a short last chunk, a
+    # ragged last stripe, a partial last tile
+    for rows, b, stripes, rem in ((450, 256, 64, 0), (450, 256, 300, 17), (230, 512, 1100, 0), (120, 1000, 65, 999),
+                                  (500, 264, 16, 0), (460, 256, 33, 5)):
+        shapes.append((rows, stripes * b + rem, b * j))
     for seed, (rows, n, k0) in enumerate(shapes):
         for dist in ("randn", "ties"):
             check_stage1_exact(make(rows, n, dtype, 3000 + seed, dist), k0, j, True)
@@ -431,8 +437,21 @@ def test_stage1_short_columns_two_pass_scan(dtype, j):
     x[3, : 64 * 100] = -0.0                       # both zeros tie; the sign of the input is returned
     x[3, 64 * 100:] = 0.0
     check_stage1_exact(x, 64 * j, j, True)
+    x = make(460, 256 * 130, dtype, 2)            # the same special rows through the tile kernel
+    x[0] = 1.5
+    x[1, ::3] = float("-inf")
+    x[2] = float("-inf")
+    x[2, 77] = 0.25
+    x[3, : 256 * 100] = -0.0
+    x[3, 256 * 100:] = 0.0
+    x[4, 5::7] = float("nan")                     # NaNs are outside the contract; nothing may crash or hang
+    v, i = api.stage1(x, 256 * j, j, True)
+    ov, oi = oracle.stage1(x[:4].cpu(), 256 * j, j, True)
+    assert torch.equal(bits(v[:4]), bits(ov)) and torch.equal(i[:4].cpu(), oi)
+    assert bool(((i[4] >= 0) & (i[4] < x.shape[1])).all())
     # the packed hand-off to the select on such shapes (k_mult > 1)
-    for rows, n, k, k_mult in ((70, 65536, 512 * j, 2), (33, 12 * 1000 + 5, 6 * j, 2), (300, 4096, 32 * j, 4)):
+    for rows, n, k, k_mult in ((70, 65536, 512 * j, 2), (33, 12 * 1000 + 5, 6 * j, 2), (300, 4096, 32 * j, 4),
+                               (500, 65536, 512 * j, 2), (450, 256 * 70 + 3, 64 * j, 4)):
         for dist in ("randn", "ties"):
             xx = make(rows, n, dtype, 3100 + rows, dist)
             v, i = api.topk(xx, k, j, k_mult, True)
