@@ -105,12 +105,10 @@ __device__ __forceinline__ long long sweep_walk(QS (&qs)[V / QS::kCols], const S
 // How a thread scans its columns (template argument MODE of the kernel):
 //   kScanQueues   insertion into the queues of Q, element by element;
 //   kScanSimd     16-bit float inputs on the vector path: two-column SIMD queues
-//                 that are converted to packed entries after the walk;
-//   16 / 32 / 64  16-bit float inputs, two columns per thread, short columns: the
-//                 two-pass tile of atk_tile.cuh with chunks of that many stripes.
+//                 that are converted to packed entries after the walk.
+// (16-bit float inputs with enough columns take tile_kernel below instead.)
 constexpr int kScanQueues = 0;
 constexpr int kScanSimd = 1;
-constexpr int kScanTile = -1;   // launcher-side tag: pick the chunk length from the launch shape
 
 // Scan into q[V].
 template <typename T, typename Q, int V, bool SKIP, int MODE>
@@ -121,10 +119,7 @@ __device__ __forceinline__ void sweep_scan(Q (&q)[V], const SweepParams& p, cons
   long long l_end = l_begin + p.z_chunk;
   if (l_end > p.l_full || z == p.z - 1) l_end = p.l_full;
   long long l;
-  if constexpr (MODE >= 16) {
-    static_assert(V == 2 && Q::kPacked && !Q::kFirst, "the tile scan works on two columns of packed queues");
-    l = tile_walk<T, Q::kJ, MODE>(q, xrow + c0, p.stripe_stride, ty, S, l_begin, l_end);
-  } else if constexpr (MODE == kScanSimd) {
+  if constexpr (MODE == kScanSimd) {
     using QS = Simd16Queue<T, Q::kJ, Q::kFirst>;
     QS qs[V / 2];
 #pragma unroll

@@ -46,34 +46,12 @@ inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
 // ---- stage 1 -----------------------------------------------------------------
 // One launch of the sweep kernel for a scan mode (head-test variant by `skip`).
 template <typename T, typename Q, int J, int V, int MODE, bool PACKED_OUT>
-void launch_sweep_kernel(const dim3& grid, const dim3& block, size_t smem, cudaStream_t stream, const SweepParams& p,
-                         bool skip) {
-  if constexpr (MODE >= 16) {
-    // the tile scan has no head-test variant (it is chosen for short columns)
-    sweep_kernel<T, Q, J, V, false, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
-  } else {
-    if (skip)
-      sweep_kernel<T, Q, J, V, true, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
-    else
-      sweep_kernel<T, Q, J, V, false, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
-  }
-}
-
-// MODE: kScanQueues, kScanSimd, or kScanTile (chunk length picked from the launch shape).
-template <typename T, typename Q, int J, int V, int MODE, bool PACKED_OUT>
 void launch_sweep_mode(const dim3& grid, const dim3& block, size_t smem, cudaStream_t stream, const SweepParams& p,
-                       bool skip, long long stripes_per_thread) {
-  if constexpr (MODE == kScanTile) {
-    // the shortest chunk that holds a thread's stripes (a longer walk loops over chunks of 64)
-    if (stripes_per_thread <= 16)
-      launch_sweep_kernel<T, Q, J, V, 16, PACKED_OUT>(grid, block, smem, stream, p, false);
-    else if (stripes_per_thread <= 32)
-      launch_sweep_kernel<T, Q, J, V, 32, PACKED_OUT>(grid, block, smem, stream, p, false);
-    else
-      launch_sweep_kernel<T, Q, J, V, 64, PACKED_OUT>(grid, block, smem, stream, p, false);
-  } else {
-    launch_sweep_kernel<T, Q, J, V, MODE, PACKED_OUT>(grid, block, smem, stream, p, skip);
-  }
+                       bool skip) {
+  if (skip)
+    sweep_kernel<T, Q, J, V, true, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
+  else
+    sweep_kernel<T, Q, J, V, false, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
 }
 
 template <typename T, typename Q, int J, int V, int MODE>
@@ -119,15 +97,14 @@ int launch_stage1(const SweepLaunch& a) {
   const dim3 block(static_cast<unsigned>(pl.cw), static_cast<unsigned>(pl.S));
   // The head test pays off once a thread walks a long column.
   const bool skip = (pl.z_chunk / pl.S) >= kSkipStripes;
-  const long long stripes_per_thread = (pl.z_chunk + pl.S - 1) / pl.S;
   if constexpr (kCanPack) {
     if (a.out_keys != nullptr) {
-      launch_sweep_mode<T, Q, J, V, MODE, true>(grid, block, smem, a.stream, p, skip, stripes_per_thread);
+      launch_sweep_mode<T, Q, J, V, MODE, true>(grid, block, smem, a.stream, p, skip);
       note_launch();
       return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
     }
   }
-  launch_sweep_mode<T, Q, J, V, MODE, false>(grid, block, smem, a.stream, p, skip, stripes_per_thread);
+  launch_sweep_mode<T, Q, J, V, MODE, false>(grid, block, smem, a.stream, p, skip);
   note_launch();
   if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   if (pl.Z > 1) {
@@ -223,18 +200,6 @@ int launch_tile_shared(const SweepLaunch& a) {
   }
 }
 
-// 16-bit float inputs, queues of two to four entries, columns short enough that no
-// head test would skip insertions: the two-pass tile scan (two columns per thread).
-template <typename T>
-int launch_tile(const SweepLaunch& a) {
-  switch (a.j) {
-    case 2: return launch_stage1<T, PackedQueue<T, 2, false>, 2, 2, kScanTile>(a);
-    case 3: return launch_stage1<T, PackedQueue<T, 3, false>, 3, 2, kScanTile>(a);
-    case 4: return launch_stage1<T, PackedQueue<T, 4, false>, 4, 2, kScanTile>(a);
-    default: return ATK_ERR_BAD_J;
-  }
-}
-
 // Columns per thread.  A vector of V elements is loaded per stripe, so it must
 // be aligned and lie inside one stripe.  The type's preferred vector (16 bytes;
 // 8 bytes for 8-bit elements) by default; for elements of 16 bits or fewer,
@@ -265,13 +230,6 @@ int launch_sweep(const SweepLaunch& a) {
       if (a.j >= 2 && !a.first_wins && fits(8) && l_full + 1 <= PackedQueue<T, 1, false>::kMaxStripes &&
           l_full <= kTileMaxStripes && a.b >= kTileCols && a.rows * tiles >= 3ll * a.sm_count)
         return launch_tile_shared<T>(a);
-    }
-#endif
-#ifdef ATK_TILE_SCAN   // build knob: measured slower than the two-column SIMD queues so far (latency-bound)
-    const long long l_full = a.n / a.b;
-    if (a.j >= 2 && !a.first_wins && fits(2) && l_full + 1 <= PackedQueue<T, 1, false>::kMaxStripes) {
-      const SweepPlan pl = plan_sweep(a.rows, a.b, l_full, 2, a.sm_count);
-      if (pl.z_chunk / pl.S < kSkipStripes) return launch_tile<T>(a);
     }
 #endif
   }

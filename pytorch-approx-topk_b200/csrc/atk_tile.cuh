@@ -5,8 +5,10 @@
 // the stripe numbers), and that pipe issues 64 lanes per clock and SM: short
 // columns (no head test to skip insertions) are bound by it, not by memory.
 // Here a thread owns two adjacent columns (one 32-bit word per stripe) and sees
-// a chunk of CH stripes of them twice (held in registers, tile_walk; or staged in
-// shared memory by asynchronous copies, tile_chunk_shared):
+// a chunk of CH stripes of them, staged in shared memory by asynchronous copies,
+// twice (tile_chunk_shared; holding the chunk in registers instead was measured
+// slower: 156 registers leave too few warps to hide the load and the dependent
+// min/max chains):
 //   pass 1  finds the J-th largest VALUE of either column in the chunk with a
 //           values-only network of packed fp16x2 / bf16x2 min/max (sorted batches
 //           merged into a running sorted top-J: no stripe numbers are carried);
@@ -133,66 +135,7 @@ __device__ __forceinline__ uint32_t tile_threshold(const uint32_t (&d)[CH]) {
   }
 }
 
-// Walks this thread's complete stripes (l_begin + ty, + S, ... < lf) of the two
-// columns at c0 in chunks of CH and leaves their top-J in q[0], q[1] (packed
-// entries).  Returns the first stripe number not visited, like sweep_walk.
-template <typename T, int J, int CH>
-__device__ __forceinline__ long long tile_walk(PackedQueue<T, J, false> (&q)[2], const T* col, long long stripe_stride,
-                                               int ty, int S, long long l_begin, long long lf) {
-  using Ops = Half2Ops<T>;
-  using PQ = PackedQueue<T, J, false>;
-  using Img = PackedImage<T>;
-  const long long l0 = l_begin + ty;
-  const long long total = l0 < lf ? (lf - l0 + S - 1) / S : 0;
-  const long long step = static_cast<long long>(S) * stripe_stride;
-  for (long long i0 = 0; i0 < total; i0 += CH) {
-    const T* ptr = col + (l0 + i0 * S) * stripe_stride;
-    const int cnt = total - i0 < CH ? static_cast<int>(total - i0) : CH;
-    uint32_t d[CH];
-    if (cnt == CH) {
-#pragma unroll
-      for (int i = 0; i < CH; ++i) d[i] = *reinterpret_cast<const uint32_t*>(ptr + i * step);
-    } else {
-      // a short last chunk: the missing stripes read as -inf and are masked out below
-#pragma unroll
-      for (int i = 0; i < CH; ++i) d[i] = i < cnt ? *reinterpret_cast<const uint32_t*>(ptr + i * step) : Ops::kNegInf2;
-    }
-    const uint32_t thr = tile_threshold<Ops, J, CH>(d);
-    // one bit per (column, stripe): 16 stripes per accumulator, low half = even column
-    constexpr int NA = CH / 16;
-    uint32_t acc[NA];
-#pragma unroll
-    for (int a = 0; a < NA; ++a) acc[a] = 0u;
-#pragma unroll
-    for (int i = 0; i < CH; ++i) acc[i / 16] |= Ops::ge(d[i], thr) & (0x00010001u << (i % 16));
-    constexpr int NW = CH >= 32 ? CH / 32 : 1;   // 32-bit mask words per column
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        uint32_t m;
-        if constexpr (CH >= 32) m = __byte_perm(acc[2 * w], acc[2 * w + 1], h ? 0x7632 : 0x5410);
-        else m = h ? (acc[0] >> 16) : (acc[0] & 0xffffu);
-        if (cnt < CH) {
-          const int live = cnt - 32 * w;             // stripes of this word that exist
-          m = live >= 32 ? m : (live <= 0 ? 0u : (m & ((1u << live) - 1u)));
-        }
-        while (m != 0u) {
-          const int bit = 31 - __clz(m);
-          m ^= 1u << bit;
-          const long long i = i0 + 32 * w + bit;
-          const int l = static_cast<int>(l0 + i * S);
-          const uint16_t vb = *reinterpret_cast<const uint16_t*>(col + static_cast<long long>(l) * stripe_stride + h);
-          const uint32_t key = PQ::key_of(Img::word(vb), 0, PQ::low(l));
-          if (key > q[h].k[0]) q[h].push(key);
-        }
-      }
-    }
-  }
-  return l0 + total * S;
-}
-
-// The same two passes over a chunk that asynchronous copies staged in shared
+// The two passes over a chunk that asynchronous copies staged in shared
 // memory: `words` points at this thread's word of the chunk's first stripe,
 // consecutive stripes are PITCH words apart (a warp reads consecutive words of a
 // stripe: no bank conflicts).  `cnt` <= CH stripes exist (FULL: cnt == CH); stripe
