@@ -296,14 +296,21 @@ sweep_kernel(const SweepParams p) {
 }
 
 // ---------------------------------------------------------------------------
-// Stage 1 for 16-bit float inputs with short columns: a block of 128 threads
-// stages a tile of 256 columns x CH stripes in shared memory with asynchronous
-// 16-byte copies (cp.async, global -> shared without passing through registers)
-// and every thread runs the two-pass scan of atk_tile.cuh on its two columns.
-// Longer columns take several chunks of CH stripes.  Needs: buckets a multiple of
-// 8, rows and stripes 16-byte aligned, no stripe split (p.s == p.z == 1).
+// Stage 1 through shared-memory tiles (16-bit floats and float32): a block of 128
+// threads stages a tile of 512 bytes x CH stripes in shared memory with
+// asynchronous 16-byte copies (cp.async, global -> shared without passing through
+// registers) and every thread runs the two-pass scan of atk_tile.cuh on its
+// word of every stripe (two 16-bit columns, or one float32 column).  Longer
+// columns take several chunks of CH stripes; the stripes of a column can also be
+// split over p.z blocks that write partial candidates to scratch planes (p.s is
+// 1).  Needs rows and stripes that are 16-byte aligned and a bucket count that is
+// a multiple of 16 bytes' worth of elements.
 constexpr int kTileThreads = 128;
-constexpr int kTileCols = 2 * kTileThreads;
+template <typename T> struct TileShape {
+  static constexpr int kColsPerThread = sizeof(T) == 2 ? 2 : 1;
+  static constexpr int kCols = kTileThreads * kColsPerThread;       // columns of a tile: 512 bytes per stripe
+  static constexpr int kPerPiece = 16 / static_cast<int>(sizeof(T));  // elements per 16-byte copy
+};
 // Resident blocks the compiler must allow for (a build knob for measurements).
 #ifndef ATK_TILE_MINBLOCKS
 #define ATK_TILE_MINBLOCKS 6
@@ -317,39 +324,55 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 
+template <typename T, int J> struct TileQueue {
+  using type = PackedQueue<T, J, false>;
+};
+template <int J> struct TileQueue<float, J> {
+  using type = FloatQueue<float, J, false>;
+};
+
 template <typename T, int J, int CH, bool PACKED_OUT>
 __global__ void __launch_bounds__(kTileThreads, ATK_TILE_MINBLOCKS)
 tile_kernel(const SweepParams p) {
-  using Q = PackedQueue<T, J, false>;
+  using Q = typename TileQueue<T, J>::type;
+  using Shape = TileShape<T>;
+  constexpr int V = Shape::kColsPerThread;
   extern __shared__ __align__(16) uint32_t tile_smem[];     // CH x kTileThreads words
   const int tx = threadIdx.x;
-  const long long row = static_cast<long long>(blockIdx.x) / p.tiles;
-  const long long tile = static_cast<long long>(blockIdx.x) - row * p.tiles;
-  const long long tile_c0 = tile * kTileCols;
-  const long long c0 = tile_c0 + 2 * tx;
+  const long long unit = static_cast<long long>(blockIdx.x) / p.z;        // (row, tile)
+  const int z = static_cast<int>(static_cast<long long>(blockIdx.x) - unit * p.z);
+  const long long row = unit / p.tiles;
+  const long long tile = unit - row * p.tiles;
+  const long long tile_c0 = tile * Shape::kCols;
+  const long long c0 = tile_c0 + V * tx;
   const bool active = c0 < p.b;
   const T* xrow = static_cast<const T*>(p.x) + row * p.row_stride;
-  long long wcols = p.b - tile_c0;                           // columns of this tile (a multiple of 8)
-  if (wcols > kTileCols) wcols = kTileCols;
-  const int pieces_per_stripe = static_cast<int>(wcols / 8); // 16-byte pieces
+  long long wcols = p.b - tile_c0;                           // columns of this tile (whole 16-byte pieces)
+  if (wcols > Shape::kCols) wcols = Shape::kCols;
+  const int pieces_per_stripe = static_cast<int>(wcols / Shape::kPerPiece);
+  // stripe range of this block (the whole column unless stripes are split over blocks)
+  const long long l_begin = static_cast<long long>(z) * p.z_chunk;
+  long long l_end = l_begin + p.z_chunk;
+  if (l_end > p.l_full || z == p.z - 1) l_end = p.l_full;
 
-  Q q[2];
-  q[0].init();
-  q[1].init();
-  for (long long l0 = 0; l0 < p.l_full; l0 += CH) {
-    const int cnt = p.l_full - l0 < CH ? static_cast<int>(p.l_full - l0) : CH;
-    if (l0 > 0) __syncthreads();                             // the previous chunk has been read
+  Q q[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) q[e].init();
+  for (long long l0 = l_begin; l0 < l_end; l0 += CH) {
+    const int cnt = l_end - l0 < CH ? static_cast<int>(l_end - l0) : CH;
+    if (l0 > l_begin) __syncthreads();                       // the previous chunk has been read
     const int pieces = cnt * pieces_per_stripe;
     const T* src = xrow + l0 * p.stripe_stride + tile_c0;
-    if (pieces_per_stripe == kTileCols / 8) {
+    if (pieces_per_stripe == kTileThreads / 4) {
       for (int piece = tx; piece < pieces; piece += kTileThreads)
         cp_async_16(tile_smem + (piece >> 5) * kTileThreads + (piece & 31) * 4,
-                    src + static_cast<long long>(piece >> 5) * p.stripe_stride + (piece & 31) * 8);
+                    src + static_cast<long long>(piece >> 5) * p.stripe_stride + (piece & 31) * Shape::kPerPiece);
     } else {
       for (int piece = tx; piece < pieces; piece += kTileThreads) {
         const int i = piece / pieces_per_stripe;
         const int c = piece - i * pieces_per_stripe;
-        cp_async_16(tile_smem + i * kTileThreads + c * 4, src + static_cast<long long>(i) * p.stripe_stride + c * 8);
+        cp_async_16(tile_smem + i * kTileThreads + c * 4,
+                    src + static_cast<long long>(i) * p.stripe_stride + c * Shape::kPerPiece);
       }
     }
     cp_async_wait_all();
@@ -357,24 +380,35 @@ tile_kernel(const SweepParams p) {
     if (active) {
       const uint32_t* words = tile_smem + tx;
       const int lf = static_cast<int>(l0);
-      if (l0 == 0) {
-        if (cnt == CH) tile_chunk_shared<T, J, CH, kTileThreads, true, true>(q, words, cnt, lf);
-        else tile_chunk_shared<T, J, CH, kTileThreads, false, true>(q, words, cnt, lf);
+      const bool first = l0 == l_begin;
+      if constexpr (sizeof(T) == 2) {
+        if (first) {
+          if (cnt == CH) tile_chunk_shared<T, J, CH, kTileThreads, true, true>(q, words, cnt, lf);
+          else tile_chunk_shared<T, J, CH, kTileThreads, false, true>(q, words, cnt, lf);
+        } else {
+          if (cnt == CH) tile_chunk_shared<T, J, CH, kTileThreads, true, false>(q, words, cnt, lf);
+          else tile_chunk_shared<T, J, CH, kTileThreads, false, false>(q, words, cnt, lf);
+        }
       } else {
-        if (cnt == CH) tile_chunk_shared<T, J, CH, kTileThreads, true, false>(q, words, cnt, lf);
-        else tile_chunk_shared<T, J, CH, kTileThreads, false, false>(q, words, cnt, lf);
+        if (first) {
+          if (cnt == CH) tile_chunk_shared_f32<J, CH, kTileThreads, true, true>(q[0], words, cnt, lf);
+          else tile_chunk_shared_f32<J, CH, kTileThreads, false, true>(q[0], words, cnt, lf);
+        } else {
+          if (cnt == CH) tile_chunk_shared_f32<J, CH, kTileThreads, true, false>(q[0], words, cnt, lf);
+          else tile_chunk_shared_f32<J, CH, kTileThreads, false, false>(q[0], words, cnt, lf);
+        }
       }
     }
   }
   if (!active) return;
-  // ragged last stripe (b does not divide n): only columns < rem exist
-  if (p.rem > 0) {
+  // ragged last stripe (b does not divide n): only columns < rem exist; it belongs to the last split
+  if (p.rem > 0 && z == p.z - 1) {
     const T* last = xrow + p.l_full * p.stripe_stride + c0;
 #pragma unroll
-    for (int e = 0; e < 2; ++e)
+    for (int e = 0; e < V; ++e)
       if (c0 + e < p.rem) q[e].push_tail(load_elem_bits<T>(last + e), static_cast<int>(p.l_full));
   }
-  sweep_write_out<T, Q, J, 2, PACKED_OUT>(p, q, xrow, row, c0, 0);
+  sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
 }
 
 // Combine the z partial candidate planes written by a stripe-split sweep: a
@@ -509,6 +543,13 @@ inline void set_chunks(SweepPlan& pl, long long l_full) {
   pl.Z = used >= 1 ? used : 1;
 }
 
+// Columns at least this long are never given narrower tiles for in-block splits
+// (a build knob for measurements).
+#ifndef ATK_TRADE_MAX_STRIPES
+#define ATK_TRADE_MAX_STRIPES 2048
+#endif
+constexpr long long kTradeMaxStripes = ATK_TRADE_MAX_STRIPES;
+
 // Threads across columns, stripe splits inside a block (S) and over blocks (Z).
 // Splitting happens only when the columns alone cannot fill the machine, and
 // never beyond what the block size or the stripe count allow.
@@ -531,7 +572,9 @@ inline SweepPlan plan_sweep(long long rows, long long b, long long l_full, int V
     if (pl.S < 1) pl.S = 1;
     // A full-width block leaves no room for splits: trade columns for splits
     // (narrower tiles, more of them) while at least a warp of columns remains.
-    while (pl.S < by_need && pl.S < by_work && pl.cw >= 64 && pl.cw % 2 == 0) {
+    // Not for long columns: those are split over blocks below, which keeps the
+    // blocks reading full-width (2 KiB) pieces of every stripe.
+    while (l_full < kTradeMaxStripes && pl.S < by_need && pl.S < by_work && pl.cw >= 64 && pl.cw % 2 == 0) {
       pl.cw /= 2;
       pl.S *= 2;
     }
@@ -553,6 +596,18 @@ inline SweepPlan plan_sweep(long long rows, long long b, long long l_full, int V
 }
 
 }  // namespace sweep_detail
+
+// Stripe split of the tile kernel: enough blocks for about two waves of its six
+// resident blocks per SM, every split at least 256 stripes long.
+inline long long tile_split(long long rows, long long tiles, long long l_full, int sm_count) {
+  const long long units = rows * tiles;
+  if (units <= 0) return 1;
+  long long z = (12ll * sm_count + units - 1) / units;
+  const long long by_work = l_full / 256;
+  if (z > by_work) z = by_work;
+  if (z > 64) z = 64;
+  return z < 1 ? 1 : z;
+}
 
 // Arguments of the typed launchers (one translation unit per element type).
 struct SweepLaunch {
@@ -585,10 +640,17 @@ inline size_t sweep_workspace_bytes(int elem_size, long long rows, long long n, 
   if (rows <= 0 || b <= 0 || n < b) return 0;
   const int vec = elem_size == 1 ? 8 : 16 / elem_size;   // ElemTraits<T>::kVec by element size
   const sweep_detail::SweepPlan pl = sweep_detail::plan_sweep(rows, b, n / b, (j >= 3 && elem_size <= 2) ? vec / 2 : vec, sm_count);
-  if (pl.Z <= 1) return 0;
+  long long planes = pl.Z;
+  if (elem_size == 2 || elem_size == 4) {
+    // the shared-memory tile kernel (16-bit floats, float32) splits long columns too
+    const long long tile_cols = elem_size == 2 ? 256 : 128;
+    const long long zt = tile_split(rows, (b + tile_cols - 1) / tile_cols, n / b, sm_count);
+    if (zt > planes) planes = zt;
+  }
+  if (planes <= 1) return 0;
   const size_t k0 = static_cast<size_t>(b) * j;
-  return sweep_detail::align256(static_cast<size_t>(pl.Z) * rows * k0 * elem_size) +
-         static_cast<size_t>(pl.Z) * rows * k0 * 8 + 256;
+  return sweep_detail::align256(static_cast<size_t>(planes) * rows * k0 * elem_size) +
+         static_cast<size_t>(planes) * rows * k0 * 8 + 256;
 }
 
 int launch_sweep_f32(const SweepLaunch& a);

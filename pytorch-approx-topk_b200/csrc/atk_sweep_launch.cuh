@@ -16,9 +16,21 @@ namespace sweep_detail {
 constexpr long long kSkipStripes = 256;
 // Longest columns the shared-memory tile kernel takes (a build knob for measurements).
 #ifndef ATK_TILE_MAX_STRIPES
-#define ATK_TILE_MAX_STRIPES 65535
+#define ATK_TILE_MAX_STRIPES 65536
 #endif
-constexpr long long kTileMaxStripes = ATK_TILE_MAX_STRIPES;
+constexpr long long kTileMaxStripes = ATK_TILE_MAX_STRIPES;   // stripe numbers of 16-bit elements: 16 bits
+// Shortest float32 columns the tile kernel takes, for queues of two entries and of
+// three or four (build knobs for measurements).  Measured on 128 x 2^20 rows: two
+// entries 97 us (sweep) against 112 us (tiles) at 32 stripes, even at 128 and 512,
+// and 1.1-1.35x for the tiles on columns of 8192 stripes split over blocks; four
+// entries 140 against 117 us at 64 stripes, 148 against 104 us at 512.  Queues of
+// one entry stay with the sweep for every element type (90 against 118 us).
+#ifndef ATK_TILE_FLOAT_MIN_STRIPES_J2
+#define ATK_TILE_FLOAT_MIN_STRIPES_J2 1024
+#endif
+#ifndef ATK_TILE_FLOAT_MIN_STRIPES
+#define ATK_TILE_FLOAT_MIN_STRIPES 64
+#endif
 
 inline void fill_common(SweepParams& p, const SweepLaunch& a, int elem_size) {
   p.x = a.x;
@@ -155,39 +167,84 @@ int launch_by_j(const SweepLaunch& a) {
   }
 }
 
-// The shared-memory tile kernel: 16-bit float inputs, 2 <= J <= 4, short columns,
-// enough columns that no stripe split is wanted.
+// Returned by the tile launcher (nothing launched) when the shape does not give its
+// kernel enough blocks, e.g. because the scratch for a stripe split is missing: the
+// caller goes on to the sweep kernel.
+constexpr int kTileDeclined = 2;
+
+// The shared-memory tile kernel (tile_kernel): 16-bit floats and float32, 2 <= J <= 4.
 template <typename T, int J>
 int launch_tile_shared_j(const SweepLaunch& a) {
-  using Q = PackedQueue<T, J, false>;
+  using Q = typename TileQueue<T, J>::type;
+  using Bits = typename ElemTraits<T>::Bits;
+  using Shape = TileShape<T>;
+  constexpr bool kCanPack = Q::kPacked;
+  if (a.out_keys != nullptr && !kCanPack) return kPackedUnavailable;
   SweepParams p;
   fill_common(p, a, static_cast<int>(sizeof(T)));
   const long long k0 = a.b * J;
   p.out_keys = a.out_keys;
   p.vec_keys = (reinterpret_cast<uintptr_t>(a.out_keys) % 16 == 0) && ((k0 * 4) % 16 == 0);
-  p.tiles = (a.b + kTileCols - 1) / kTileCols;
+  p.tiles = (a.b + Shape::kCols - 1) / Shape::kCols;
   p.cw = kTileThreads;
   p.s = 1;
-  p.z = 1;
-  p.z_chunk = p.l_full;
+  // stripe split over blocks: as many planes as wanted and as the caller's scratch holds
+  long long Z = a.out_keys != nullptr ? 1 : tile_split(a.rows, p.tiles, p.l_full, a.sm_count);
+  if (Z > 1) {
+    const size_t per_z = static_cast<size_t>(a.rows) * k0 * (sizeof(Bits) + 8);
+    long long fit = 0;
+    if (a.workspace != nullptr && a.workspace_bytes > 256) fit = static_cast<long long>((a.workspace_bytes - 256) / per_z);
+    if (fit < Z) Z = fit >= 2 ? fit : 1;
+  }
+  SweepPlan pl;
+  pl.S = 1;
+  pl.Z = Z;
+  set_chunks(pl, p.l_full);
+  // half a wave of blocks at least; below that the sweep with its in-block splits takes over
+  if (a.rows * p.tiles * pl.Z < 3ll * a.sm_count) return a.out_keys != nullptr ? kPackedUnavailable : kTileDeclined;
+  p.z = static_cast<int>(pl.Z);
+  p.z_chunk = pl.z_chunk;
   p.part_vals = nullptr;
   p.part_idx = nullptr;
   p.vec_part = 0;
-  if (a.rows * p.tiles >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
-  const dim3 grid(static_cast<unsigned>(a.rows * p.tiles));
+  if (pl.Z > 1) {
+    unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+    p.part_vals = ws;
+    p.part_idx = reinterpret_cast<long long*>(ws + align256(static_cast<size_t>(pl.Z) * a.rows * k0 * sizeof(Bits)));
+    p.vec_part = (reinterpret_cast<uintptr_t>(ws) % 16 == 0) && ((k0 * sizeof(Bits)) % 16 == 0) && ((k0 * 8) % 16 == 0);
+  }
+  if (a.rows * p.tiles * pl.Z >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+  const dim3 grid(static_cast<unsigned>(a.rows * p.tiles * pl.Z));
   const bool packed = a.out_keys != nullptr;
+  const long long per_block = pl.z_chunk < p.l_full ? pl.z_chunk : p.l_full;
 #define ATK_LAUNCH_TILE(CH)                                                                          \
   do {                                                                                               \
     const size_t smem = static_cast<size_t>(CH) * kTileThreads * 4;                                  \
-    if (packed) tile_kernel<T, J, CH, true><<<grid, kTileThreads, smem, a.stream>>>(p);              \
-    else tile_kernel<T, J, CH, false><<<grid, kTileThreads, smem, a.stream>>>(p);                    \
+    if constexpr (kCanPack) {                                                                        \
+      if (packed) tile_kernel<T, J, CH, true><<<grid, kTileThreads, smem, a.stream>>>(p);            \
+      else tile_kernel<T, J, CH, false><<<grid, kTileThreads, smem, a.stream>>>(p);                  \
+    } else {                                                                                         \
+      tile_kernel<T, J, CH, false><<<grid, kTileThreads, smem, a.stream>>>(p);                       \
+    }                                                                                                \
   } while (0)
-  if (p.l_full <= 16) ATK_LAUNCH_TILE(16);
-  else if (p.l_full <= 32) ATK_LAUNCH_TILE(32);
+  if (per_block <= 16) ATK_LAUNCH_TILE(16);
+  else if (per_block <= 32) ATK_LAUNCH_TILE(32);
   else ATK_LAUNCH_TILE(64);
 #undef ATK_LAUNCH_TILE
   note_launch();
-  return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
+  if (pl.Z > 1) {
+    int g = 1;                                   // lanes per bucket: about 8 planes per lane
+    while (g < 32 && g * 8 < pl.Z) g *= 2;
+    const long long blocks = (a.rows * a.b * g + 255) / 256;
+    if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+    sweep_merge_planes_kernel<T, J, false><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, a.out_vals, a.out_idx,
+        a.out_row_stride, a.out_format);
+    note_launch();
+    if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
+  }
+  return ATK_OK;
 }
 
 template <typename T>
@@ -216,23 +273,27 @@ int launch_sweep(const SweepLaunch& a) {
     return (reinterpret_cast<uintptr_t>(a.x) % bytes == 0) && ((a.row_stride * s) % bytes == 0) &&
            ((a.stripe_stride * s) % bytes == 0) && (a.b % v == 0);
   };
-  if constexpr (ElemTraits<T>::kHalfFloat) {
 #ifndef ATK_NO_TILE_KERNEL
-    {
-      // The shared-memory tile kernel: copies of 16 bytes need 16-byte aligned rows
-      // and stripes; stripe numbers must fit the packed entries; and there must be
-      // enough tiles of 256 columns to occupy the GPU without splitting stripes
-      // (half a wave of its blocks; below that the sweep with its splits takes over).
-      // Measured faster than the insertion queues at every column length from 16 to
-      // 1024 stripes for two to four entries per queue.
-      const long long l_full = a.n / a.b;
-      const long long tiles = (a.b + kTileCols - 1) / kTileCols;
-      if (a.j >= 2 && !a.first_wins && fits(8) && l_full + 1 <= PackedQueue<T, 1, false>::kMaxStripes &&
-          l_full <= kTileMaxStripes && a.b >= kTileCols && a.rows * tiles >= 3ll * a.sm_count)
-        return launch_tile_shared<T>(a);
+  if constexpr (ElemTraits<T>::kHalfFloat || std::is_same<T, float>::value) {
+    // The shared-memory tile kernel: copies of 16 bytes need 16-byte aligned rows
+    // and stripes and whole 16-byte pieces per stripe; with 16-bit elements the
+    // stripe numbers must fit the packed entries.  16-bit floats: measured faster
+    // than the insertion queues at every column length from 16 to 2048 stripes for
+    // two to four entries per queue.  float32: for long columns, where the sweep
+    // splits stripes over many threads and every split pays for warps that run the
+    // insertion network at almost every stripe until their queues have warmed up.
+    using Shape = TileShape<T>;
+    const long long l_full = a.n / a.b;
+    bool wanted = a.j >= 2 && !a.first_wins && fits(Shape::kPerPiece) && a.b >= Shape::kCols;
+    if (sizeof(T) == 2) wanted = wanted && l_full + 1 <= kTileMaxStripes;
+    else wanted = wanted && l_full >= (a.j == 2 ? ATK_TILE_FLOAT_MIN_STRIPES_J2 : ATK_TILE_FLOAT_MIN_STRIPES) &&
+                    l_full + 1 < (1ll << 31);
+    if (wanted) {
+      const int rc = launch_tile_shared<T>(a);
+      if (rc != kTileDeclined) return rc;
     }
-#endif
   }
+#endif
   if constexpr (sizeof(T) <= 2) {
     constexpr int kHalfVec = kVec / 2;
     if (a.j >= 3 && fits(kHalfVec)) return launch_by_j<T, kHalfVec>(a);

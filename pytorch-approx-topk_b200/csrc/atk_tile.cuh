@@ -222,4 +222,65 @@ __device__ __forceinline__ void tile_chunk_shared(PackedQueue<T, J, false> (&q)[
   }
 }
 
+// ---- float32 columns ---------------------------------------------------------
+// The same two passes for float32, one column per thread (one word per stripe).
+// What it buys here is different: long columns that are split over many blocks.
+// With insertion queues a warp runs the whole insertion network whenever any of
+// its 128 columns takes an element, which is at almost every stripe for the first
+// few hundred stripes of every split; here the threshold compare costs the same
+// at every stripe and only real candidates reach the queue.
+struct FloatWordOps {
+  static constexpr uint32_t kNegInf2 = 0xff800000u;
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    return __float_as_uint(fmaxf(__uint_as_float(a), __uint_as_float(b)));
+  }
+  static __device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) {
+    return __float_as_uint(fminf(__uint_as_float(a), __uint_as_float(b)));
+  }
+};
+
+template <int J, int CH, int PITCH, bool FULL, bool FIRST_CHUNK>
+__device__ __forceinline__ void tile_chunk_shared_f32(FloatQueue<float, J, false>& q, const uint32_t* words, int cnt,
+                                                      int l_first) {
+  using Ops = FloatWordOps;
+  auto word = [&](int i) -> uint32_t { return (FULL || i < cnt) ? words[i * PITCH] : Ops::kNegInf2; };
+  float thr;
+  if constexpr (FIRST_CHUNK) {
+    constexpr int kGroup = TileGroup<CH>::kSize;
+    constexpr int G = CH / kGroup;
+    uint32_t gmax[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      uint32_t m = word(g * kGroup);
+#pragma unroll
+      for (int e = 1; e < kGroup; ++e) m = Ops::max2(m, word(g * kGroup + e));
+      gmax[g] = m;
+    }
+    thr = __uint_as_float(tile_threshold<Ops, J, G>(gmax));
+  } else {
+    thr = q.v[0];        // the J-th largest value so far (-inf while the queue is not full)
+  }
+  constexpr int NW = CH / 32 > 0 ? CH / 32 : 1;
+  uint32_t acc[NW];
+#pragma unroll
+  for (int w = 0; w < NW; ++w) acc[w] = 0u;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) acc[i / 32] |= (__uint_as_float(word(i)) >= thr) ? (1u << (i % 32)) : 0u;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) {
+    uint32_t m = acc[w];
+    if (!FULL) {
+      const int live = cnt - 32 * w;
+      m = live >= 32 ? m : (live <= 0 ? 0u : (m & ((1u << live) - 1u)));
+    }
+    while (m != 0u) {
+      const int bit = 31 - __clz(m);
+      m ^= 1u << bit;
+      const int i = 32 * w + bit;
+      const float v = __uint_as_float(words[i * PITCH]);
+      if (v >= q.v[0]) queue_push_ranked<J, false>(q.v, q.s, v, l_first + i);
+    }
+  }
+}
+
 }  // namespace atk

@@ -457,3 +457,33 @@ def test_stage1_short_columns_two_pass_scan(dtype, j):
             v, i = api.topk(xx, k, j, k_mult, True)
             ov, oi = oracle.topk(xx.cpu(), k, j, k_mult, True)
             assert_valid_selection(xx, v, i, ov)
+
+
+@pytest.mark.parametrize("j", [2, 3, 4])
+def test_stage1_float32_long_columns_tile_kernel(j):
+    # float32 columns of 1024 stripes or more with enough 128-column tiles take the shared-memory
+    # tile kernel: one split, stripes split over blocks (with scratch) and not (without), a ragged
+    # last stripe, a partial last tile, several chunks with a short last one, ties, -inf.
+    # (queues of three or four entries take it from 64 stripes on)
+    for seed, (rows, b, stripes, rem) in enumerate(((4, 4096, 1500, 77), (1, 8192, 2049, 0), (30, 512, 1100, 3),
+                                                    (500, 128, 1024, 0), (7, 1000, 1030, 999), (2, 16384, 1024, 5),
+                                                    (40, 2048, 64, 0), (9, 8192, 100, 4097), (600, 128, 70, 1),
+                                                    (40, 2048, 600, 8))):
+        n, k0 = stripes * b + rem, b * j
+        for dist in ("randn", "ties"):
+            x = make(rows, n, torch.float32, 4000 + seed, dist)
+            if dist == "randn":
+                x[0, ::5] = float("-inf")
+            ov, oi = oracle.stage1(x.cpu(), k0, j, True)
+            for use_workspace in (True, False):
+                v, i = api.stage1(x, k0, j, True, use_workspace=use_workspace)
+                assert torch.equal(bits(v), bits(ov)) and torch.equal(i.cpu(), oi), (rows, b, stripes, rem, dist, use_workspace)
+    # through the operator (second stage behind it) and the slab entry point of the long-row path
+    x = make(2, 2048 * 4096, torch.float32, 4100)
+    v, i = api.topk(x, 2048 * j, j, 2, True)
+    ov, oi = oracle.topk(x.cpu(), 2048 * j, j, 2, True)
+    assert_pairs_identical(v, i, ov, oi)
+    slab = x[0].view(2048, 4096)[:, 1024:3072].contiguous()
+    sv, si = api.stage1_slab(slab, 4096, 1024, j)
+    fv, fi = api.stage1(x[:1], 4096 * j, j, True)
+    assert torch.equal(bits(sv), bits(fv[0, 1024 * j:3072 * j])) and torch.equal(si, fi[0, 1024 * j:3072 * j])
