@@ -168,7 +168,7 @@ int atk_select(const void* cand_vals, const int64_t* cand_idx, int dtype, int64_
  * Limit: when atk_select_workspace_bytes(dtype, rows, k0, k) exceeds the
  * built-in 1 MiB the call is refused with ATK_ERR_SCRATCH_LIMIT and launches
  * nothing (rows of up to 16384 candidates need no scratch at all; one row of
- * 2^21 fp32 candidates needs about 13 KiB; 16 rows of 2^20 about 0.13 MiB).
+ * 2^21 fp32 candidates needs about 33 KiB; 16 rows of 2^20 about 0.45 MiB).
  *
  * First call on a device: looks up the device address of the array
  * (cudaGetSymbolAddress, with that device current) and caches it per device.

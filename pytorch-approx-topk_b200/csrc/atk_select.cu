@@ -24,21 +24,22 @@ namespace {
 constexpr int kSmallMaxK0 = 16384;   // 512 threads x 32 candidates in registers (32-bit keys)
 constexpr int kChunk = 2048;         // candidates per block on the large path
 constexpr int kLargeThreads = 256;
-// Vector loads a thread keeps in flight before it starts computing, in the
-// histogram and in the count kernel of the multi-block path (build knobs; more
-// cost registers and with them resident blocks: 2 measured best for 16-bit
-// elements, 4 for 32-bit ones in the count kernel).
+// Vector loads a thread keeps in flight before it starts computing in the
+// histogram kernel of the multi-block path (a build knob; more cost registers
+// and with them resident blocks).
 // Resident blocks the compiler must allow for in the packed-entry select with at
 // most eight entries per thread (2 and 3 measured alike on 1024 rows x 4096 entries,
 // 65-66 us for the whole operator; leaving it to the compiler cost 10 us).
 #ifndef ATK_SELECT_PACKED_MINBLOCKS
 #define ATK_SELECT_PACKED_MINBLOCKS 2
 #endif
+// Counts of the chunks chained inside the write kernel (1), by a count pass (0), or
+// by the shape (-1); a build knob for measurements.
+#ifndef ATK_SELECT_CHAINED
+#define ATK_SELECT_CHAINED -1
+#endif
 #ifndef ATK_HIST_BATCH
 #define ATK_HIST_BATCH 2
-#endif
-#ifndef ATK_COUNT_BATCH
-#define ATK_COUNT_BATCH (sizeof(Bits) == 4 ? 4 : 2)
 #endif
 #ifndef ATK_SELECT_ROW_THREADS
 #define ATK_SELECT_ROW_THREADS 512
@@ -117,6 +118,22 @@ template <typename K> __device__ __forceinline__ int digit_shift(int pass) {
   return static_cast<int>(sizeof(typename K::Key)) * 8 - 8 - 8 * pass;
 }
 
+// Digits of the multi-block path.  Elements of 32 bits are cut into digits of
+// 11 + 11 + 10 bits (three passes over the candidates instead of four, and 2048
+// bins spread the shared-memory atomics of float keys, whose leading bits are
+// badly skewed); the other widths keep one pass per byte.
+template <typename T> struct LargeDigits {
+  using K = KeyOf<T>;
+  static constexpr bool kWide = sizeof(T) == 4;
+  static constexpr int kPasses = kWide ? 3 : K::kPasses;
+  static constexpr int kBins = kWide ? 2048 : 256;
+  static __host__ __device__ constexpr int width(int pass) { return kWide ? (pass < 2 ? 11 : 10) : 8; }
+  static __host__ __device__ constexpr int shift(int pass) {
+    return kWide ? (pass == 0 ? 21 : (pass == 1 ? 10 : 0))
+                 : static_cast<int>(sizeof(typename K::Key)) * 8 - 8 - 8 * pass;
+  }
+};
+
 // ITEMS consecutive raw candidates of one thread, loaded with the widest
 // vector loads their size allows (16 bytes at a time).
 template <typename B, int ITEMS>
@@ -143,7 +160,8 @@ __device__ __forceinline__ void load_items(const B* __restrict__ row, long long 
 template <typename KEY>
 struct RowState {
   KEY prefix, mask;
-  uint32_t need, pad;
+  uint32_t need;
+  uint32_t gave_up;   // set when a bounded wait of the write kernel ran out (never seen; the row's output is then invalid)
 };
 
 // ---- write-out through shared memory ------------------------------------------
@@ -486,7 +504,45 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
 }
 
 // ------------------------------------------------------------------ large path
-// One radix pass.  Every block histograms its chunk into the row's global
+// Block-wide choice of the bin that holds the need-th largest key: NB bins in
+// shared memory, walked from the top; all kLargeThreads threads take part.
+template <int NB>
+__device__ __forceinline__ void pick_digit_block(const uint32_t* sh, uint32_t need, uint32_t* res /* [2], shared */,
+                                                 uint32_t* wsum /* [kLargeThreads / 32], shared */) {
+  constexpr int P = NB / kLargeThreads;
+  static_assert(P >= 1 && P * kLargeThreads == NB, "bins divide evenly over the block");
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t h[P];
+  uint32_t total = 0;
+#pragma unroll
+  for (int t = 0; t < P; ++t) {
+    h[t] = sh[NB - 1 - (tid * P + t)];
+    total += h[t];
+  }
+  uint32_t incl = total;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += nb;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  uint32_t before = 0;
+#pragma unroll
+  for (int w = 0; w < kLargeThreads / 32; ++w) before += w < warp ? wsum[w] : 0u;
+  uint32_t running = before + incl - total;
+#pragma unroll
+  for (int t = 0; t < P; ++t) {
+    if (running < need && running + h[t] >= need) {
+      res[0] = static_cast<uint32_t>(NB - 1 - (tid * P + t));
+      res[1] = need - running;
+    }
+    running += h[t];
+  }
+  __syncthreads();
+}
+
+// One radix pass.  Every block histograms its chunks into the row's global
 // histogram; the block that finishes last for a row (a ticket counter, no
 // waiting) then picks the digit and advances the row's (prefix, mask, need).
 // `tickets` and `hist` must be zero on entry (one memset per select call).
@@ -495,13 +551,16 @@ __global__ void __launch_bounds__(kLargeThreads)
 select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, long long k0,
                    long long cand_row_stride, int pass, long long k,
                    RowState<typename KeyOf<T>::Key>* __restrict__ state,
-                   uint32_t* __restrict__ hist /* [rows][passes][256] */,
+                   uint32_t* __restrict__ hist /* [rows][passes][bins] */,
                    uint32_t* __restrict__ tickets /* [rows][passes + 1] */, int cpb /* chunks per block */,
                    int vec /* rows are aligned for vector loads */) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
-  __shared__ uint32_t sh[256];
+  using D = LargeDigits<T>;
+  constexpr int NB = D::kBins;
+  __shared__ uint32_t sh[NB];
   __shared__ uint32_t res[2];
+  __shared__ uint32_t wsum[kLargeThreads / 32];
   __shared__ bool last;
   const long long row = blockIdx.y;
   RowState<Key> st;
@@ -509,12 +568,13 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
     st.prefix = 0;
     st.mask = 0;
     st.need = static_cast<uint32_t>(k);
-    st.pad = 0;
+    st.gave_up = 0;
   } else {
     st = state[row];
   }
-  const int shift = digit_shift<K>(pass);
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = 0;
+  const int shift = D::shift(pass);
+  const uint32_t digit_mask = (1u << D::width(pass)) - 1u;
+  for (int i = threadIdx.x; i < NB; i += blockDim.x) sh[i] = 0;
   __syncthreads();
   // The block owns cpb consecutive chunks = one contiguous range of the row.
   // Thread t takes packs t, t + 256, ... of ITEMS consecutive candidates, kHistBatch
@@ -544,29 +604,28 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
         const Key key = K::key(raw[bb][u]);
         bool in = (key & st.mask) == st.prefix;
         if (valid < ITEMS) in = in && u < valid;        // only the last pack of a row is short
-        if (in) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & 255u], 1u);
+        if (in) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
       }
     }
   }
   __syncthreads();
-  uint32_t* gh = hist + (row * K::kPasses + pass) * 256;
-  for (int i = threadIdx.x; i < 256; i += blockDim.x)
+  uint32_t* gh = hist + (row * D::kPasses + pass) * NB;
+  for (int i = threadIdx.x; i < NB; i += blockDim.x)
     if (sh[i]) atomicAdd(&gh[i], sh[i]);
   // publish, then take a ticket; the holder of the last ticket sees every add
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0)
-    last = atomicAdd(&tickets[row * (K::kPasses + 1) + pass], 1u) == gridDim.x - 1;
+    last = atomicAdd(&tickets[row * (D::kPasses + 1) + pass], 1u) == gridDim.x - 1;
   __syncthreads();
   if (!last) return;
   __threadfence();
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) sh[i] = __ldcg(&gh[i]);
+  for (int i = threadIdx.x; i < NB; i += blockDim.x) sh[i] = __ldcg(&gh[i]);
   __syncthreads();
-  if (threadIdx.x < 32) pick_digit(sh, st.need, threadIdx.x, &res[0], &res[1]);
-  __syncthreads();
+  pick_digit_block<NB>(sh, st.need, res, wsum);
   if (threadIdx.x == 0) {
     st.prefix |= static_cast<Key>(res[0]) << shift;
-    st.mask |= static_cast<Key>(255u) << shift;
+    st.mask |= static_cast<Key>(digit_mask) << shift;
     st.need = res[1];
     state[row] = st;
   }
@@ -585,6 +644,7 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
   using K = KeyOf<T>;
   using Key = typename K::Key;
   using Bits = typename ElemTraits<T>::Bits;
+  using D = LargeDigits<T>;
   __shared__ bool last;
   const long long row = blockIdx.y;
   const Key thr = state[row].prefix;
@@ -597,7 +657,7 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
     const int len = static_cast<int>(len_ll);
     const Bits* vchunk = cand_vals + row * cand_row_stride + begin;
     constexpr int kPacks = kLargeThreads / 32;                       // packs per lane
-    constexpr int kBatch = ATK_COUNT_BATCH;
+    constexpr int kBatch = sizeof(Bits) == 4 ? 4 : 2;   // vector loads in flight per lane (more cost registers)
     uint32_t gt = 0, eq = 0;
 #pragma unroll
     for (int b0 = 0; b0 < kPacks; b0 += kBatch) {
@@ -636,7 +696,7 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0)
-    last = atomicAdd(&tickets[row * (K::kPasses + 1) + K::kPasses], 1u) == gridDim.x - 1;
+    last = atomicAdd(&tickets[row * (D::kPasses + 1) + D::kPasses], 1u) == gridDim.x - 1;
   __syncthreads();
   if (!last || threadIdx.x >= 32) return;
   __threadfence();
@@ -661,26 +721,53 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
   }
 }
 
-template <typename T, int ITEMS>
+// Status word of a chunk in the write kernel's chained scan: a flag in the top two
+// bits (0 nothing yet, 1 the chunk's own counts, 2 the counts of the chunk and all
+// chunks before it) over two 31-bit counts (above the threshold, equal to it).
+constexpr unsigned long long kScanOwn = 1ull << 62;
+constexpr unsigned long long kScanAll = 2ull << 62;
+__device__ __forceinline__ unsigned long long scan_pack(unsigned long long gt, unsigned long long eq) {
+  return (gt << 31) | eq;
+}
+// Polls of a predecessor's status word before the write kernel gives up on a row
+// (about a quarter of a second; reached only if a started block stops running).
+constexpr int kScanMaxPolls = 1 << 22;
+
+// The write pass.  Every block takes the next chunk of its row (a ticket, so that a
+// block only ever waits for chunks whose blocks have already started), counts its
+// candidates above / on the threshold, learns how many precede it in the row from
+// the status words of the earlier chunks (a chained scan with look-back: no
+// separate count pass over the candidates), and writes its winners.
+// `tickets` (slot kPasses of the row) and `status` must be zero on entry.
+// With CHAINED false the counts come from select_count_kernel instead (`status`
+// then holds its exclusive prefixes as uint2 per chunk, and chunk = blockIdx.x).
+template <typename T, int ITEMS, bool CHAINED>
 __global__ void __launch_bounds__(kLargeThreads)
 select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                     const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride,
-                    long long k, const RowState<typename KeyOf<T>::Key>* __restrict__ state,
-                    const uint2* __restrict__ bases, void* __restrict__ out_vals, void* __restrict__ out_idx,
+                    long long k, RowState<typename KeyOf<T>::Key>* __restrict__ state,
+                    uint32_t* __restrict__ tickets, unsigned long long* __restrict__ status /* [rows][chunks] */,
+                    void* __restrict__ out_vals, void* __restrict__ out_idx,
                     long long out_row_stride, int out_fmt, int vec) {
   using K = KeyOf<T>;
   using Key = typename K::Key;
+  using D = LargeDigits<T>;
   __shared__ uint32_t wsum[32];
   __shared__ uint32_t block_total;
+  __shared__ uint32_t chunk_s;
+  __shared__ uint32_t base_s[2];
   __shared__ __align__(16) long long sidx[kLargeThreads * ITEMS];
   __shared__ __align__(16) typename ElemTraits<T>::Bits sval[kLargeThreads * ITEMS];
   const long long row = blockIdx.y;
+  if (CHAINED) {
+    if (threadIdx.x == 0) chunk_s = atomicAdd(&tickets[row * (D::kPasses + 1) + D::kPasses], 1u);
+    __syncthreads();
+  }
+  const long long chunk = CHAINED ? static_cast<long long>(chunk_s) : static_cast<long long>(blockIdx.x);
   const Key thr = state[row].prefix;
   const uint32_t need = state[row].need;
   const long long n_gt = k - need;
-  const uint2 b = bases[row * gridDim.x + blockIdx.x];
-  const uint32_t gt_base = b.x, eq_base = b.y;
-  const long long begin = static_cast<long long>(blockIdx.x) * (kLargeThreads * ITEMS);
+  const long long begin = chunk * (kLargeThreads * ITEMS);
   long long end = begin + kLargeThreads * ITEMS;
   if (end > k0) end = k0;
   const auto* vrow = cand_vals + row * cand_row_stride;
@@ -728,11 +815,67 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   }
   __syncthreads();
   const uint32_t excl = wsum[warp] + incl - mine;
+  const uint32_t tot_gt = block_total & 0xffffu;
+  const uint32_t tot_eq = block_total >> 16;
+  // Chained scan over the chunks of the row (warp 0): publish this chunk's counts,
+  // look back over the earlier chunks 32 at a time until one of them already knows
+  // the total of everything before it, then publish this chunk's total as well.
+  if (!CHAINED) {
+    if (threadIdx.x == 0) {
+      const uint2 b = reinterpret_cast<const uint2*>(status)[row * static_cast<long long>(gridDim.x) + chunk];
+      base_s[0] = b.x;
+      base_s[1] = b.y;
+    }
+  } else if (warp == 0) {
+    volatile unsigned long long* st = status + row * static_cast<long long>(gridDim.x);
+    unsigned long long before_gt = 0, before_eq = 0;
+    if (chunk > 0) {
+      if (lane == 0) st[chunk] = kScanOwn | scan_pack(tot_gt, tot_eq);
+      long long j = chunk - 1;
+      int polls = 0;
+      bool done = false;
+      while (!done) {
+        const long long at = j - lane;
+        unsigned long long w = 2ull << 62;                               // before the first chunk: nothing
+        if (at >= 0) w = st[at];
+        const unsigned flag = static_cast<unsigned>(w >> 62);
+        const unsigned ready = __ballot_sync(0xffffffffu, flag != 0u);
+        const unsigned total_known = __ballot_sync(0xffffffffu, flag == 2u);
+        const int stop = total_known ? __ffs(total_known) - 1 : 32;       // nearest chunk that knows its total
+        const unsigned wanted = stop >= 31 ? 0xffffffffu : ((2u << stop) - 1u);
+        if ((ready & wanted) == wanted) {
+          const bool use = lane <= stop;
+          unsigned long long g = use ? ((w >> 31) & 0x7fffffffull) : 0ull;
+          unsigned long long e = use ? (w & 0x7fffffffull) : 0ull;
+#pragma unroll
+          for (int off = 16; off >= 1; off >>= 1) {
+            g += __shfl_xor_sync(0xffffffffu, g, off);
+            e += __shfl_xor_sync(0xffffffffu, e, off);
+          }
+          before_gt += g;
+          before_eq += e;
+          if (stop < 32) done = true;
+          else j -= 32;
+          polls = 0;
+        } else if (++polls > kScanMaxPolls) {
+          if (lane == 0) state[row].gave_up = 1u;     // never seen; the row's output is invalid then
+          done = true;
+        } else {
+          __nanosleep(40);
+        }
+      }
+    }
+    if (lane == 0) {
+      st[chunk] = kScanAll | scan_pack(before_gt + tot_gt, before_eq + tot_eq);
+      base_s[0] = static_cast<uint32_t>(before_gt);
+      base_s[1] = static_cast<uint32_t>(before_eq);
+    }
+  }
+  __syncthreads();
+  const uint32_t gt_base = base_s[0], eq_base = base_s[1];
   // The block's winners occupy two contiguous output ranges: those above the
   // threshold at gt_base ..., the selected ones equal to it at n_gt + eq_base ....
   // They are collected in shared memory in that order and copied out coalesced.
-  const uint32_t tot_gt = block_total & 0xffffu;
-  const uint32_t tot_eq = block_total >> 16;
   uint32_t sel_eq = need > eq_base ? need - eq_base : 0u;   // equal candidates this block may still take
   if (sel_eq > tot_eq) sel_eq = tot_eq;
   uint32_t lgt = excl & 0xffffu;
@@ -768,14 +911,26 @@ inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255);
 // registers, half that for 64-bit elements.
 template <typename T> constexpr int small_max_k0() { return sizeof(T) == 8 ? kSmallMaxK0 / 2 : kSmallMaxK0; }
 
+// Workspace of the multi-block path: [row states][digit histograms | tickets |
+// chunk status words], the bracketed part zeroed at the start of every call.
+template <typename T>
+struct LargeLayout {
+  using D = LargeDigits<T>;
+  size_t state_bytes, hist_words, ticket_words, status_offset, zero_bytes, total;
+  LargeLayout(long long rows, long long k0) {
+    state_bytes = align256(sizeof(RowState<typename KeyOf<T>::Key>) * rows);
+    hist_words = static_cast<size_t>(D::kBins) * D::kPasses * rows;
+    ticket_words = static_cast<size_t>(D::kPasses + 1) * rows;
+    status_offset = ((hist_words + ticket_words) * sizeof(uint32_t) + 7) & ~static_cast<size_t>(7);
+    zero_bytes = status_offset + sizeof(unsigned long long) * chunks_of(k0) * rows;
+    total = state_bytes + align256(zero_bytes);
+  }
+};
+
 template <typename T>
 size_t workspace_typed(long long rows, long long k0) {
   if (k0 <= small_max_k0<T>()) return 0;
-  const size_t state = align256(sizeof(RowState<typename KeyOf<T>::Key>) * rows);
-  // digit histograms followed by the ticket counters: the part zeroed per call
-  const size_t hist = align256(sizeof(uint32_t) * (256 * KeyOf<T>::kPasses + KeyOf<T>::kPasses + 1) * rows);
-  const size_t counts = align256(sizeof(uint2) * chunks_of(k0) * rows);
-  return state + hist + counts;
+  return LargeLayout<T>(rows, k0).total;
 }
 
 template <typename T>
@@ -821,27 +976,25 @@ int select_typed(const SelectLaunch& a) {
     return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
   }
 
-  if (a.k0 >= (1ll << 32) || a.rows > 65535) return ATK_ERR_TOO_LARGE;
-  const size_t need_ws = workspace_typed<T>(a.rows, a.k0);
-  if (a.workspace == nullptr || a.workspace_bytes < need_ws) return ATK_ERR_WORKSPACE;
+  if (a.k0 >= (1ll << 31) || a.rows > 65535) return ATK_ERR_TOO_LARGE;
+  using D = LargeDigits<T>;
+  const LargeLayout<T> lay(a.rows, a.k0);
+  if (a.workspace == nullptr || a.workspace_bytes < lay.total) return ATK_ERR_WORKSPACE;
   const long long chunks = chunks_of(a.k0);
   unsigned char* ws = static_cast<unsigned char*>(a.workspace);
   State* state = reinterpret_cast<State*>(ws);
-  ws += align256(sizeof(State) * a.rows);
+  ws += lay.state_bytes;
   uint32_t* hist = reinterpret_cast<uint32_t*>(ws);
-  const size_t hist_words = static_cast<size_t>(256) * K::kPasses * a.rows;
-  uint32_t* tickets = hist + hist_words;
-  const size_t zero_bytes = sizeof(uint32_t) * (hist_words + static_cast<size_t>(K::kPasses + 1) * a.rows);
-  ws += align256(zero_bytes);
-  uint2* counts = reinterpret_cast<uint2*>(ws);
+  uint32_t* tickets = hist + lay.hist_words;
+  unsigned long long* status = reinterpret_cast<unsigned long long*>(ws + lay.status_offset);
 
-  if (cudaMemsetAsync(hist, 0, zero_bytes, a.stream) != cudaSuccess) return ATK_ERR_CUDA;
+  if (cudaMemsetAsync(hist, 0, lay.zero_bytes, a.stream) != cudaSuccess) return ATK_ERR_CUDA;
   // 8 candidates per thread (2048 per block): 32 per thread with wider chunks was
   // measured 40 % slower on 256 rows x 131072 candidates.
   constexpr int kItems = kChunk / kLargeThreads;
-  // The histogram and count blocks loop over several chunks when there are many
-  // more chunks than the GPU holds blocks, so that the per-block epilogue (global
-  // flush, fence, ticket) is paid once per group of chunks.
+  // The histogram blocks loop over several chunks when there are many more chunks
+  // than the GPU holds blocks, so that the per-block epilogue (global flush,
+  // fence, ticket) is paid once per group of chunks.
   const long long sms = sm_count_of_current_device();
   long long cpb = (a.rows * chunks + sms * 6 - 1) / (sms * 6);
   if (cpb < 1) cpb = 1;
@@ -852,20 +1005,34 @@ int select_typed(const SelectLaunch& a) {
   // vector loads need 16-byte aligned rows of values and of positions
   const int vec = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * sizeof(Bits)) % 16 == 0) &&
                   (reinterpret_cast<uintptr_t>(a.cand_idx) % 16 == 0) && ((a.cand_row_stride * 8) % 16 == 0);
-  for (int pass = 0; pass < K::kPasses; ++pass)
+  for (int pass = 0; pass < D::kPasses; ++pass)
     select_hist_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
         cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
-  // count: one warp per cpw chunks, about one wave of blocks (every block ends with a fence and a ticket)
-  constexpr int kWarps = kLargeThreads / 32;
-  long long cpw = (a.rows * chunks + sms * 8 * kWarps - 1) / (sms * 8 * kWarps);
-  if (cpw < 1) cpw = 1;
-  if (cpw > 16) cpw = 16;
-  const dim3 grid_c(static_cast<unsigned>((chunks + kWarps * cpw - 1) / (kWarps * cpw)), static_cast<unsigned>(a.rows));
-  select_count_kernel<T, kItems><<<grid_c, kLargeThreads, 0, a.stream>>>(
-      cv, a.k0, a.cand_row_stride, state, counts, tickets, static_cast<int>(chunks), static_cast<int>(cpw), vec);
-  select_write_kernel<T, kItems><<<grid, kLargeThreads, 0, a.stream>>>(
-      cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, counts, ov, a.out_idx, a.out_row_stride, a.out_format, vec);
-  note_launch(K::kPasses + 2);
+  // Few chunks in all (a long row or two): the write kernel chains the counts of the
+  // chunks itself (one launch and one pass over the values fewer: 57 -> 47 us on one
+  // row of 2^21).  Many rows: a separate count pass was measured faster (256 rows x
+  // 131072: 290 us against 355 us chained).
+  const bool chained = ATK_SELECT_CHAINED < 0 ? a.rows * chunks <= 4 * sms * 8 : ATK_SELECT_CHAINED != 0;
+  if (chained) {
+    select_write_kernel<T, kItems, true><<<grid, kLargeThreads, 0, a.stream>>>(
+        cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, tickets, status, ov, a.out_idx, a.out_row_stride,
+        a.out_format, vec);
+    note_launch(D::kPasses + 1);
+  } else {
+    // count: one warp per cpw chunks, about one wave of blocks (every block ends with a fence and a ticket)
+    constexpr int kWarps = kLargeThreads / 32;
+    long long cpw = (a.rows * chunks + sms * 8 * kWarps - 1) / (sms * 8 * kWarps);
+    if (cpw < 1) cpw = 1;
+    if (cpw > 16) cpw = 16;
+    const dim3 grid_c(static_cast<unsigned>((chunks + kWarps * cpw - 1) / (kWarps * cpw)), static_cast<unsigned>(a.rows));
+    select_count_kernel<T, kItems><<<grid_c, kLargeThreads, 0, a.stream>>>(
+        cv, a.k0, a.cand_row_stride, state, reinterpret_cast<uint2*>(status), tickets, static_cast<int>(chunks),
+        static_cast<int>(cpw), vec);
+    select_write_kernel<T, kItems, false><<<grid, kLargeThreads, 0, a.stream>>>(
+        cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, tickets, status, ov, a.out_idx, a.out_row_stride,
+        a.out_format, vec);
+    note_launch(D::kPasses + 2);
+  }
   return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
 }
 
