@@ -163,16 +163,28 @@ class LongRowTopK:
         self.stripes = stripes
         self.dtype, self.device = dtype, torch.device(device)
         block = group_width(self.total_buckets, self.world) * j      # candidates per rank, padded groups included
+        self.block = block
         lib = _native.lib()
         code = _native.dtype_code(dtype)
         dev = self.device
+        esize = torch.empty(0, dtype=dtype).element_size()
         with torch.cuda.device(dev):
-            self.local_vals = torch.empty(block, device=dev, dtype=dtype)
-            self.local_idx = torch.empty(block, device=dev, dtype=torch.int64)
             if self.world > 1:
+                # One exchange instead of two: a rank's positions and values travel in one
+                # packed block [block x int64 | block x dtype, padded to 16 bytes]; stage 1
+                # writes straight into views of it, and the gathered blocks are unpacked into
+                # the dense candidate arrays the select reads.
+                self._idx_bytes = block * 8
+                self._block_bytes = (self._idx_bytes + block * esize + 15) // 16 * 16
+                self._packed_local = torch.empty(self._block_bytes, device=dev, dtype=torch.uint8)
+                self._packed_all = torch.empty(self._block_bytes * self.world, device=dev, dtype=torch.uint8)
+                self.local_idx = self._packed_local[:self._idx_bytes].view(torch.int64)
+                self.local_vals = self._packed_local[self._idx_bytes:self._idx_bytes + block * esize].view(dtype)
                 self.cand_vals = torch.empty(block * self.world, device=dev, dtype=dtype)
                 self.cand_idx = torch.empty(block * self.world, device=dev, dtype=torch.int64)
             else:
+                self.local_vals = torch.empty(block, device=dev, dtype=dtype)
+                self.local_idx = torch.empty(block, device=dev, dtype=torch.int64)
                 self.cand_vals, self.cand_idx = self.local_vals, self.local_idx
             ws1 = lib.atk_stage1_slab_workspace_bytes(code, stripes, self.cols, j) if self.cols else 0
             self.stage1_ws = torch.empty(ws1, device=dev, dtype=torch.uint8) if ws1 else None
@@ -204,8 +216,12 @@ class LongRowTopK:
         if self.world > 1:
             # rank g's block is slots [g*block, (g+1)*block); real columns fill the
             # gathered buffer from the front, so its first k0 slots are the candidates
-            dist.all_gather_into_tensor(self.cand_vals, self.local_vals, group=self.group)
-            dist.all_gather_into_tensor(self.cand_idx, self.local_idx, group=self.group)
+            dist.all_gather_into_tensor(self._packed_all, self._packed_local, group=self.group)
+            blocks = self._packed_all.view(self.world, self._block_bytes)
+            esize = self.local_vals.element_size()
+            self.cand_idx.view(self.world, self.block).copy_(blocks[:, :self._idx_bytes].view(torch.int64))
+            self.cand_vals.view(self.world, self.block).copy_(
+                blocks[:, self._idx_bytes:self._idx_bytes + self.block * esize].view(self.dtype))
         mark()
         if self.k0 > self.k:
             _native_select(self.cand_vals[:self.k0], self.cand_idx[:self.k0], self.k,
