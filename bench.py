@@ -438,6 +438,60 @@ def extra_record(name: str, lib, native, dev, stream, steps: int, replays: int, 
     return rec
 
 
+def fused_scores_record(lib, native, dev, stream, steps: int, replays: int, peak: float) -> dict:
+    """The attention-score configuration with the scores produced inside the kernel
+    (atk_score_topk): q [1024, 128] against keys [1024, 65536, 128] in bf16, 16 GiB of keys
+    read per step, the 128 MiB score matrix never written.  Beside it the unfused form:
+    torch.bmm producing the bf16 scores, then atk_topk on them."""
+    w = WORKLOADS["c3"]
+    rows, n, k, j, k_mult, d = w["rows"], w["n"], w["k"], w["j"], w["k_mult"], 128
+    g = torch.Generator(device=dev).manual_seed(4242)
+    q = torch.randn(rows, d, device=dev, generator=g).bfloat16()
+    keys = torch.empty(rows, n, d, device=dev, dtype=torch.bfloat16)
+    flat = keys.view(-1)
+    for off in range(0, flat.numel(), 1 << 28):
+        flat[off:off + (1 << 28)] = torch.randn(min(1 << 28, flat.numel() - off), device=dev, generator=g).bfloat16()
+    code = native.dtype_code(torch.bfloat16)
+    scale = d ** -0.5
+    out_v = torch.empty(rows, k, device=dev, dtype=torch.bfloat16)
+    out_i = torch.empty(rows, k, device=dev, dtype=torch.int64)
+    ws_bytes = lib.atk_score_topk_workspace_bytes(code, rows, n, k, j, k_mult)
+    ws = torch.empty(max(ws_bytes, 1), device=dev, dtype=torch.uint8)
+
+    def fused(i, ptr=None):
+        rc = lib.atk_score_topk(q.data_ptr(), keys.data_ptr(), code, rows, n, d, d, n * d, scale, k, j, k_mult,
+                                out_v.data_ptr(), out_i.data_ptr(), k, ws.data_ptr(), ws_bytes,
+                                stream.cuda_stream if ptr is None else ptr)
+        if rc != 0:
+            raise RuntimeError(native.strerror(rc))
+
+    scores = torch.empty(rows, n, 1, device=dev, dtype=torch.bfloat16)
+    ws2_bytes = lib.atk_topk_workspace_bytes(code, rows, n, k, j, k_mult)
+    ws2 = torch.empty(max(ws2_bytes, 1), device=dev, dtype=torch.uint8)
+    q_col = (q.float() * scale).bfloat16().unsqueeze(-1)
+
+    def unfused(i, ptr=None):
+        torch.bmm(keys, q_col, out=scores)
+        rc = lib.atk_topk(scores.data_ptr(), code, rows, n, n, k, j, k_mult, 1, -1, out_v.data_ptr(), out_i.data_ptr(),
+                          k, ws2.data_ptr(), ws2_bytes, stream.cuda_stream if ptr is None else ptr)
+        if rc != 0:
+            raise RuntimeError(native.strerror(rc))
+
+    rec = {"workload": "bf16 q [1024,128] x keys [1024,65536,128] -> scores * 128^-0.5 -> k=2048, j=4, k_mult=2",
+           "key_bytes_per_step": keys.numel() * 2}
+    for name, fn in (("fused", fused), ("unfused_bmm_then_topk", unfused)):
+        for i in range(2):
+            fn(i)
+        graph = capture_steps(fn, steps, dev)
+        ms = timed_replays(graph, fn, steps, replays, dev, stream, lambda: torch.cuda.synchronize(dev))
+        sp = spread([m / steps for m in ms])
+        rec[name] = {"ms_per_step": sp["mean"], "ms_per_step_min": sp["min"],
+                     "key_read_gbs": keys.numel() * 2 / (sp["mean"] * 1e-3) / 1e9,
+                     "frac_of_measured_peak": keys.numel() * 2 / (sp["mean"] * 1e-3) / 1e9 / peak}
+        del graph
+    return rec
+
+
 def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, replays: int, peak: float) -> dict | None:
     """The one-long-row configuration at this world size (all ranks take part)."""
     import torch.distributed as dist
@@ -645,6 +699,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
             except Exception as exc:
                 extra[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
             torch.cuda.empty_cache()
+        try:
+            extra["c3_fused_scores"] = fused_scores_record(lib, _native, dev, stream, 3, 3, peak)
+        except Exception as exc:
+            extra["c3_fused_scores"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        torch.cuda.empty_cache()
         line["extra"] = extra
     if args.workload == "c2" and not args.no_long_row:
         try:

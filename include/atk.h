@@ -214,6 +214,41 @@ int atk_topk_ex(const void* x, int dtype, int64_t rows, int64_t n, int64_t row_s
                 void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Fused score producer + operator for the attention-score use case (one query
+ * per row against that row's n keys of dimension d): computes
+ *     score[r][i] = round_to_dtype( (sum over t = 0..d-1 of q[r][t] * keys[r][i][t]) * scale )
+ * on the fly -- the products are exact in float32 and accumulated in float32
+ * by warp-wide matrix instructions (the order of the additions inside one
+ * instruction is the hardware's), the scaled sum is rounded once to `dtype`
+ * (nearest even) -- and applies approx_topk.topk(score, k, dim=-1, j, k_mult)
+ * with interleaved buckets to it, without the rows x n scores ever being
+ * written to memory.  No counterpart in the reference, whose users materialise
+ * the scores with a matrix product first (the key-selection experiments behind
+ * its paper's figures).  The selection is exactly atk_topk's on the scores that
+ * atk_scores writes for the same arguments (same arithmetic, bit for bit); a
+ * score of -0.0 is returned as +0.0.
+ *   q      rows x d elements of `dtype` (ATK_F16 or ATK_BF16), row r at q + r*q_row_stride
+ *   keys   rows x n x d elements, the keys of row r at keys + r*keys_row_stride, key i at + i*d;
+ *          16-byte aligned, keys_row_stride a multiple of 8 elements; d = 64 or 128
+ *   out_*  rows x k values (`dtype`) and int64 key positions, as for atk_topk
+ * workspace: atk_score_topk_workspace_bytes() bytes (candidates and select state when k_mult > 1).
+ * Limits: n / (k*k_mult/j) < 65536.
+ *
+ * atk_scores: the scores alone, rows x n elements of `dtype` at out_scores +
+ * r*out_row_stride (the unfused form; also what the fused kernel's selection is
+ * checked against).  At most 65535 rows.
+ */
+int atk_scores(const void* q, const void* keys, int dtype, int64_t rows, int64_t n, int64_t d,
+               int64_t q_row_stride, int64_t keys_row_stride, float scale,
+               void* out_scores, int64_t out_row_stride, void* stream);
+size_t atk_score_topk_workspace_bytes(int dtype, int64_t rows, int64_t n, int64_t k, int j, int64_t k_mult);
+int atk_score_topk(const void* q, const void* keys, int dtype, int64_t rows, int64_t n, int64_t d,
+                   int64_t q_row_stride, int64_t keys_row_stride, float scale,
+                   int64_t k, int j, int64_t k_mult,
+                   void* out_vals, int64_t* out_idx, int64_t out_row_stride,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * k_b = 1 bucketed arg-max with the conventions of
  * experimental/bucketed_argmax.py (topk_torch :18-42, Triton kernels :70-142):
  * k buckets, rows padded to a multiple of k with the dtype's lowest value,

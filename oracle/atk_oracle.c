@@ -79,3 +79,28 @@ static void bucket_geometry(int64_t bucket, int64_t n, int64_t b, int interleave
 #undef ATK_T
 #undef ATK_NAME
 #undef ATK_ISNAN
+
+
+/* Reference scores for the fused producer (include/atk.h, atk_score_topk /
+ * atk_scores): one query per row against the row's n keys, the dot product formed
+ * in double precision (the 16-bit inputs and their products are exact there),
+ * rounded to float and multiplied by `scale` in float.  The caller rounds the
+ * result to the element type.  The kernels accumulate in float32 inside matrix
+ * instructions, so they agree with this to within one unit in the last place of
+ * the 16-bit result (a tolerance, stated in the tests); what the fused kernel
+ * SELECTS is checked exactly, against the operator's oracle applied to the
+ * scores atk_scores wrote.  No counterpart in the reference. */
+int atk_oracle_scores(const float* q, const float* keys, int64_t rows, int64_t n, int64_t d, float scale,
+                      float* out) {
+  if (rows < 0 || n < 0 || d <= 0) return -1;
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* qr = q + r * d;
+    for (int64_t i = 0; i < n; ++i) {
+      const float* kr = keys + (r * n + i) * d;
+      double a = 0.0;
+      for (int64_t t = 0; t < d; ++t) a += (double)kr[t] * (double)qr[t];
+      out[r * n + i] = (float)a * scale;
+    }
+  }
+  return 0;
+}

@@ -168,6 +168,26 @@ def bucketed_argmax(x: torch.Tensor, k: int, interleaved: bool) -> tuple[torch.T
     return vals.to(x.dtype).reshape(*batch, k), idx.reshape(*batch, k)
 
 
+def scores(q: torch.Tensor, keys: torch.Tensor, scale: float) -> torch.Tensor:
+    """Reference scores for the fused producer (atk_score_topk / atk_scores): q [rows, d],
+    keys [rows, n, d] of a 16-bit float type; dot products in double precision, rounded to
+    float, times `scale`, rounded once to the element type.  The kernels agree with it to
+    within one unit in the last place."""
+    rows, n, d = keys.shape
+    qf = q.detach().to("cpu").float().contiguous()
+    kf = keys.detach().to("cpu").float().contiguous()
+    out = torch.empty(rows, n, dtype=torch.float32)
+    f = lib().atk_oracle_scores
+    fp = ctypes.POINTER(ctypes.c_float)
+    f.argtypes = [fp, fp, _i64, _i64, _i64, ctypes.c_float, fp]
+    f.restype = ctypes.c_int
+    rc = f(ctypes.cast(qf.data_ptr(), fp), ctypes.cast(kf.data_ptr(), fp), rows, n, d, float(scale),
+           ctypes.cast(out.data_ptr(), fp))
+    if rc != 0:
+        raise ValueError("atk_oracle_scores rejected the arguments")
+    return out.to(q.dtype)
+
+
 def recall(x: torch.Tensor, approx_vals: torch.Tensor) -> float:
     """Value-threshold recall (reference benchmarks/run_recall.py:27-36)."""
     x2, _ = _rows(x)

@@ -61,6 +61,10 @@ SIGNATURES = {
     "atk_topk": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_topk_ex": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _int, _int, _vp, _vp, _i64, _vp, _sz,
                            _vp]),
+    "atk_scores": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _vp, _i64, _vp]),
+    "atk_score_topk_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64]),
+    "atk_score_topk": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _i64, _int, _i64, _vp, _vp,
+                              _i64, _vp, _sz, _vp]),
     "atk_bucketed_argmax": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _vp, _vp, _i64, _vp, _sz, _vp]),
     "atk_topk_host_scratch_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64, _i64]),
     "atk_topk_host": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _vp, _vp, _vp, _sz, _i64]),

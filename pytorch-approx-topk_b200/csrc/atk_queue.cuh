@@ -162,9 +162,10 @@ template <> struct PackedImage<__half> {
   static constexpr int kBits = 16;
   static __device__ __forceinline__ uint32_t word(uint32_t w) { return ord16x2(w); }
   // Both zeros share one image; the element itself is read back to return the
-  // sign the input had (a load that almost never executes).
+  // sign the input had (a load that almost never executes).  `elem` is null when
+  // the values were never in memory (fused score producer): +0 is returned then.
   static __device__ __forceinline__ uint16_t inverse(uint32_t o, const __half* elem) {
-    if (o == 0x8000u) return ld_stream_2(elem);
+    if (o == 0x8000u) return elem != nullptr ? ld_stream_2(elem) : uint16_t(0);
     return ord16_inverse(o);
   }
 };
@@ -172,7 +173,7 @@ template <> struct PackedImage<__nv_bfloat16> {
   static constexpr int kBits = 16;
   static __device__ __forceinline__ uint32_t word(uint32_t w) { return ord16x2(w); }
   static __device__ __forceinline__ uint16_t inverse(uint32_t o, const __nv_bfloat16* elem) {
-    if (o == 0x8000u) return ld_stream_2(elem);
+    if (o == 0x8000u) return elem != nullptr ? ld_stream_2(elem) : uint16_t(0);
     return ord16_inverse(o);
   }
 };

@@ -228,7 +228,7 @@ __device__ __forceinline__ void sweep_write_out(const SweepParams& p, Q (&q)[V],
         oi[e * J + j] = p.idx_offset + c0 + e;
       } else {
         const long long stripe = q[e].stripe(j);
-        ov[e * J + j] = q[e].value_bits(j, xrow + stripe * p.stripe_stride + c0 + e);
+        ov[e * J + j] = q[e].value_bits(j, xrow != nullptr ? xrow + stripe * p.stripe_stride + c0 + e : nullptr);
         oi[e * J + j] = stripe * p.idx_stride + p.idx_offset + c0 + e;
       }
     }

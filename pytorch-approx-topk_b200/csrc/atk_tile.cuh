@@ -89,11 +89,31 @@ template <typename Ops> struct TileNet<Ops, 2> {
   }
 };
 
+template <typename Ops, int J, int CH>
+__device__ __forceinline__ uint32_t tile_threshold_net(const uint32_t (&d)[CH]);
+
 // J-th largest value per half among the CH words of d (values only).  Two
 // independent running lists (even and odd batches) give the scheduler two chains
 // to interleave; they are combined at the end.
 template <typename Ops, int J, int CH>
 __device__ __forceinline__ uint32_t tile_threshold(const uint32_t (&d)[CH]) {
+  if constexpr (J == 1) {
+    // one entry per queue: the largest value, a balanced tree of maxima
+    uint32_t m[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) m[i] = d[i];
+#pragma unroll
+    for (int w = CH / 2; w >= 1; w /= 2)
+#pragma unroll
+      for (int i = 0; i < w; ++i) m[i] = Ops::max2(m[i], m[i + w]);
+    return m[0];
+  } else {
+    return tile_threshold_net<Ops, J, CH>(d);
+  }
+}
+
+template <typename Ops, int J, int CH>
+__device__ __forceinline__ uint32_t tile_threshold_net(const uint32_t (&d)[CH]) {
   constexpr int N = (J == 3) ? 4 : J;          // three entries: the four-entry network, third largest
   using Net = TileNet<Ops, N>;
   constexpr int B = Net::kBatch;

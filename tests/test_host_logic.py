@@ -226,3 +226,50 @@ def test_reference_cpu_tests_pass_unmodified_against_this_package():
                          timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert " passed" in res.stdout and "failed" not in res.stdout
+
+
+def test_bench_reference_arm_prints_the_contract_line_with_the_gpu_arms_config():
+    # the reference arm (CPU path on the host cores) must describe the same configuration as
+    # the GPU arm does -- the two lines are compared key for key -- and carry the contract's keys
+    import importlib.util
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    res = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                          "--workload", "c4j1"], capture_output=True, text=True, timeout=900, cwd=str(root))
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    spec = importlib.util.spec_from_file_location("atk_bench_cfg", root / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert line["config"] == bench.config_of(bench.WORKLOADS["c4j1"], "c4j1")
+    assert line["impl"] == "reference" and line["metric"] == bench.METRIC and line["unit"] == "rows/s"
+    assert line["higher_is_better"] is True and line["gpu_launches"] == 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["value"] == line["value"]
+    assert line["e2e"] == {"value": line["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["value"] > 0 and abs(line["ms_per_step"] * line["value"] / 1e3 / 4096 - 1.0) < 1e-6
+
+
+def test_bench_host_samples_follow_the_workloads_distribution():
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("atk_bench_data", Path(__file__).resolve().parents[1] / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    # attention scores on the host: N(0, |q|^2 / 128) per row, in bf16
+    x, k, scale = bench.cpu_sample(dict(bench.WORKLOADS["c3"], n=4096), 8)
+    assert x.shape == (8, 4096) and x.dtype == torch.bfloat16 and k == 2048 and scale == 1
+    assert 0.5 < float(x.float().std()) < 1.5
+    # spikes: 16 positions per row stand 8 above the N(0, 2) body
+    x, _, _ = bench.cpu_sample(dict(bench.WORKLOADS["c4j1"], n=8192), 4)
+    assert x.dtype == torch.float16 and int((x.float() > 7.5).sum()) >= 4 * 8
+    # the long row is sampled by a slice with the same bucket length
+    w = bench.WORKLOADS["c5b"]
+    n = 1 << 26
+    assert w["n"] // n == 64 and max(w["k"] // 64, w["j"]) * w["k_mult"] // w["j"] * (w["n"] // (w["k"] * w["k_mult"] // w["j"])) == n
