@@ -1,7 +1,7 @@
 """Benchmark of the bucketed approximate top-k hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--replays R] [--impl ours|reference]
-                    [--workload c2|c3|c4j1|c4j2|c5b] [--no-extra] [--no-long-row] [--no-e2e]
+                    [--workload c2|c3|c4j1|c4j2|c5b|c5bs|c3f] [--rows R] [--no-extra] [--no-long-row] [--no-e2e]
 
 Default workload "c2" (synthetic, seeded) is the configuration the headline
 metric is quoted on — fp32 rows of 2^20 elements ~N(0,1), k = 2^16, j = 2,
@@ -76,6 +76,14 @@ WORKLOADS = {
     "c5b": dict(dtype="float32", rows=1, n=1 << 32, k=1 << 20, j=4, k_mult=2, data="randn", long_row=True,
                 text="one fp32 row of 2^32 ~N(0,1), k=2^20, j=4, k_mult=2; bucket groups sharded over the "
                      "GPUs, all-gather of candidates, exact select over 2^21 candidates"),
+    # a 1/16 slice of the long row with the same column length (8192 stripes), for profiler captures
+    "c5bs": dict(dtype="float32", rows=1, n=1 << 28, k=1 << 16, j=4, k_mult=2, data="randn", long_row=True,
+                 text="one fp32 row of 2^28 ~N(0,1), k=2^16, j=4, k_mult=2 (the long row's 8192 stripes per "
+                      "bucket at 1/16 of its buckets)"),
+    # the attention-score configuration with the scores produced inside the kernel (--rows shrinks it)
+    "c3f": dict(dtype="bfloat16", rows=1024, n=65536, k=2048, j=4, k_mult=2, data="attention", fused=True,
+                text="bf16 q [rows,128] against keys [rows,65536,128], scores q.K^T/sqrt(128) produced inside the "
+                     "kernel, k=2048, j=4, k_mult=2"),
 }
 DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
 DTYPE_TAG = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
@@ -438,13 +446,14 @@ def extra_record(name: str, lib, native, dev, stream, steps: int, replays: int, 
     return rec
 
 
-def fused_scores_record(lib, native, dev, stream, steps: int, replays: int, peak: float) -> dict:
+def fused_scores_record(lib, native, dev, stream, steps: int, replays: int, peak: float, rows: int = 0,
+                        unfused: bool = True) -> dict:
     """The attention-score configuration with the scores produced inside the kernel
     (atk_score_topk): q [1024, 128] against keys [1024, 65536, 128] in bf16, 16 GiB of keys
     read per step, the 128 MiB score matrix never written.  Beside it the unfused form:
     torch.bmm producing the bf16 scores, then atk_topk on them."""
     w = WORKLOADS["c3"]
-    rows, n, k, j, k_mult, d = w["rows"], w["n"], w["k"], w["j"], w["k_mult"], 128
+    rows, n, k, j, k_mult, d = rows or w["rows"], w["n"], w["k"], w["j"], w["k_mult"], 128
     g = torch.Generator(device=dev).manual_seed(4242)
     q = torch.randn(rows, d, device=dev, generator=g).bfloat16()
     keys = torch.empty(rows, n, d, device=dev, dtype=torch.bfloat16)
@@ -470,16 +479,17 @@ def fused_scores_record(lib, native, dev, stream, steps: int, replays: int, peak
     ws2 = torch.empty(max(ws2_bytes, 1), device=dev, dtype=torch.uint8)
     q_col = (q.float() * scale).bfloat16().unsqueeze(-1)
 
-    def unfused(i, ptr=None):
+    def unfused_step(i, ptr=None):
         torch.bmm(keys, q_col, out=scores)
         rc = lib.atk_topk(scores.data_ptr(), code, rows, n, n, k, j, k_mult, 1, -1, out_v.data_ptr(), out_i.data_ptr(),
                           k, ws2.data_ptr(), ws2_bytes, stream.cuda_stream if ptr is None else ptr)
         if rc != 0:
             raise RuntimeError(native.strerror(rc))
 
-    rec = {"workload": "bf16 q [1024,128] x keys [1024,65536,128] -> scores * 128^-0.5 -> k=2048, j=4, k_mult=2",
+    rec = {"workload": f"bf16 q [{rows},128] x keys [{rows},65536,128] -> scores * 128^-0.5 -> k=2048, j=4, k_mult=2",
            "key_bytes_per_step": keys.numel() * 2}
-    for name, fn in (("fused", fused), ("unfused_bmm_then_topk", unfused)):
+    forms = [("fused", fused)] + ([("unfused_bmm_then_topk", unfused_step)] if unfused else [])
+    for name, fn in forms:
         for i in range(2):
             fn(i)
         graph = capture_steps(fn, steps, dev)
@@ -492,13 +502,14 @@ def fused_scores_record(lib, native, dev, stream, steps: int, replays: int, peak
     return rec
 
 
-def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, replays: int, peak: float) -> dict | None:
+def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, replays: int, peak: float,
+                    name: str = "c5b") -> dict | None:
     """The one-long-row configuration at this world size (all ranks take part)."""
     import torch.distributed as dist
 
     from approx_topk import distributed as atd
 
-    w = WORKLOADS["c5b"]
+    w = WORKLOADS[name]
     n, k, j, k_mult = w["n"], w["k"], w["j"], w["k_mult"]
     dtype = DTYPES[w["dtype"]]
     b = k * k_mult // j
@@ -575,9 +586,29 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
     peak, peak_src = measured_hbm_peak()
     replays = max(1, args.replays)
 
+    if w.get("fused"):
+        # --workload c3f: the fused score producer alone is the line
+        rows_f = args.rows or w["rows"]
+        rec = fused_scores_record(lib, _native, dev, stream, args.steps, replays, peak, rows=rows_f, unfused=False)
+        if rank == 0:
+            f = rec["fused"]
+            line = {"metric": METRIC, "value": rows_f / (f["ms_per_step"] * 1e-3), "unit": "rows/s", "n_gpus": world,
+                    "steps": args.steps, "warmup": 2, "ms_per_step": f["ms_per_step"], "replays": replays,
+                    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                    "data": "synthetic", "config": dict(config_of(w, args.workload), rows_per_gpu=rows_f),
+                    "timed_call": "atk_score_topk (C ABI), buffers preallocated, steps in one CUDA graph",
+                    "roofline": {"bound": "hbm", "achieved": f["key_read_gbs"], "peak": peak, "unit": "GB/s",
+                                 "frac": f["frac_of_measured_peak"], "traffic": None,
+                                 "alg_bytes_per_step_per_gpu": rec["key_bytes_per_step"], "peak_source": peak_src},
+                    "e2e": None, "gpu_launches": 2 * args.steps * replays}
+            args.out.emit(json.dumps(line))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
     if w.get("long_row"):
         # --workload c5b: the long row alone is the line
-        rec = long_row_record(rank, world, dev, stream, barrier, args.steps, replays, peak)
+        rec = long_row_record(rank, world, dev, stream, barrier, args.steps, replays, peak, name=args.workload)
         if rank == 0:
             line = {"metric": METRIC, "value": rec["rows_s"], "unit": "rows/s", "n_gpus": world, "steps": args.steps,
                     "warmup": 3, "ms_per_step": rec["ms_per_step"], "replays": replays,
@@ -796,6 +827,7 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="skip the records of the other configurations")
     ap.add_argument("--no-long-row", action="store_true", help="skip the long-row record")
+    ap.add_argument("--rows", type=int, default=0, help="rows of the c3f workload (default 1024; smaller for profiler captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
