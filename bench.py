@@ -90,9 +90,9 @@ DTYPE_TAG = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
 # dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch (the dominant
 # kernel of each workload), from the ncu captures summarised under profiles/.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    "c2": 623_600_000,      # 536.9 MB read + 86.7 MB written (mean of two captured launches)
-    "c3": 152_700_000,      # stage-1 kernel: 134.2 MB read + 18.5 MB written
-    "c4j1": 1_060_650_000,  # stage-1 kernel: 1050.7 MB read + 10.0 MB written
+    "c2": 622_300_000,      # 537.0 MB read + 85.3 MB written (mean of two captured launches)
+    "c3": 142_970_000,      # tile kernel: 134.26 MB read + 8.71 MB written
+    "c4j1": 1_056_300_000,  # stage-1 kernel: 1050.7 MB read + 5.6 MB written
 }
 
 
