@@ -34,6 +34,11 @@ int sm_count_of_current_device() {
   return n;
 }
 
+bool overlapped_launch_enabled() {
+  static const bool on = std::getenv("ATK_NO_OVERLAPPED_LAUNCH") == nullptr;
+  return on;
+}
+
 namespace {
 
 int elem_size(int dtype) {

@@ -16,6 +16,34 @@ void note_launch(int n = 1);
 // Number of SMs of the current device (queried once per device, then cached).
 int sm_count_of_current_device();
 
+// Programmatic dependent launch.  The stage-1 kernels announce at their start that the
+// kernel after them in the stream may be brought onto the GPU; a consumer launched with
+// launch_overlapped() then becomes resident while the producer's last blocks still run,
+// does what does not depend on the producer (index arithmetic, clearing shared memory)
+// and stops at grid_dependency_wait() until the producer has finished and its writes
+// are visible.  Both instructions do nothing in a kernel that was launched the plain way.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// false when ATK_NO_OVERLAPPED_LAUNCH is set in the environment (read once)
+bool overlapped_launch_enabled();
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlapped_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // Where the final (value, position) pairs of a row go, in one of the output
 // formats of include/atk.h: values + int64 positions (the reference's layout),
 // values + int32 positions, or 8-byte records {value bits zero-extended to 32

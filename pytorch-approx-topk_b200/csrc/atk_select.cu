@@ -13,6 +13,7 @@
 //  * large rows: several blocks per row; digit histograms, block counts and
 //    the running (prefix, need) state live in a caller-provided workspace.
 #include <atomic>
+#include <type_traits>
 
 #include "atk_select.cuh"
 #include "atk_block_select.cuh"
@@ -178,6 +179,8 @@ __host__ __device__ inline size_t stage_val_offset(int tile) { return (static_ca
 template <typename B> size_t stage_bytes(long long k) {
   return stage_val_offset(stage_tile(k)) + static_cast<size_t>(stage_tile(k)) * sizeof(B);
 }
+// The packed hand-off stages one (entry, slot) pair of words per output position.
+inline size_t packed_stage_bytes(long long k) { return static_cast<size_t>(stage_tile(k)) * sizeof(uint2); }
 
 // Copies staged entries [0, cnt) to the output row `o` (already advanced to the
 // first destination slot); all threads of the block take part.  `vec`: the
@@ -369,8 +372,16 @@ select_row_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
 // the top bits of an entry are the order-preserving image of the value (the
 // radix digits), the low bits the stripe.  Nothing but the entries is read;
 // value bits and positions are rebuilt for the winners only.
+// Resident blocks the packed kernel is compiled for: what the register file holds at the
+// register count a run of ITEMS entries per thread needs without spilling.
+constexpr int packed_min_blocks(int items, int maxt) {
+  const int regs = items <= 4 ? 40 : (items <= 8 ? 48 : (items <= 16 ? 64 : 96));
+  const int blocks = 65536 / (maxt * regs);
+  return blocks < 1 ? 1 : (blocks > 8 ? 8 : blocks);
+}
+
 template <typename T, int ITEMS, int MAXT, bool FULL>
-__global__ void __launch_bounds__(MAXT, ITEMS <= 8 ? ATK_SELECT_PACKED_MINBLOCKS : 1)
+__global__ void __launch_bounds__(MAXT, packed_min_blocks(ITEMS, MAXT))
 select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const T* __restrict__ x,
                          long long x_row_stride, long long b, int j,
                          void* __restrict__ out_vals, void* __restrict__ out_idx, long long out_row_stride,
@@ -398,6 +409,7 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
     valid = valid < 0 ? 0 : (valid > ITEMS ? ITEMS : valid);
   }
   uint32_t key[ITEMS];
+  grid_dependency_wait();   // the entries are stage 1's output; everything above overlapped its last blocks
   load_items<uint32_t, ITEMS>(krow, slot0, slot0 + valid, FULL || (vec_ok && valid == ITEMS), key);
   __syncthreads();   // histograms are clear
 
@@ -428,15 +440,19 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
     need = misc[1];
   }
 
-  // per-thread counts of entries above / on the threshold value, then the block scan
-  uint32_t mine = 0;
+  // Ranking needs no unpacking: an entry is above the threshold value exactly when it
+  // is above the threshold's largest entry (all stripe bits set), and on or above it
+  // when it is at least the threshold's smallest entry.  Slots past the end of a ragged
+  // row hold entry 0; they are the last slots of the row, so even when they tie with the
+  // threshold every real tie is ranked before them and takes the places there are.
+  const uint32_t top = prefix | PQ::kStripeMask;
+  uint32_t n_above = 0, n_from = 0;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const bool in = FULL || i < valid;
-    const uint32_t v = key[i] & kValMask;
-    mine += (in && v > prefix) ? 1u : 0u;
-    mine += (in && v == prefix) ? 0x10000u : 0u;
+    n_above += key[i] > top ? 1u : 0u;
+    n_from += key[i] >= prefix ? 1u : 0u;
   }
+  const uint32_t mine = n_above + ((n_from - n_above) << 16);
   uint32_t incl = mine;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
@@ -458,48 +474,65 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
   }
   __syncthreads();
   const uint32_t excl = wsum[warp] + incl - mine;
-  uint32_t gt_rank = excl & 0xffffu;
-  uint32_t eq_rank = excl >> 16;
   const uint32_t n_gt = static_cast<uint32_t>(k) - need;
-  int pos[ITEMS];
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    pos[i] = -1;
-    if (FULL || i < valid) {
-      const uint32_t v = key[i] & kValMask;
-      if (v > prefix) {
-        pos[i] = static_cast<int>(gt_rank++);
-      } else if (v == prefix) {
-        if (eq_rank < need) pos[i] = static_cast<int>(n_gt + eq_rank);
-        ++eq_rank;
-      }
-    }
-  }
+  // Winners go to shared memory as (entry, slot) at their output position, one tile of
+  // output positions at a time.  Value bits and positions are rebuilt from there by the
+  // thread that stores them, so that work runs once per winner with the warp converged,
+  // and every store is coalesced.
   const OutRow<Bits> orow(out_vals, out_idx, row, out_row_stride, out_fmt);
   const T* xrow = x + row * x_row_stride;
-  // slot s belongs to bucket s / j
-  const int jshift = j == 1 ? 0 : (j == 2 ? 1 : (j == 4 ? 2 : -1));
+  const int jshift = j == 1 ? 0 : (j == 2 ? 1 : (j == 4 ? 2 : -1));   // slot s belongs to bucket s / j
   extern __shared__ __align__(16) unsigned char stage_smem[];
-  long long* sidx = reinterpret_cast<long long*>(stage_smem);
-  const int tile = stage_tile(k);
-  Bits* sval = reinterpret_cast<Bits*>(stage_smem + stage_val_offset(tile));
-  const bool vec_out = orow.aligned16();
-  for (int base = 0; base < k; base += tile) {
+  uint2* staged = reinterpret_cast<uint2*>(stage_smem);
+  const uint32_t tile = static_cast<uint32_t>(stage_tile(k));
+  auto rebuild = [&](uint2 e, Bits& value, long long& at) {
+    const uint32_t bucket = jshift >= 0 ? (e.y >> jshift) : e.y / 3u;
+    at = static_cast<long long>(e.x & PQ::kStripeMask) * b + bucket;
+    value = Img::inverse(e.x >> PQ::kShift, xrow + at);
+  };
+  for (uint32_t base = 0; base < static_cast<uint32_t>(k); base += tile) {
+    // output position of every entry of this thread, in slot order (ranked again for
+    // every tile: cheaper than keeping the positions in registers)
+    uint32_t gt_rank = (excl & 0xffffu) - base;
+    uint32_t eq_rank = excl >> 16;
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-      const uint32_t rel = static_cast<uint32_t>(pos[i] - base);
-      if (pos[i] >= 0 && rel < static_cast<uint32_t>(tile)) {
-        const int slot = slot0 + i;
-        const long long bucket = jshift >= 0 ? (slot >> jshift) : slot / 3;
-        const long long at = static_cast<long long>(key[i] & PQ::kStripeMask) * b + bucket;
-        sval[rel] = Img::inverse(key[i] >> PQ::kShift, xrow + at);
-        sidx[rel] = at;
-      }
+      const bool above = key[i] > top;
+      const bool tie = !above && key[i] >= prefix;
+      const uint32_t rel = above ? gt_rank : n_gt - base + eq_rank;   // wraps below the tile: never passes
+      if ((above || (tie && eq_rank < need)) && rel < tile)
+        staged[rel] = make_uint2(key[i], static_cast<uint32_t>(slot0 + i));
+      gt_rank += above ? 1u : 0u;
+      eq_rank += tie ? 1u : 0u;
     }
     __syncthreads();
-    const int cnt = k - base < tile ? k - base : tile;
-    stage_copy_out<Bits>(sidx, sval, cnt, orow.at(base), tid, nthr, vec_out);
-    if (base + tile < k) __syncthreads();
+    const int cnt = static_cast<int>(min(tile, static_cast<uint32_t>(k) - base));
+    const OutRow<Bits> o = orow.at(base);
+    // two neighbouring outputs per thread: 16 bytes of positions, one word of values
+    using Pair = typename std::conditional<sizeof(Bits) == 2, uint32_t, uint16_t>::type;
+    const bool pairs = o.fmt == ATK_OUT_I64 && reinterpret_cast<uintptr_t>(o.i) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(o.v) % sizeof(Pair) == 0;
+    int done = 0;
+    if (pairs) {
+      const int np = cnt >> 1;
+      for (int q = tid; q < np; q += nthr) {
+        const uint4 e = reinterpret_cast<const uint4*>(staged)[q];
+        Bits v0, v1;
+        long long a0, a1;
+        rebuild(make_uint2(e.x, e.y), v0, a0);
+        rebuild(make_uint2(e.z, e.w), v1, a1);
+        reinterpret_cast<longlong2*>(o.i)[q] = make_longlong2(a0, a1);
+        reinterpret_cast<Pair*>(o.v)[q] = static_cast<Pair>(static_cast<Pair>(v0) | (static_cast<Pair>(v1) << (8 * sizeof(Bits))));
+      }
+      done = np * 2;
+    }
+    for (int p = done + tid; p < cnt; p += nthr) {
+      Bits v;
+      long long at;
+      rebuild(staged[p], v, at);
+      o.put(p, v, at);
+    }
+    if (base + tile < static_cast<uint32_t>(k)) __syncthreads();
   }
 }
 
@@ -1054,8 +1087,8 @@ size_t select_workspace_bytes(int dtype, long long rows, long long k0) {
 }
 
 namespace {
-// Rows of up to 8192 entries (16 per thread): with 32 per thread the packed form
-// was measured slower than the plain hand-off (88 vs 66 us for 256 rows x 16384).
+// Rows of up to 8192 entries (16 per thread in a block of 512): with 32 per thread the
+// packed form was measured slower than the plain hand-off (88 vs 66 us for 256 rows x 16384).
 constexpr long long kPackedMaxK0 = 8192;
 
 template <typename T>
@@ -1072,19 +1105,37 @@ int select_packed_typed(const SelectPackedLaunch& a) {
   };
   const T* x = static_cast<const T*>(a.x);
   void* ov = a.out_vals;
-#define ATK_LAUNCH_SELECT_PACKED(ITEMS)                                                                   \
+#define ATK_LAUNCH_SELECT_PACKED(ITEMS, MAXT)                                                             \
   do {                                                                                                    \
     if (vec_ok && threads_for(ITEMS) * (ITEMS) == k0)                                                     \
-      select_row_packed_kernel<T, ITEMS, 512, true><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
-          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, a.out_format, vec_ok); \
+      launch_overlapped(select_row_packed_kernel<T, ITEMS, MAXT, true>, dim3(rows), dim3(threads_for(ITEMS)), \
+                        packed_stage_bytes(k), a.stream, a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov,  \
+                        a.out_idx, a.out_row_stride, a.out_format, vec_ok);                               \
     else                                                                                                  \
-      select_row_packed_kernel<T, ITEMS, 512, false><<<rows, threads_for(ITEMS), stage_bytes<Bits>(k), a.stream>>>( \
-          a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov, a.out_idx, a.out_row_stride, a.out_format, vec_ok); \
+      launch_overlapped(select_row_packed_kernel<T, ITEMS, MAXT, false>, dim3(rows), dim3(threads_for(ITEMS)), \
+                        packed_stage_bytes(k), a.stream, a.keys, k0, k, x, a.x_row_stride, a.b, a.j, ov,  \
+                        a.out_idx, a.out_row_stride, a.out_format, vec_ok);                               \
   } while (0)
-  // at least 16 bytes of entries per thread, more until the block is at most 512 wide
-  if (threads_for(4) <= kSelectRowThreads) ATK_LAUNCH_SELECT_PACKED(4);
-  else if (threads_for(8) <= kSelectRowThreads) ATK_LAUNCH_SELECT_PACKED(8);
-  else ATK_LAUNCH_SELECT_PACKED(16);
+#define ATK_LAUNCH_SELECT_PACKED_ITEMS(ITEMS)                                 \
+  do {                                                                        \
+    if (threads_for(ITEMS) <= 128) ATK_LAUNCH_SELECT_PACKED(ITEMS, 128);      \
+    else if (threads_for(ITEMS) <= 256) ATK_LAUNCH_SELECT_PACKED(ITEMS, 256); \
+    else ATK_LAUNCH_SELECT_PACKED(ITEMS, 512);                                \
+  } while (0)
+  // Entries per thread: few threads with long runs beat many threads with short ones
+  // (the per-thread cost of the scans and barriers is spread over more entries; for
+  // bf16 1024 x 4096 -> 2048: 16 per thread 46.4 us for the whole operator, 8 per thread
+  // 48.8, 32 per thread 49.8).  ATK_SELECT_PACKED_ITEMS = 4, 8 or 16 overrides the choice.
+  static const int forced = [] {
+    const char* e = std::getenv("ATK_SELECT_PACKED_ITEMS");
+    return e ? std::atoi(e) : 0;
+  }();
+  int items = k0 >= 4096 ? 16 : (k0 >= 256 ? 8 : 4);
+  if ((forced == 4 || forced == 8 || forced == 16) && threads_for(forced) <= kSelectRowThreads) items = forced;
+  if (items == 4) ATK_LAUNCH_SELECT_PACKED_ITEMS(4);
+  else if (items == 8) ATK_LAUNCH_SELECT_PACKED_ITEMS(8);
+  else ATK_LAUNCH_SELECT_PACKED_ITEMS(16);
+#undef ATK_LAUNCH_SELECT_PACKED_ITEMS
 #undef ATK_LAUNCH_SELECT_PACKED
   note_launch();
   return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;

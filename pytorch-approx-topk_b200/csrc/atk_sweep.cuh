@@ -292,6 +292,10 @@ sweep_kernel(const SweepParams p) {
   if (active) sweep_scan<T, Q, V, SKIP, MODE>(q, p, xrow, c0, ty, S, z);
   if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
   if (!active || ty != 0) return;
+  // The select that reads the packed entries may come onto the GPU once every block has
+  // finished scanning (announcing it at the start of the kernel measured slower: early
+  // select blocks pile up on the SMs that ran out of stage-1 work first).
+  if (PACKED_OUT) grid_launch_dependents();
   sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
 }
 
@@ -408,6 +412,7 @@ tile_kernel(const SweepParams p) {
     for (int e = 0; e < V; ++e)
       if (c0 + e < p.rem) q[e].push_tail(load_elem_bits<T>(last + e), static_cast<int>(p.l_full));
   }
+  if (PACKED_OUT) grid_launch_dependents();   // see sweep_kernel
   sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
 }
 
