@@ -324,9 +324,10 @@ __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src
   const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+// all groups of this thread but the one committed last have arrived
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 
 template <typename T, int J> struct TileQueue {
   using type = PackedQueue<T, J, false>;
@@ -335,13 +336,13 @@ template <int J> struct TileQueue<float, J> {
   using type = FloatQueue<float, J, false>;
 };
 
-template <typename T, int J, int CH, bool PACKED_OUT>
+template <typename T, int J, int CH, bool PACKED_OUT, int BUFS>
 __global__ void __launch_bounds__(kTileThreads, ATK_TILE_MINBLOCKS)
 tile_kernel(const SweepParams p) {
   using Q = typename TileQueue<T, J>::type;
   using Shape = TileShape<T>;
   constexpr int V = Shape::kColsPerThread;
-  extern __shared__ __align__(16) uint32_t tile_smem[];     // CH x kTileThreads words
+  extern __shared__ __align__(16) uint32_t tile_smem[];     // BUFS buffers of CH x kTileThreads words
   const int tx = threadIdx.x;
   const long long unit = static_cast<long long>(blockIdx.x) / p.z;        // (row, tile)
   const int z = static_cast<int>(static_cast<long long>(blockIdx.x) - unit * p.z);
@@ -362,29 +363,47 @@ tile_kernel(const SweepParams p) {
   Q q[V];
 #pragma unroll
   for (int e = 0; e < V; ++e) q[e].init();
-  for (long long l0 = l_begin; l0 < l_end; l0 += CH) {
+  // Long columns (BUFS = 2) go through two buffers of CH stripes in turns: the
+  // copies of chunk c + 1 are in flight while chunk c is scanned.  Columns of a few
+  // chunks use one buffer of twice the stripes instead (the threshold of a longer first
+  // chunk lets fewer elements through, which measured better up to 256 stripes).
+  constexpr int bufs = BUFS;
+  const int n_chunks = l_end > l_begin ? static_cast<int>((l_end - l_begin + CH - 1) / CH) : 0;
+  auto issue = [&](int c) {
+    const long long l0 = l_begin + static_cast<long long>(c) * CH;
     const int cnt = l_end - l0 < CH ? static_cast<int>(l_end - l0) : CH;
-    if (l0 > l_begin) __syncthreads();                       // the previous chunk has been read
+    uint32_t* buf = tile_smem + (c & (bufs - 1)) * (CH * kTileThreads);
     const int pieces = cnt * pieces_per_stripe;
     const T* src = xrow + l0 * p.stripe_stride + tile_c0;
     if (pieces_per_stripe == kTileThreads / 4) {
       for (int piece = tx; piece < pieces; piece += kTileThreads)
-        cp_async_16(tile_smem + (piece >> 5) * kTileThreads + (piece & 31) * 4,
+        cp_async_16(buf + (piece >> 5) * kTileThreads + (piece & 31) * 4,
                     src + static_cast<long long>(piece >> 5) * p.stripe_stride + (piece & 31) * Shape::kPerPiece);
     } else {
       for (int piece = tx; piece < pieces; piece += kTileThreads) {
         const int i = piece / pieces_per_stripe;
-        const int c = piece - i * pieces_per_stripe;
-        cp_async_16(tile_smem + i * kTileThreads + c * 4,
-                    src + static_cast<long long>(i) * p.stripe_stride + c * Shape::kPerPiece);
+        const int c4 = piece - i * pieces_per_stripe;
+        cp_async_16(buf + i * kTileThreads + c4 * 4,
+                    src + static_cast<long long>(i) * p.stripe_stride + c4 * Shape::kPerPiece);
       }
     }
-    cp_async_wait_all();
-    __syncthreads();
+    cp_async_commit();
+  };
+  if (n_chunks > 0) issue(0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (bufs == 2 && c + 1 < n_chunks) {
+      issue(c + 1);
+      cp_async_wait_but_one();
+    } else {
+      cp_async_wait_all();
+    }
+    __syncthreads();                                         // chunk c is in shared memory for every thread
     if (active) {
-      const uint32_t* words = tile_smem + tx;
+      const long long l0 = l_begin + static_cast<long long>(c) * CH;
+      const int cnt = l_end - l0 < CH ? static_cast<int>(l_end - l0) : CH;
+      const uint32_t* words = tile_smem + (c & (bufs - 1)) * (CH * kTileThreads) + tx;
       const int lf = static_cast<int>(l0);
-      const bool first = l0 == l_begin;
+      const bool first = c == 0;
       if constexpr (sizeof(T) == 2) {
         if (first) {
           if (cnt == CH) tile_chunk_shared<T, J, CH, kTileThreads, true, true>(q, words, cnt, lf);
@@ -403,6 +422,8 @@ tile_kernel(const SweepParams p) {
         }
       }
     }
+    if (c + bufs < n_chunks) __syncthreads();                // chunk c has been read: its buffer is filled again
+    if (bufs == 1 && c + 1 < n_chunks) issue(c + 1);
   }
   if (!active) return;
   // ragged last stripe (b does not divide n): only columns < rem exist; it belongs to the last split

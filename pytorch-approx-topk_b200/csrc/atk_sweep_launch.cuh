@@ -217,19 +217,32 @@ int launch_tile_shared_j(const SweepLaunch& a) {
   const dim3 grid(static_cast<unsigned>(a.rows * p.tiles * pl.Z));
   const bool packed = a.out_keys != nullptr;
   const long long per_block = pl.z_chunk < p.l_full ? pl.z_chunk : p.l_full;
-#define ATK_LAUNCH_TILE(CH)                                                                          \
+#define ATK_LAUNCH_TILE(CH, BUFS)                                                                    \
   do {                                                                                               \
-    const size_t smem = static_cast<size_t>(CH) * kTileThreads * 4;                                  \
+    const size_t smem = static_cast<size_t>(BUFS) * (CH) * kTileThreads * 4;                         \
     if constexpr (kCanPack) {                                                                        \
-      if (packed) tile_kernel<T, J, CH, true><<<grid, kTileThreads, smem, a.stream>>>(p);            \
-      else tile_kernel<T, J, CH, false><<<grid, kTileThreads, smem, a.stream>>>(p);                  \
+      if (packed) tile_kernel<T, J, CH, true, BUFS><<<grid, kTileThreads, smem, a.stream>>>(p);      \
+      else tile_kernel<T, J, CH, false, BUFS><<<grid, kTileThreads, smem, a.stream>>>(p);            \
     } else {                                                                                         \
-      tile_kernel<T, J, CH, false><<<grid, kTileThreads, smem, a.stream>>>(p);                       \
+      tile_kernel<T, J, CH, false, BUFS><<<grid, kTileThreads, smem, a.stream>>>(p);                 \
     }                                                                                                \
   } while (0)
-  if (per_block <= 16) ATK_LAUNCH_TILE(16);
-  else if (per_block <= 32) ATK_LAUNCH_TILE(32);
-  else ATK_LAUNCH_TILE(64);
+  // Up to 256 stripes per block: one buffer of up to 64 stripes, filled and scanned in
+  // turns.  Longer columns: two buffers of 32 stripes, the copies of one in flight while
+  // the other is scanned (fp16 256 x 2^20, j=4: 512 stripes 100.3 -> 98.0 us, 2048
+  // stripes 195.2 -> 190.8; fp32 4 x 2^26 j=4 197 -> 188; at 128 and 256 stripes the
+  // shorter chunks cost more than the overlap gives: 114.8 -> 129.5 and 103.0 -> 110.4).
+  // ATK_TILE_BUFS = 1 or 2 overrides the choice (an experiment knob).
+  static const int forced_bufs = [] {
+    const char* e = std::getenv("ATK_TILE_BUFS");
+    return e ? std::atoi(e) : 0;
+  }();
+  int bufs = per_block >= 512 ? 2 : 1;
+  if (forced_bufs == 1 || forced_bufs == 2) bufs = forced_bufs;
+  if (bufs == 2) ATK_LAUNCH_TILE(32, 2);
+  else if (per_block <= 16) ATK_LAUNCH_TILE(16, 1);
+  else if (per_block <= 32) ATK_LAUNCH_TILE(32, 1);
+  else ATK_LAUNCH_TILE(64, 1);
 #undef ATK_LAUNCH_TILE
   note_launch();
   if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
