@@ -506,6 +506,7 @@ select_row_packed_kernel(const uint32_t* __restrict__ keys, int k0, int k, const
       eq_rank += tie ? 1u : 0u;
     }
     __syncthreads();
+    grid_launch_dependents();   // the next kernel in the stream may come onto the GPU
     const int cnt = static_cast<int>(min(tile, static_cast<uint32_t>(k) - base));
     const OutRow<Bits> o = orow.at(base);
     // two neighbouring outputs per thread: 16 bytes of positions, one word of values

@@ -273,6 +273,9 @@ sweep_kernel(const SweepParams p) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
   extern __shared__ __align__(16) uint32_t sweep_smem[];
+  // Launched overlapped with the end of the kernel before it in the stream: nothing is
+  // read or written before that kernel has finished.
+  grid_dependency_wait();
 
   const int tx = threadIdx.x;
   const int ty = threadIdx.y;
@@ -292,10 +295,12 @@ sweep_kernel(const SweepParams p) {
   if (active) sweep_scan<T, Q, V, SKIP, MODE>(q, p, xrow, c0, ty, S, z);
   if (S > 1) sweep_merge<Q, V>(q, sweep_smem, p.cw, tx, ty, S);
   if (!active || ty != 0) return;
-  // The select that reads the packed entries may come onto the GPU once every block has
-  // finished scanning (announcing it at the start of the kernel measured slower: early
-  // select blocks pile up on the SMs that ran out of stage-1 work first).
-  if (PACKED_OUT) grid_launch_dependents();
+  // The kernel after this one (the select that reads the packed entries, or the next
+  // call's stage 1) may come onto the GPU once every block has finished scanning; it
+  // waits for this kernel's end before it touches memory.  (Announcing it at the start of
+  // the kernel measured slower: early blocks of the select pile up on the SMs that ran
+  // out of stage-1 work first.)
+  grid_launch_dependents();
   sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
 }
 
@@ -343,6 +348,7 @@ tile_kernel(const SweepParams p) {
   using Shape = TileShape<T>;
   constexpr int V = Shape::kColsPerThread;
   extern __shared__ __align__(16) uint32_t tile_smem[];     // BUFS buffers of CH x kTileThreads words
+  grid_dependency_wait();   // see sweep_kernel
   const int tx = threadIdx.x;
   const long long unit = static_cast<long long>(blockIdx.x) / p.z;        // (row, tile)
   const int z = static_cast<int>(static_cast<long long>(blockIdx.x) - unit * p.z);
@@ -433,7 +439,7 @@ tile_kernel(const SweepParams p) {
     for (int e = 0; e < V; ++e)
       if (c0 + e < p.rem) q[e].push_tail(load_elem_bits<T>(last + e), static_cast<int>(p.l_full));
   }
-  if (PACKED_OUT) grid_launch_dependents();   // see sweep_kernel
+  grid_launch_dependents();   // see sweep_kernel
   sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
 }
 

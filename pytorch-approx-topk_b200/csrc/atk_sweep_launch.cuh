@@ -61,9 +61,9 @@ template <typename T, typename Q, int J, int V, int MODE, bool PACKED_OUT>
 void launch_sweep_mode(const dim3& grid, const dim3& block, size_t smem, cudaStream_t stream, const SweepParams& p,
                        bool skip) {
   if (skip)
-    sweep_kernel<T, Q, J, V, true, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
+    launch_overlapped(sweep_kernel<T, Q, J, V, true, MODE, PACKED_OUT>, grid, block, smem, stream, p);
   else
-    sweep_kernel<T, Q, J, V, false, MODE, PACKED_OUT><<<grid, block, smem, stream>>>(p);
+    launch_overlapped(sweep_kernel<T, Q, J, V, false, MODE, PACKED_OUT>, grid, block, smem, stream, p);
 }
 
 template <typename T, typename Q, int J, int V, int MODE>
@@ -221,10 +221,10 @@ int launch_tile_shared_j(const SweepLaunch& a) {
   do {                                                                                               \
     const size_t smem = static_cast<size_t>(BUFS) * (CH) * kTileThreads * 4;                         \
     if constexpr (kCanPack) {                                                                        \
-      if (packed) tile_kernel<T, J, CH, true, BUFS><<<grid, kTileThreads, smem, a.stream>>>(p);      \
-      else tile_kernel<T, J, CH, false, BUFS><<<grid, kTileThreads, smem, a.stream>>>(p);            \
+      if (packed) launch_overlapped(tile_kernel<T, J, CH, true, BUFS>, grid, dim3(kTileThreads), smem, a.stream, p); \
+      else launch_overlapped(tile_kernel<T, J, CH, false, BUFS>, grid, dim3(kTileThreads), smem, a.stream, p); \
     } else {                                                                                         \
-      tile_kernel<T, J, CH, false, BUFS><<<grid, kTileThreads, smem, a.stream>>>(p);                 \
+      launch_overlapped(tile_kernel<T, J, CH, false, BUFS>, grid, dim3(kTileThreads), smem, a.stream, p); \
     }                                                                                                \
   } while (0)
   // Up to 256 stripes per block: one buffer of up to 64 stripes, filled and scanned in
