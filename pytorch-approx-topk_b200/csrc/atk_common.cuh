@@ -28,9 +28,10 @@ __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepco
 // false when ATK_NO_OVERLAPPED_LAUNCH is set in the environment (read once)
 bool overlapped_launch_enabled();
 
+// `overlap` false: a plain launch of the same kernel.
 template <typename... Params, typename... Args>
-inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
-                                     cudaStream_t stream, Args&&... args) {
+inline cudaError_t launch_overlapped_if(bool overlap, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -40,8 +41,14 @@ inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = overlapped_launch_enabled() ? 1 : 0;
+  cfg.numAttrs = overlap && overlapped_launch_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
+  return launch_overlapped_if(true, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
 }
 
 // Where the final (value, position) pairs of a row go, in one of the output

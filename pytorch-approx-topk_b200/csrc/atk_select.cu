@@ -601,6 +601,10 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   __shared__ uint32_t wsum[kLargeThreads / 32];
   __shared__ bool last;
   const long long row = blockIdx.y;
+  for (int i = threadIdx.x; i < NB; i += blockDim.x) sh[i] = 0;
+  // launched overlapped with the end of the kernel before it (the pass before, or the
+  // producer of the candidates): nothing of global memory is touched before it has ended
+  grid_dependency_wait();
   RowState<Key> st;
   if (pass == 0) {
     st.prefix = 0;
@@ -612,7 +616,6 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
   }
   const int shift = D::shift(pass);
   const uint32_t digit_mask = (1u << D::width(pass)) - 1u;
-  for (int i = threadIdx.x; i < NB; i += blockDim.x) sh[i] = 0;
   __syncthreads();
   // The block owns cpb consecutive chunks = one contiguous range of the row.
   // Thread t takes packs t, t + 256, ... of ITEMS consecutive candidates, kHistBatch
@@ -647,6 +650,7 @@ select_hist_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, l
     }
   }
   __syncthreads();
+  grid_launch_dependents();   // the next pass may come onto the GPU; it waits for this one to end
   uint32_t* gh = hist + (row * D::kPasses + pass) * NB;
   for (int i = threadIdx.x; i < NB; i += blockDim.x)
     if (sh[i]) atomicAdd(&gh[i], sh[i]);
@@ -684,6 +688,7 @@ select_count_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals, 
   using Bits = typename ElemTraits<T>::Bits;
   using D = LargeDigits<T>;
   __shared__ bool last;
+  grid_dependency_wait();   // see select_hist_kernel
   const long long row = blockIdx.y;
   const Key thr = state[row].prefix;
   const int lane = threadIdx.x & 31;
@@ -796,6 +801,7 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
   __shared__ uint32_t base_s[2];
   __shared__ __align__(16) long long sidx[kLargeThreads * ITEMS];
   __shared__ __align__(16) typename ElemTraits<T>::Bits sval[kLargeThreads * ITEMS];
+  grid_dependency_wait();   // see select_hist_kernel
   const long long row = blockIdx.y;
   if (CHAINED) {
     if (threadIdx.x == 0) chunk_s = atomicAdd(&tickets[row * (D::kPasses + 1) + D::kPasses], 1u);
@@ -1043,18 +1049,22 @@ int select_typed(const SelectLaunch& a) {
   // vector loads need 16-byte aligned rows of values and of positions
   const int vec = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * sizeof(Bits)) % 16 == 0) &&
                   (reinterpret_cast<uintptr_t>(a.cand_idx) % 16 == 0) && ((a.cand_row_stride * 8) % 16 == 0);
+  // Few chunks in all (a long row or two): every launch overlaps the end of the one before
+  // it (one row of 2^21: 46.3 -> 45.0 us).  With many blocks per launch the early blocks
+  // crowd the SMs that finish first (256 rows x 131072: 259.7 -> 264.4 us): plain launches.
+  const bool small = a.rows * chunks <= 4 * sms * 8;
   for (int pass = 0; pass < D::kPasses; ++pass)
-    select_hist_kernel<T, kItems><<<grid_g, kLargeThreads, 0, a.stream>>>(
-        cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
+    launch_overlapped_if(small, select_hist_kernel<T, kItems>, grid_g, dim3(kLargeThreads), 0, a.stream,
+                      cv, a.k0, a.cand_row_stride, pass, a.k, state, hist, tickets, static_cast<int>(cpb), vec);
   // Few chunks in all (a long row or two): the write kernel chains the counts of the
   // chunks itself (one launch and one pass over the values fewer: 57 -> 47 us on one
   // row of 2^21).  Many rows: a separate count pass was measured faster (256 rows x
   // 131072: 290 us against 355 us chained).
-  const bool chained = ATK_SELECT_CHAINED < 0 ? a.rows * chunks <= 4 * sms * 8 : ATK_SELECT_CHAINED != 0;
+  const bool chained = ATK_SELECT_CHAINED < 0 ? small : ATK_SELECT_CHAINED != 0;
   if (chained) {
-    select_write_kernel<T, kItems, true><<<grid, kLargeThreads, 0, a.stream>>>(
-        cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, tickets, status, ov, a.out_idx, a.out_row_stride,
-        a.out_format, vec);
+    launch_overlapped_if(small, select_write_kernel<T, kItems, true>, grid, dim3(kLargeThreads), 0, a.stream,
+                      cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, tickets, status, ov, a.out_idx,
+                      a.out_row_stride, a.out_format, vec);
     note_launch(D::kPasses + 1);
   } else {
     // count: one warp per cpw chunks, about one wave of blocks (every block ends with a fence and a ticket)
@@ -1063,12 +1073,12 @@ int select_typed(const SelectLaunch& a) {
     if (cpw < 1) cpw = 1;
     if (cpw > 16) cpw = 16;
     const dim3 grid_c(static_cast<unsigned>((chunks + kWarps * cpw - 1) / (kWarps * cpw)), static_cast<unsigned>(a.rows));
-    select_count_kernel<T, kItems><<<grid_c, kLargeThreads, 0, a.stream>>>(
-        cv, a.k0, a.cand_row_stride, state, reinterpret_cast<uint2*>(status), tickets, static_cast<int>(chunks),
-        static_cast<int>(cpw), vec);
-    select_write_kernel<T, kItems, false><<<grid, kLargeThreads, 0, a.stream>>>(
-        cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, tickets, status, ov, a.out_idx, a.out_row_stride,
-        a.out_format, vec);
+    launch_overlapped_if(small, select_count_kernel<T, kItems>, grid_c, dim3(kLargeThreads), 0, a.stream,
+                      cv, a.k0, a.cand_row_stride, state, reinterpret_cast<uint2*>(status), tickets,
+                      static_cast<int>(chunks), static_cast<int>(cpw), vec);
+    launch_overlapped_if(small, select_write_kernel<T, kItems, false>, grid, dim3(kLargeThreads), 0, a.stream,
+                      cv, a.cand_idx, a.k0, a.cand_row_stride, a.k, state, tickets, status, ov, a.out_idx,
+                      a.out_row_stride, a.out_format, vec);
     note_launch(D::kPasses + 2);
   }
   return cudaGetLastError() == cudaSuccess ? ATK_OK : ATK_ERR_CUDA;
