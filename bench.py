@@ -503,7 +503,7 @@ def fused_scores_record(lib, native, dev, stream, steps: int, replays: int, peak
 
 
 def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, replays: int, peak: float,
-                    name: str = "c5b") -> dict | None:
+                    name: str = "c5b", exchange: str = "push") -> dict | None:
     """The one-long-row configuration at this world size (all ranks take part)."""
     import torch.distributed as dist
 
@@ -518,7 +518,10 @@ def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, rep
     # This rank's bucket group as a dense stripes x cols slab, generated directly in
     # that layout (the values are i.i.d., so the slab of a random row is a random slab).
     slab = make_input(dict(w, n=stripes * (c1 - c0)), 1, 77 + rank, dev).view(stripes, c1 - c0)
-    plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev)
+    exchange = exchange if world > 1 else "none"
+    plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev, exchange=exchange if world > 1 else "all_gather")
+    if exchange == "push":
+        steps += steps & 1        # the two candidate buffer sets alternate: a replayed graph holds an even number of steps
 
     def step(i, _ptr=None):
         plan(slab)
@@ -543,6 +546,7 @@ def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, rep
     used_graph = graph is not None
     del graph                     # a graph that holds a collective must be gone before the process group is torn down
     torch.cuda.synchronize(dev)
+    plan.close()                  # collective: unmaps and frees the buffers shared between the ranks
     t = torch.tensor(ms + phase_ms, device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -556,10 +560,14 @@ def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, rep
     return {"workload": w["text"], "ms_per_step": sp["mean"], "ms_per_step_min": sp["min"],
             "ms_per_step_stderr": sp["stderr"], "rows_s": 1.0 / (sp["mean"] * 1e-3), "scaling": "strong",
             "frac_per_gpu": alg / (sp["mean"] * 1e-3) / 1e9 / peak, "alg_bytes_per_step_per_gpu": alg,
-            "phase_ms": {"stage1": phase_ms[0], "all_gather": phase_ms[1], "select": phase_ms[2],
+            "phase_ms": {"stage1": phase_ms[0], "exchange": phase_ms[1], "select": phase_ms[2],
                          "how": "CUDA events between the phases of plain launches, max over ranks, mean of 3 steps"},
+            "exchange": {"push": "atk_push_blocks: one kernel stores this rank's candidates into every peer's buffer "
+                                 "over NVLink (CUDA IPC mappings), then a one-element NCCL all-reduce orders the streams",
+                         "all_gather": "one NCCL all-gather of the packed candidate blocks, two unpack copies",
+                         "none": "single GPU: no exchange"}[exchange],
             "steps": steps, "replays": replays, "graph": used_graph,
-            "timed_call": "approx_topk.distributed.LongRowTopK step (atk_stage1_slab, NCCL all-gather, atk_select)"}
+            "timed_call": "approx_topk.distributed.LongRowTopK step (atk_stage1_slab, exchange, atk_select)"}
 
 
 def run_ours(args, rank: int, local_rank: int, world: int) -> int:

@@ -300,6 +300,48 @@ int atk_gather_records(const void* src, int64_t rows, int64_t n, int64_t record_
                        int64_t src_row_stride_bytes, const int64_t* idx, int64_t k,
                        int64_t idx_row_stride, void* out, void* stream);
 
+/*
+ * Candidate exchange of the multi-GPU long row over peer memory (no counterpart in
+ * the reference, which is single-GPU).  Copies up to ATK_PUSH_MAX_SEGMENTS blocks
+ * of this GPU's memory to n_dst <= ATK_PUSH_MAX_DST destinations each, with one
+ * kernel that reads every piece once and stores it to every destination.  The
+ * destinations are device pointers valid in this process and may lie in other GPUs'
+ * memory (CUDA IPC mappings with peer access): that is the use, a rank writes its
+ * block of stage-1 candidates into every peer's candidate buffer over NVLink.
+ *
+ *   src[s], bytes[s]    segment s in this GPU's memory (host arrays of n_seg entries)
+ *   dst[s*n_dst + d]    where segment s goes in destination d (host array)
+ *
+ * Pointers and sizes must be multiples of 4 bytes (ATK_ERR_BAD_ARG otherwise);
+ * pieces of 16 bytes are used when everything is a multiple of 16.  Segments of a
+ * destination must not overlap one another or a source.  The call only stores:
+ * the peers learn that the data has arrived by whatever orders their streams
+ * after this kernel (approx_topk.distributed uses a small all-reduce), never by
+ * polling memory.
+ */
+#define ATK_PUSH_MAX_SEGMENTS 4
+#define ATK_PUSH_MAX_DST 16
+int atk_push_blocks(int n_seg, const void* const* src, const size_t* bytes, int n_dst,
+                    void* const* dst, void* stream);
+
+/*
+ * Buffers for atk_push_blocks destinations (CUDA interprocess memory handles).
+ *   atk_peer_alloc  a zero-filled buffer of its own cudaMalloc on the current device,
+ *                   and its 64-byte handle, which the caller sends to the other ranks
+ *                   of the node (one process per GPU, all GPUs visible to every process);
+ *   atk_peer_open   maps the buffer behind a handle received from another rank into the
+ *                   address space of the CURRENT device, i.e. of the GPU whose kernels
+ *                   will store to it, and enables peer access to the owner's GPU;
+ *   atk_peer_close  unmaps it; every rank closes its mappings of a buffer before the
+ *                   owner calls atk_peer_free.
+ * These calls synchronise the device like cudaMalloc / cudaFree do: set-up and tear-down
+ * only, never inside a CUDA-graph capture.
+ */
+int atk_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int atk_peer_open(const void* handle64, void** ptr);
+int atk_peer_close(void* ptr);
+int atk_peer_free(void* ptr);
+
 /* Number of kernel launches issued by this library on the calling thread since
  * the last atk_reset_launch_count(); benchmarks use it to report launches. */
 int64_t atk_launch_count(void);

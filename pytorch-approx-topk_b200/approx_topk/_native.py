@@ -69,6 +69,11 @@ SIGNATURES = {
     "atk_topk_host_scratch_bytes": (_sz, [_int, _i64, _i64, _i64, _int, _i64, _i64]),
     "atk_topk_host": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _int, _i64, _int, _vp, _vp, _vp, _sz, _i64]),
     "atk_gather_records": (_int, [_vp, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
+    "atk_push_blocks": (_int, [_int, _vp, _vp, _int, _vp, _vp]),
+    "atk_peer_alloc": (_int, [_sz, _vp, _vp]),
+    "atk_peer_open": (_int, [_vp, _vp]),
+    "atk_peer_close": (_int, [_vp]),
+    "atk_peer_free": (_int, [_vp]),
     "atk_launch_count": (_i64, []),
     "atk_reset_launch_count": (None, []),
 }

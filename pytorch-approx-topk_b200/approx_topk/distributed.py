@@ -133,6 +133,74 @@ def _native_select(cand_vals: Tensor, cand_idx: Tensor, k: int,
     return vals, idx
 
 
+class _RawCudaBytes:
+    """Lets torch view device memory it did not allocate (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerBuffers:
+    """One buffer of ``nbytes`` bytes per rank of a node, each mapped into every rank.
+
+    ``local`` is this rank's buffer as a ``uint8`` tensor (zero-filled); ``ptrs[r]`` is the
+    address of rank ``r``'s buffer in THIS process, valid in kernels of this rank's GPU
+    (CUDA interprocess handles, opened with this rank's device current; peer access is
+    enabled by the mapping).  The handles travel over the process group.  Set-up and
+    :meth:`close` are collective and synchronise; neither may run inside a graph capture.
+    """
+
+    def __init__(self, nbytes: int, device: torch.device, group: dist.ProcessGroup | None = None):
+        import ctypes
+
+        self.group, self.device, self.nbytes = group, torch.device(device), nbytes
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        lib = _native.lib()
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _native.check(lib.atk_peer_alloc(nbytes, ctypes.byref(own), handle))
+        self._own = own.value
+        self.local = torch.as_tensor(_RawCudaBytes(self._own, nbytes), device=self.device)
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, (self.device.index, bytes(handle.raw)), group=group)
+        self.ptrs: list[int] = []
+        self._opened: list[int] = []
+        with torch.cuda.device(self.device):
+            for r, (peer_device, raw) in enumerate(handles):
+                if r == self.rank:
+                    self.ptrs.append(self._own)
+                    continue
+                if not torch.cuda.can_device_access_peer(self.device.index, peer_device):
+                    raise RuntimeError(f"GPU {self.device.index} has no peer access to GPU {peer_device} (rank {r})")
+                mapped = ctypes.c_void_p()
+                _native.check(lib.atk_peer_open(ctypes.create_string_buffer(raw, 64), ctypes.byref(mapped)))
+                self.ptrs.append(mapped.value)
+                self._opened.append(mapped.value)
+        dist.barrier(group)
+
+    def close(self) -> None:
+        """Collective: every rank unmaps its peers' buffers, then the owners free them."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self._release()
+
+    def _release(self) -> None:
+        lib = _native.lib()
+        with torch.cuda.device(self.device):
+            for ptr in self._opened:
+                lib.atk_peer_close(ptr)
+            self._opened = []
+            if dist.is_initialized():
+                try:
+                    dist.barrier(self.group)          # no owner frees while a peer still maps its buffer
+                except Exception:                     # the group is already gone: nothing left to order
+                    pass
+            lib.atk_peer_free(self._own)
+        self._own, self.local = None, None
+
+
 class LongRowTopK:
     """The long-row operator with every buffer allocated once.
 
@@ -144,10 +212,27 @@ class LongRowTopK:
 
     ``events``, when given to a step, receives one recorded CUDA event after each
     phase (stage 1, exchange, select) for a per-phase breakdown.
+
+    ``exchange`` picks how the candidates travel:
+
+    * ``"all_gather"`` (default): one NCCL all-gather of the packed blocks into every
+      rank's own memory, then two copies that unpack them.
+    * ``"push"`` (ranks of one node with peer access): every rank maps the candidate
+      buffers of all ranks once (:class:`PeerBuffers`), stage 1 writes this rank's
+      block into its own buffer, ONE kernel (``atk_push_blocks``) stores the block into
+      every peer's buffer over NVLink, and a one-element all-reduce orders the ranks'
+      streams before the select reads.  Nothing is unpacked and no rank loads from a
+      peer.  The buffers exist twice and steps alternate between them, so a rank that
+      runs ahead never writes into a buffer a peer is still selecting from; for the same
+      reason a CUDA graph that is replayed must hold an EVEN number of steps.  Call
+      :meth:`close` (collective) when done, before the process group is destroyed.
     """
 
     def __init__(self, stripes: int, k: int, j: int, k_mult: int, dtype: torch.dtype,
-                 device: torch.device, group: dist.ProcessGroup | None = None):
+                 device: torch.device, group: dist.ProcessGroup | None = None,
+                 exchange: str = "all_gather"):
+        if exchange not in ("all_gather", "push"):
+            raise ValueError(f"exchange must be 'all_gather' or 'push', was {exchange!r}")
         if k_mult < 1:
             raise ValueError(f"k_mult must be >=1, was {k_mult}")
         self.k, self.j, self.k_mult = k, j, k_mult
@@ -168,8 +253,12 @@ class LongRowTopK:
         code = _native.dtype_code(dtype)
         dev = self.device
         esize = torch.empty(0, dtype=dtype).element_size()
+        self.exchange = exchange if self.world > 1 else "none"
+        self._step = 0
         with torch.cuda.device(dev):
-            if self.world > 1:
+            if self.exchange == "push":
+                self._init_push(block, esize)
+            elif self.world > 1:
                 # One exchange instead of two: a rank's positions and values travel in one
                 # packed block [block x int64 | block x dtype, padded to 16 bytes]; stage 1
                 # writes straight into views of it, and the gathered blocks are unpacked into
@@ -197,6 +286,55 @@ class LongRowTopK:
                 self.select_ws = None
                 self.values, self.indices = self.cand_vals[:k], self.cand_idx[:k]
 
+    def _init_push(self, block: int, esize: int) -> None:
+        """Two sets of dense candidate arrays in one shared buffer, the peers' mappings of
+        theirs, and the argument arrays of the push for either set."""
+        import ctypes
+
+        dev, world, rank = self.device, self.world, self.rank
+        idx_bytes = (block * world * 8 + 255) // 256 * 256
+        val_bytes = (block * world * esize + 255) // 256 * 256
+        set_bytes = idx_bytes + val_bytes
+        self._shared = PeerBuffers(2 * set_bytes, dev, self.group)
+        self._recv = self._shared.local
+        self._flag = torch.zeros(1, device=dev, dtype=torch.float32)
+        self._sets = []
+        mine = self.cols * self.j                                  # real candidates of this rank
+        for s in range(2):
+            base = s * set_bytes
+            cand_idx = self._recv[base:base + block * world * 8].view(torch.int64)
+            cand_vals = self._recv[base + idx_bytes:base + idx_bytes + block * world * esize].view(self.dtype)
+            local_idx = cand_idx[rank * block:rank * block + mine]
+            local_vals = cand_vals[rank * block:rank * block + mine]
+            others = [r for r in range(world) if r != rank]
+            src = (ctypes.c_void_p * 2)(local_idx.data_ptr(), local_vals.data_ptr())
+            nbytes = (ctypes.c_size_t * 2)(mine * 8, mine * esize)
+            dst = (ctypes.c_void_p * (2 * len(others)))()
+            for d, r in enumerate(others):
+                peer = self._shared.ptrs[r] + base
+                dst[d] = peer + rank * block * 8
+                dst[len(others) + d] = peer + idx_bytes + rank * block * esize
+            self._sets.append({"cand_idx": cand_idx, "cand_vals": cand_vals, "local_idx": local_idx,
+                               "local_vals": local_vals, "push": (src, nbytes, len(others), dst)})
+        self._use_set(0)
+
+    def _use_set(self, s: int) -> None:
+        cur = self._sets[s]
+        self.cand_idx, self.cand_vals = cur["cand_idx"], cur["cand_vals"]
+        self.local_idx, self.local_vals = cur["local_idx"], cur["local_vals"]
+        self._push_args = cur["push"]
+
+    def close(self) -> None:
+        """Collective tear-down of the buffers shared with the peers (``"push"`` only)."""
+        shared = getattr(self, "_shared", None)
+        if shared is not None:
+            self._sets, self._recv, self.cand_idx, self.cand_vals = [], None, None, None
+            self.local_idx, self.local_vals = None, None
+            if self.k0 <= self.k:                 # the results were views of the shared buffer
+                self.values, self.indices = None, None
+            shared.close()
+            self._shared = None
+
     def __call__(self, slab: Tensor, events: list | None = None) -> tuple[Tensor, Tensor]:
         if slab.ndim != 2 or tuple(slab.shape) != (self.stripes, self.cols) or slab.dtype != self.dtype:
             raise ValueError(f"slab must be {self.stripes} x {self.cols} of {self.dtype}, got "
@@ -208,12 +346,22 @@ class LongRowTopK:
                 ev.record(torch.cuda.current_stream(self.device))
                 events.append(ev)
 
+        if self.exchange == "push":
+            self._use_set(self._step & 1)
+            self._step += 1
         if self.cols:
             _native_stage1_slab(slab, self.total_buckets, self.start, self.j,
                                 out=(self.local_vals[:self.cols * self.j], self.local_idx[:self.cols * self.j]),
                                 workspace=self.stage1_ws)
         mark()
-        if self.world > 1:
+        if self.exchange == "push":
+            src, nbytes, n_dst, dst = self._push_args
+            with torch.cuda.device(self.device):
+                _native.check(_native.lib().atk_push_blocks(2, src, nbytes, n_dst, dst,
+                                                            _native.current_stream_ptr(self.device)))
+            # orders the streams: when it ends here, every rank's push kernel has ended
+            dist.all_reduce(self._flag, group=self.group)
+        elif self.world > 1:
             # rank g's block is slots [g*block, (g+1)*block); real columns fill the
             # gathered buffer from the front, so its first k0 slots are the candidates
             dist.all_gather_into_tensor(self._packed_all, self._packed_local, group=self.group)
@@ -226,6 +374,8 @@ class LongRowTopK:
         if self.k0 > self.k:
             _native_select(self.cand_vals[:self.k0], self.cand_idx[:self.k0], self.k,
                            out=(self.values, self.indices), workspace=self.select_ws)
+        elif self.exchange == "push":             # nothing to select: the candidates of this step's set
+            self.values, self.indices = self.cand_vals[:self.k], self.cand_idx[:self.k]
         mark()
         return self.values, self.indices
 

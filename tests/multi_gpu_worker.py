@@ -1,9 +1,9 @@
 """Worker of tests/test_multi_gpu.py: one rank per GPU under torchrun (NCCL).
 
-Checks on real GPUs that (1) the bucket-group sharding of one long row with the
-all-gather of candidates gives bit-identical results to the single-GPU
-operator on the same row, on every rank, and (2) row sharding reproduces the
-unsharded result row for row.
+Checks on real GPUs that (1) the bucket-group sharding of one long row with either
+exchange of the candidates (NCCL all-gather; stores into the peers' buffers over
+NVLink) gives bit-identical results to the single-GPU operator on the same row, on
+every rank, and (2) row sharding reproduces the unsharded result row for row.
 """
 
 import os
@@ -20,6 +20,11 @@ import torch.distributed as dist
 
 import approx_topk
 from approx_topk import distributed as atd
+
+
+def trace(*what):
+    if os.environ.get("ATK_WORKER_TRACE"):
+        print(f"[rank {os.environ.get('RANK')}]", *what, file=sys.stderr, flush=True)
 
 
 def canonical(v, i):
@@ -40,7 +45,9 @@ def main() -> int:
             row = torch.randn(n, device=dev, generator=g).to(dtype)
             b = k * k_mult // j
             slab = atd.slab_of_row(row, b, rank, world)
+            trace("long row", dtype, n, k, j, k_mult)
             v, i = atd.topk_long_row(slab, k, j, k_mult)
+            trace("single-GPU operator")
             ev, ei = approx_topk.topk(row.view(1, -1), k, -1, j=j, k_mult=k_mult)
             (v, i), (ev, ei) = canonical(v, i), canonical(ev.view(-1), ei.view(-1))
             assert torch.equal(i, ei), f"rank {rank}: indices differ ({dtype}, n={n})"
@@ -59,23 +66,35 @@ def main() -> int:
             ev, ei = canonical(ev.view(-1), ei.view(-1))
             v, i = canonical(*atd.topk_long_row(slab, k, j, k_mult))
             assert torch.equal(i, ei) and torch.equal(v, ev), f"rank {rank}: padded groups differ ({dtype}, b={b})"
-            plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev)
-            for _ in range(2):
-                v, i = canonical(*plan(slab))
-                assert torch.equal(i, ei) and torch.equal(v, ev), f"rank {rank}: plan differs ({dtype}, b={b})"
-            torch.cuda.synchronize(dev)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                plan(slab)
-            plan.values.zero_()
-            for _ in range(2):
-                graph.replay()
-            torch.cuda.synchronize(dev)
-            v, i = canonical(plan.values.clone(), plan.indices.clone())
-            assert torch.equal(i, ei) and torch.equal(v, ev), f"rank {rank}: graph replay differs ({dtype}, b={b})"
-            # a graph that holds a collective must be gone before the process group is torn down
-            del graph
-            torch.cuda.synchronize(dev)
+            # both exchanges: the NCCL all-gather, and the push over peer memory (two buffer
+            # sets that alternate: a replayed graph holds an even number of steps)
+            for exchange, graph_steps in (("all_gather", 1), ("push", 2)):
+                trace("plan", exchange, dtype, stripes, k, j, k_mult)
+                plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev, exchange=exchange)
+                for _ in range(3):
+                    v, i = canonical(*plan(slab))
+                    assert torch.equal(i, ei) and torch.equal(v, ev), \
+                        f"rank {rank}: plan differs ({exchange}, {dtype}, b={b})"
+                torch.cuda.synchronize(dev)
+                dist.barrier()
+                trace("graph", exchange)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    for _ in range(graph_steps):
+                        plan(slab)
+                plan.values.zero_()
+                for _ in range(3):
+                    graph.replay()
+                torch.cuda.synchronize(dev)
+                v, i = canonical(plan.values.clone(), plan.indices.clone())
+                assert torch.equal(i, ei) and torch.equal(v, ev), \
+                    f"rank {rank}: graph replay differs ({exchange}, {dtype}, b={b})"
+                # a graph that holds a collective must be gone before the process group is torn down
+                del graph
+                torch.cuda.synchronize(dev)
+                plan.close()
+                dist.barrier()
+                del plan
         # rows: each rank computes its span; together they equal the full batch
         g = torch.Generator(device=dev).manual_seed(99)
         x = torch.randn(37, 1 << 14, device=dev, generator=g)
