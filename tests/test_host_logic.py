@@ -273,3 +273,33 @@ def test_bench_host_samples_follow_the_workloads_distribution():
     w = bench.WORKLOADS["c5b"]
     n = 1 << 26
     assert w["n"] // n == 64 and max(w["k"] // 64, w["j"]) * w["k_mult"] // w["j"] * (w["n"] // (w["k"] * w["k_mult"] // w["j"])) == n
+
+
+def test_push_exchange_argument_checks_need_no_gpu():
+    """atk_push_blocks validates counts, null pointers and alignment before it touches CUDA;
+    LongRowTopK rejects an unknown exchange before it touches the process group."""
+    import ctypes
+
+    from approx_topk import _native
+    from approx_topk.distributed import LongRowTopK
+
+    lib = _native.lib()
+    src = (ctypes.c_void_p * 1)(256)
+    nbytes = (ctypes.c_size_t * 1)(64)
+    dst = (ctypes.c_void_p * 1)(512)
+    assert lib.atk_push_blocks(0, src, nbytes, 1, dst, None) == _native.ATK_OK            # nothing to do
+    assert lib.atk_push_blocks(1, src, nbytes, 0, dst, None) == _native.ATK_OK
+    assert lib.atk_push_blocks(5, src, nbytes, 1, dst, None) == _native.ATK_ERR_BAD_ARG   # too many segments
+    assert lib.atk_push_blocks(1, src, nbytes, 17, dst, None) == _native.ATK_ERR_BAD_ARG  # too many destinations
+    assert lib.atk_push_blocks(1, None, nbytes, 1, dst, None) == _native.ATK_ERR_BAD_ARG
+    odd = (ctypes.c_size_t * 1)(6)
+    assert lib.atk_push_blocks(1, src, odd, 1, dst, None) == _native.ATK_ERR_BAD_ARG      # not a multiple of 4 bytes
+    unaligned = (ctypes.c_void_p * 1)(514)
+    assert lib.atk_push_blocks(1, src, nbytes, 1, unaligned, None) == _native.ATK_ERR_BAD_ARG
+    null_dst = (ctypes.c_void_p * 1)(None)
+    assert lib.atk_push_blocks(1, src, nbytes, 1, null_dst, None) == _native.ATK_ERR_BAD_ARG
+    assert lib.atk_peer_alloc(0, None, None) == _native.ATK_ERR_BAD_ARG
+    assert lib.atk_peer_open(None, None) == _native.ATK_ERR_BAD_ARG
+    assert lib.atk_peer_close(None) == _native.ATK_OK and lib.atk_peer_free(None) == _native.ATK_OK
+    with pytest.raises(ValueError, match="exchange"):
+        LongRowTopK(16, 8, 1, 1, torch.float32, torch.device("cpu"), exchange="carrier pigeon")
