@@ -16,8 +16,10 @@ the algorithm:
   NVLink reassembles that buffer on every rank, and the exact select over it
   gives the same answer as one GPU would (:func:`topk_long_row`).
 
-The candidates land in each GPU's own memory before the select reads them; no
-kernel touches a peer's memory.
+The candidates land in each GPU's own memory before the select reads them, either
+by the collective or, with ``exchange="push"`` (:class:`LongRowTopK`), by one kernel
+per rank that stores the rank's block into the peers' buffers over NVLink; no kernel
+loads from a peer's memory and none waits for another GPU.
 """
 
 from __future__ import annotations
