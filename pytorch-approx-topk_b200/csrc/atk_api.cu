@@ -19,7 +19,8 @@ int stage1_formatted(const void* x, int dtype, int64_t rows, int64_t n, int64_t 
 
 // Lazily cached SM count per device.  Together with the per-device address cache and
 // the built-in scratch array of atk_select_static (atk_select.cu) and the two cached
-// pipeline streams per device of atk_topk_host this is all the global state the library has.
+// pipeline streams per device of atk_topk_host this is all the global state the library has
+// (besides the ATK_* environment switches, each read once).
 int sm_count_of_current_device() {
   static std::atomic<int> cache[64];
   int dev = 0;
