@@ -948,6 +948,222 @@ select_write_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
                                                orow.at(n_gt + eq_base), threadIdx.x, kLargeThreads, false);
 }
 
+// ---- the whole multi-block select in one launch -----------------------------------
+// For problems that fit the GPU at once (one long row, a few long rows): every block
+// keeps the keys of its CPB chunks in registers through all the digit passes and the
+// write, so the candidates are read once instead of once per pass, and the launches of
+// the passes (each bound by launch and synchronisation latency at this size) become
+// barriers between the blocks of a row.  The kernel is launched cooperatively: the
+// launch fails unless every block is resident at once, so the barriers cannot wait for
+// a block that has not started.  A barrier is a counter that is zero on entry and
+// used once (the `tickets` words of the row); its wait is bounded all the same, and
+// gives up with the row's `gave_up` flag set (never seen; the output is invalid then).
+constexpr int kCoopMaxPolls = 1 << 22;
+
+__device__ __forceinline__ void row_barrier(uint32_t* counter, uint32_t expected, uint32_t* gave_up) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();                       // this block's histogram / count updates are visible before its arrival
+    atomicAdd(counter, 1u);
+    int polls = 0;
+    while (*reinterpret_cast<volatile uint32_t*>(counter) < expected) {
+      if (++polls > kCoopMaxPolls) {
+        *gave_up = 1u;
+        break;
+      }
+      __nanosleep(32);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+template <typename T, int ITEMS, int CPB>
+__global__ void __launch_bounds__(kLargeThreads, 4)   // four resident blocks per SM: one row of 2^21 fits with CPB = 2
+select_coop_kernel(const typename ElemTraits<T>::Bits* __restrict__ cand_vals,
+                   const long long* __restrict__ cand_idx, long long k0, long long cand_row_stride, long long k,
+                   RowState<typename KeyOf<T>::Key>* __restrict__ state, uint32_t* __restrict__ hist,
+                   uint32_t* __restrict__ tickets, unsigned long long* __restrict__ status /* [rows][chunks] */,
+                   int chunks, void* __restrict__ out_vals, void* __restrict__ out_idx, long long out_row_stride,
+                   int out_fmt, int vec) {
+  using K = KeyOf<T>;
+  using Key = typename K::Key;
+  using Bits = typename ElemTraits<T>::Bits;
+  using D = LargeDigits<T>;
+  constexpr int NB = D::kBins;
+  constexpr int kWarps = kLargeThreads / 32;
+  __shared__ uint32_t sh[NB];
+  __shared__ uint32_t res[2];
+  __shared__ uint32_t wsum[32];
+  __shared__ uint32_t block_total;
+  __shared__ unsigned long long red[2 * kWarps];
+  __shared__ __align__(16) long long sidx[kLargeThreads * ITEMS];
+  __shared__ __align__(16) Bits sval[kLargeThreads * ITEMS];
+  grid_dependency_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const long long row = blockIdx.y;
+  uint32_t* gave_up = &state[row].gave_up;
+  if (blockIdx.x == 0 && tid == 0) *gave_up = 0u;      // a barrier could set it a quarter of a second from now at the earliest
+  const Bits* vrow = cand_vals + row * cand_row_stride;
+  const long long* irow = cand_idx + row * cand_row_stride;
+  uint32_t* row_tickets = tickets + row * (D::kPasses + 1);
+
+  // the block's chunks, thread t owning ITEMS consecutive slots of each
+  Bits raws[CPB][ITEMS];
+  int valid[CPB];
+  long long slot0[CPB], end[CPB];
+#pragma unroll
+  for (int c = 0; c < CPB; ++c) {
+    const long long chunk = static_cast<long long>(blockIdx.x) * CPB + c;
+    const long long begin = chunk * (kLargeThreads * ITEMS);
+    end[c] = begin + kLargeThreads * ITEMS < k0 ? begin + kLargeThreads * ITEMS : k0;
+    slot0[c] = begin + static_cast<long long>(tid) * ITEMS;
+    const long long v = end[c] - slot0[c];
+    valid[c] = v >= ITEMS ? ITEMS : (v > 0 ? static_cast<int>(v) : 0);
+    if (valid[c] > 0) load_items<Bits, ITEMS>(vrow, slot0[c], end[c], vec, raws[c]);
+  }
+
+  // digit passes
+  Key prefix = 0, mask = 0;
+  uint32_t need = static_cast<uint32_t>(k);
+  for (int pass = 0; pass < D::kPasses; ++pass) {
+    const int shift = D::shift(pass);
+    const uint32_t digit_mask = (1u << D::width(pass)) - 1u;
+    for (int i = tid; i < NB; i += kLargeThreads) sh[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < CPB; ++c) {
+#pragma unroll
+      for (int u = 0; u < ITEMS; ++u) {
+        const Key key = K::key(raws[c][u]);
+        if (u < valid[c] && (key & mask) == prefix) atomicAdd(&sh[static_cast<uint32_t>(key >> shift) & digit_mask], 1u);
+      }
+    }
+    __syncthreads();
+    uint32_t* gh = hist + (row * D::kPasses + pass) * NB;
+    for (int i = tid; i < NB; i += kLargeThreads)
+      if (sh[i]) atomicAdd(&gh[i], sh[i]);
+    row_barrier(&row_tickets[pass], gridDim.x, gave_up);
+    // every block of the row picks the digit for itself from the complete histogram
+    for (int i = tid; i < NB; i += kLargeThreads) sh[i] = __ldcg(&gh[i]);
+    __syncthreads();
+    pick_digit_block<NB>(sh, need, res, wsum);
+    prefix |= static_cast<Key>(res[0]) << shift;
+    mask |= static_cast<Key>(digit_mask) << shift;
+    need = res[1];
+    __syncthreads();                       // res has been read before the next pass can write it
+  }
+  const Key thr = prefix;
+  const long long n_gt = k - need;
+
+  // counts of every chunk above / on the threshold, published for the blocks after it
+  uint32_t excl[CPB], tot_gt[CPB], tot_eq[CPB];
+#pragma unroll
+  for (int c = 0; c < CPB; ++c) {
+    uint32_t mine = 0;
+#pragma unroll
+    for (int u = 0; u < ITEMS; ++u) {
+      const Key key = K::key(raws[c][u]);
+      mine += (u < valid[c] && key > thr) ? 1u : 0u;
+      mine += (u < valid[c] && key == thr) ? 0x10000u : 0u;
+    }
+    uint32_t incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t nb = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += nb;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t w = lane < kWarps ? wsum[lane] : 0u;
+      uint32_t wi = w;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t nb = __shfl_up_sync(0xffffffffu, wi, off);
+        if (lane >= off) wi += nb;
+      }
+      wsum[lane] = wi - w;
+      if (lane == 31) block_total = wi;
+    }
+    __syncthreads();
+    excl[c] = wsum[warp] + incl - mine;
+    tot_gt[c] = block_total & 0xffffu;
+    tot_eq[c] = block_total >> 16;
+    const long long chunk = static_cast<long long>(blockIdx.x) * CPB + c;
+    if (tid == 0 && chunk < chunks)
+      status[row * chunks + chunk] = (static_cast<unsigned long long>(tot_gt[c]) << 32) | tot_eq[c];
+    __syncthreads();                       // wsum and block_total are free for the next chunk
+  }
+  row_barrier(&row_tickets[D::kPasses], gridDim.x, gave_up);
+
+  // how many candidates above / on the threshold precede this block in the row
+  unsigned long long before_gt = 0, before_eq = 0;
+  {
+    const long long first = static_cast<long long>(blockIdx.x) * CPB;
+    for (long long i = tid; i < first; i += kLargeThreads) {
+      const unsigned long long w = __ldcg(&status[row * chunks + i]);
+      before_gt += w >> 32;
+      before_eq += w & 0xffffffffull;
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      before_gt += __shfl_xor_sync(0xffffffffu, before_gt, off);
+      before_eq += __shfl_xor_sync(0xffffffffu, before_eq, off);
+    }
+    if (lane == 0) {
+      red[warp] = before_gt;
+      red[kWarps + warp] = before_eq;
+    }
+    __syncthreads();
+    before_gt = 0;
+    before_eq = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      before_gt += red[w];
+      before_eq += red[kWarps + w];
+    }
+  }
+
+  // the winners of every chunk: collected in shared memory in output order, copied out coalesced
+  const OutRow<Bits> orow(out_vals, out_idx, row, out_row_stride, out_fmt);
+  uint32_t gt_base = static_cast<uint32_t>(before_gt), eq_base = static_cast<uint32_t>(before_eq);
+#pragma unroll
+  for (int c = 0; c < CPB; ++c) {
+    if (c > 0) __syncthreads();            // the staging arrays have been copied out
+    long long idxs[ITEMS];
+    if (valid[c] > 0) load_items<long long, ITEMS>(irow, slot0[c], end[c], vec, idxs);
+    uint32_t sel_eq = need > eq_base ? need - eq_base : 0u;   // equal candidates this chunk may still take
+    if (sel_eq > tot_eq[c]) sel_eq = tot_eq[c];
+    uint32_t lgt = excl[c] & 0xffffu;
+    uint32_t leq = excl[c] >> 16;
+#pragma unroll
+    for (int u = 0; u < ITEMS; ++u) {
+      if (u < valid[c]) {
+        const Key key = K::key(raws[c][u]);
+        int at = -1;
+        if (key > thr) {
+          at = static_cast<int>(lgt++);
+        } else if (key == thr) {
+          if (leq < sel_eq) at = static_cast<int>(tot_gt[c] + leq);
+          ++leq;
+        }
+        if (at >= 0) {
+          sval[at] = raws[c][u];
+          sidx[at] = idxs[u];
+        }
+      }
+    }
+    __syncthreads();
+    const auto gt_row = orow.at(gt_base);
+    stage_copy_out<Bits>(sidx, sval, static_cast<int>(tot_gt[c]), gt_row, tid, kLargeThreads, gt_row.aligned16());
+    stage_copy_out<Bits>(sidx + tot_gt[c], sval + tot_gt[c], static_cast<int>(sel_eq), orow.at(n_gt + eq_base), tid,
+                         kLargeThreads, false);
+    gt_base += tot_gt[c];
+    eq_base += tot_eq[c];
+  }
+}
+
 inline long long chunks_of(long long k0) { return (k0 + kChunk - 1) / kChunk; }
 inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
@@ -975,6 +1191,68 @@ template <typename T>
 size_t workspace_typed(long long rows, long long k0) {
   if (k0 <= small_max_k0<T>()) return 0;
   return LargeLayout<T>(rows, k0).total;
+}
+
+// Resident blocks of the cooperative select on the current device (0: no cooperative
+// launches there), queried once per device and instantiation.
+template <typename T, int ITEMS, int CPB>
+long long coop_capacity() {
+  static std::atomic<long long> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  long long c = cache[dev].load(std::memory_order_relaxed);
+  if (c != 0) return c > 0 ? c : 0;
+  int coop = 0, per_sm = 0;
+  if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess) coop = 0;
+  if (coop && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, select_coop_kernel<T, ITEMS, CPB>, kLargeThreads,
+                                                            0) != cudaSuccess)
+    per_sm = 0;
+  cudaGetLastError();
+  c = coop ? static_cast<long long>(per_sm) * sm_count_of_current_device() : 0;
+  cache[dev].store(c > 0 ? c : -1, std::memory_order_relaxed);
+  return c;
+}
+
+constexpr int kCoopDeclined = 1;   // nothing launched: the problem does not fit the GPU at once
+
+template <typename T, int ITEMS, int CPB>
+int launch_select_coop_cpb(const SelectLaunch& a, const typename ElemTraits<T>::Bits* cv, void* ov,
+                           RowState<typename KeyOf<T>::Key>* state, uint32_t* hist, uint32_t* tickets,
+                           unsigned long long* status, long long chunks, int vec) {
+  const long long per_row = (chunks + CPB - 1) / CPB;
+  if (a.rows * per_row > coop_capacity<T, ITEMS, CPB>() || a.rows > 65535) return kCoopDeclined;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(per_row), static_cast<unsigned>(a.rows));
+  cfg.blockDim = dim3(kLargeThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t rc = cudaLaunchKernelEx(&cfg, select_coop_kernel<T, ITEMS, CPB>, cv,
+                                            static_cast<const long long*>(a.cand_idx), static_cast<long long>(a.k0),
+                                            static_cast<long long>(a.cand_row_stride), static_cast<long long>(a.k),
+                                            state, hist, tickets, status, static_cast<int>(chunks), ov,
+                                            static_cast<void*>(a.out_idx), static_cast<long long>(a.out_row_stride),
+                                            a.out_format, vec);
+  if (rc != cudaSuccess) {
+    cudaGetLastError();                   // e.g. the GPU is shared and fewer blocks fit than the occupancy query said
+    return kCoopDeclined;
+  }
+  note_launch();
+  return ATK_OK;
+}
+
+template <typename T, int ITEMS>
+int launch_select_coop(const SelectLaunch& a, const typename ElemTraits<T>::Bits* cv, void* ov,
+                       RowState<typename KeyOf<T>::Key>* state, uint32_t* hist, uint32_t* tickets,
+                       unsigned long long* status, long long chunks, int vec) {
+  if (chunks >= (1ll << 30)) return kCoopDeclined;
+  int rc = launch_select_coop_cpb<T, ITEMS, 1>(a, cv, ov, state, hist, tickets, status, chunks, vec);
+  if (rc == kCoopDeclined) rc = launch_select_coop_cpb<T, ITEMS, 2>(a, cv, ov, state, hist, tickets, status, chunks, vec);
+  return rc;
 }
 
 template <typename T>
@@ -1049,6 +1327,16 @@ int select_typed(const SelectLaunch& a) {
   // vector loads need 16-byte aligned rows of values and of positions
   const int vec = (reinterpret_cast<uintptr_t>(cv) % 16 == 0) && ((a.cand_row_stride * sizeof(Bits)) % 16 == 0) &&
                   (reinterpret_cast<uintptr_t>(a.cand_idx) % 16 == 0) && ((a.cand_row_stride * 8) % 16 == 0);
+  // Problems that fit the GPU at once (up to two chunks per resident block): the whole
+  // select in ONE cooperative launch, keys in registers from the first pass to the write
+  // (select_coop_kernel).  ATK_NO_COOP_SELECT=1 keeps the launch per pass.
+  {
+    static const bool coop_off = std::getenv("ATK_NO_COOP_SELECT") != nullptr;
+    if (!coop_off) {
+      const int rc = launch_select_coop<T, kItems>(a, cv, ov, state, hist, tickets, status, chunks, vec);
+      if (rc != kCoopDeclined) return rc;
+    }
+  }
   // Few chunks in all (a long row or two): every launch overlaps the end of the one before
   // it (one row of 2^21: 46.3 -> 45.0 us).  With many blocks per launch the early blocks
   // crowd the SMs that finish first (256 rows x 131072: 259.7 -> 264.4 us): plain launches.
