@@ -3,7 +3,7 @@
 // peer (device pointers into the peers' memory, mapped into this process by CUDA IPC)
 // with plain stores over NVLink.  One kernel reads every 16-byte piece of the block
 // once from this GPU's memory and stores it to all destinations, so all links are
-// busy at once.  No loads from peer memory, no multicast, no waiting on peers: the
+// busy at once.  No loads from peer memory, no switch-side replication, no waiting on peers: the
 // ranks synchronise afterwards on the host side of the exchange (a barrier in
 // stream order), and only then read what they received.
 #include <cstring>
