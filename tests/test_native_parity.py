@@ -259,6 +259,22 @@ def test_select_matches_oracle(dtype, rows, k0, k):
         assert torch.equal(v, v2) and torch.equal(i, i2)         # deterministic, order included
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64])
+@pytest.mark.parametrize("rows,k0,k", [(80, 32768, 9000),       # 1280 chunks: more than one cooperative launch holds
+                                       (160, 65536, 30000)])    # 5120 chunks: the count pass instead of the chained scan
+def test_select_with_a_launch_per_pass_matches_oracle(dtype, rows, k0, k):
+    """Problems too large for the one-launch select take the digit passes as separate
+    launches (chained write pass for few chunks, a count pass for many)."""
+    for dist in ("randn", "ties"):
+        cv = make(rows, k0, dtype, 900 + k, dist)
+        cv = torch.where(cv == 0, torch.zeros_like(cv), cv)
+        ci = torch.randperm(rows * k0, device="cuda", generator=torch.Generator(device="cuda").manual_seed(k)
+                            ).reshape(rows, k0)
+        v, i = api.select(cv, ci, k)
+        ov, oi = oracle.select(cv.cpu(), ci.cpu(), k)
+        assert_pairs_identical(v, i, ov, oi)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.int16, torch.int8, torch.float32])
 def test_two_stage_odd_candidate_counts_and_views(dtype):
     # Candidate counts that are not multiples of the vector width, j = 3, a
