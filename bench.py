@@ -446,6 +446,43 @@ def extra_record(name: str, lib, native, dev, stream, steps: int, replays: int, 
     return rec
 
 
+def narrow_outputs_record(wl: "RowsWorkload", lib, native, dev, stream, steps: int, replays: int, peak: float) -> dict:
+    """The headline workload through atk_topk_ex with the narrow output formats: int32
+    positions, and 8-byte {value bits, int32 position} records (same selection, fewer
+    bytes written; the reference fixes int64 positions)."""
+    w = wl.w
+    s = torch.empty(0, dtype=wl.dtype).element_size()
+    out: dict = {}
+    for name, fmt, per_entry in (("int32_positions", native.ATK_OUT_I32, s + 4), ("records", native.ATK_OUT_REC32, 8)):
+        bufs = []
+        for _ in range(2):
+            if fmt == native.ATK_OUT_REC32:
+                bufs.append((torch.empty(wl.rows, wl.k, 2, device=dev, dtype=torch.int32), None))
+            else:
+                bufs.append((torch.empty(wl.rows, wl.k, device=dev, dtype=wl.dtype),
+                             torch.empty(wl.rows, wl.k, device=dev, dtype=torch.int32)))
+
+        def step(i, on_stream=None, fmt=fmt, bufs=bufs):
+            x, (v, ix), ws = wl.xs[i % 2], bufs[i % 2], wl.wss[i % 2]
+            rc = lib.atk_topk_ex(x.data_ptr(), wl.code, wl.rows, wl.n, wl.n, wl.k, wl.j, wl.k_mult, 1, -1, fmt,
+                                 v.data_ptr(), ix.data_ptr() if ix is not None else None, wl.k,
+                                 ws.data_ptr() if wl.ws_bytes else None, wl.ws_bytes,
+                                 wl.stream_ptr if on_stream is None else on_stream)
+            if rc != 0:
+                raise RuntimeError(native.strerror(rc))
+
+        for i in range(3):
+            step(i)
+        graph = capture_steps(step, steps, dev)
+        ms = timed_replays(graph, step, steps, replays, dev, stream, lambda: torch.cuda.synchronize(dev))
+        sp = spread([m / steps for m in ms])
+        alg = wl.rows * (wl.n * s + wl.k * per_entry)
+        out[name] = {"ms_per_step": sp["mean"], "ms_per_step_min": sp["min"], "rows_s": wl.rows / (sp["mean"] * 1e-3),
+                     "alg_bytes_per_step": alg, "frac": alg / (sp["mean"] * 1e-3) / 1e9 / peak}
+    out["workload"] = w["text"] + "; atk_topk_ex output formats"
+    return out
+
+
 def fused_scores_record(lib, native, dev, stream, steps: int, replays: int, peak: float, rows: int = 0,
                         unfused: bool = True) -> dict:
     """The attention-score configuration with the scores produced inside the kernel
@@ -738,6 +775,14 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> int:
             except Exception as exc:
                 extra[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
             torch.cuda.empty_cache()
+        try:
+            wl2 = RowsWorkload(WORKLOADS["c2"], lib, _native, dev, 7000, stream.cuda_stream)
+            extra["c2_narrow_outputs"] = narrow_outputs_record(wl2, lib, _native, dev, stream, max(2, args.steps // 2),
+                                                               max(3, replays // 2), peak)
+            del wl2
+        except Exception as exc:
+            extra["c2_narrow_outputs"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        torch.cuda.empty_cache()
         try:
             extra["c3_fused_scores"] = fused_scores_record(lib, _native, dev, stream, 3, 3, peak)
         except Exception as exc:
