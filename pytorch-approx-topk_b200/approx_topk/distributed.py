@@ -226,7 +226,9 @@ class LongRowTopK:
       streams before the select reads.  Nothing is unpacked and no rank loads from a
       peer.  The buffers exist twice and steps alternate between them, so a rank that
       runs ahead never writes into a buffer a peer is still selecting from; for the same
-      reason a CUDA graph that is replayed must hold an EVEN number of steps.  Call
+      reason a CUDA graph that is replayed must hold an EVEN number of steps, and eager
+      steps must not be mixed in between replays of such a graph (two consecutive steps
+      would then use the same buffers).  Call
       :meth:`close` (collective) when done, before the process group is destroyed.
     """
 
