@@ -192,10 +192,10 @@ score_tile_kernel(const ScoreParams sp) {
   if (!second) {
     // the column that does not exist held only -inf scores: nothing of it is written
     Q one[1] = {q[0]};
-    sweep_write_out<T, Q, J, 1, false>(p, one, static_cast<const T*>(nullptr), row, c0, 0);
+    sweep_write_out<T, Q, J, 1, false>(p, one, static_cast<const T*>(nullptr), row, c0, 0, 1);
     return;
   }
-  sweep_write_out<T, Q, J, 2, false>(p, q, static_cast<const T*>(nullptr), row, c0, 0);
+  sweep_write_out<T, Q, J, 2, false>(p, q, static_cast<const T*>(nullptr), row, c0, 0, 1);
 }
 
 // The scores alone, written to memory (the unfused form of the same arithmetic):
@@ -368,6 +368,9 @@ int atk_score_topk(const void* q, const void* keys, int dtype, int64_t rows, int
   p.vec_keys = 0;
   p.z = 1;
   p.z_chunk = p.l_full;
+  p.main_units = 0;
+  p.z_main = 1;
+  p.z_chunk_main = p.l_full;
   p.part_vals = nullptr;
   p.part_idx = nullptr;
   const cudaStream_t st = static_cast<cudaStream_t>(stream);

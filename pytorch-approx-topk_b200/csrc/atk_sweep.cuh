@@ -52,6 +52,13 @@ struct SweepParams {
   long long z_chunk;
   void* part_vals;
   long long* part_idx;
+  // Tile kernel, one row: the first main_units (row, tile) units are split z_main ways
+  // (1: scanned whole by one block each and written directly), the units after them z
+  // ways; their blocks come last in the grid and fill the last, partial wave of the
+  // launch with shorter blocks.  main_units == 0: every unit is split z ways.
+  long long main_units;
+  int z_main;
+  long long z_chunk_main;
 };
 
 // Threads per block.  128 measured best on the headline workload (64: +2 %,
@@ -191,7 +198,7 @@ __device__ __forceinline__ void store_run(E* dst, const E* src, bool vec) {
 // the output format of the call.
 template <typename T, typename Q, int J, int V, bool PACKED_OUT>
 __device__ __forceinline__ void sweep_write_out(const SweepParams& p, Q (&q)[V], const T* xrow, long long row,
-                                                long long c0, int z) {
+                                                long long c0, int z, int planes) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
   if constexpr (PACKED_OUT) {
@@ -237,7 +244,7 @@ __device__ __forceinline__ void sweep_write_out(const SweepParams& p, Q (&q)[V],
   // The thread's V*J entries are contiguous in every output array and start at a
   // multiple of their total size there, so the widest store that divides that size
   // is aligned whenever the buffers and their row strides are 16-byte aligned.
-  if (p.z == 1 && p.out_format != ATK_OUT_I64) {
+  if (planes == 1 && p.out_format != ATK_OUT_I64) {
     const long long out_base = row * p.out_row_stride + c0 * J;
     if (p.out_format == ATK_OUT_REC32) {
       // records {value bits zero-extended to 32 bits, int32 position}
@@ -255,11 +262,11 @@ __device__ __forceinline__ void sweep_write_out(const SweepParams& p, Q (&q)[V],
     }
     return;
   }
-  const long long out_base = p.z > 1 ? (static_cast<long long>(z) * p.rows + row) * k0 + c0 * J
+  const long long out_base = planes > 1 ? (static_cast<long long>(z) * p.rows + row) * k0 + c0 * J
                                      : row * p.out_row_stride + c0 * J;
-  Bits* vdst = static_cast<Bits*>(p.z > 1 ? p.part_vals : p.out_vals) + out_base;
-  long long* idst = (p.z > 1 ? p.part_idx : p.out_idx) + out_base;
-  const bool vec = p.z > 1 ? p.vec_part : p.vec_out;
+  Bits* vdst = static_cast<Bits*>(planes > 1 ? p.part_vals : p.out_vals) + out_base;
+  long long* idst = (planes > 1 ? p.part_idx : p.out_idx) + out_base;
+  const bool vec = planes > 1 ? p.vec_part : p.vec_out;
   store_run<V * J * static_cast<int>(sizeof(Bits))>(vdst, ov, vec);
   store_run<V * J * 8>(idst, oi, vec);
 }
@@ -301,7 +308,7 @@ sweep_kernel(const SweepParams p) {
   // the kernel measured slower: early blocks of the select pile up on the SMs that ran
   // out of stage-1 work first.)
   grid_launch_dependents();
-  sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
+  sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z, p.z);
 }
 
 // ---------------------------------------------------------------------------
@@ -350,8 +357,27 @@ tile_kernel(const SweepParams p) {
   extern __shared__ __align__(16) uint32_t tile_smem[];     // BUFS buffers of CH x kTileThreads words
   grid_dependency_wait();   // see sweep_kernel
   const int tx = threadIdx.x;
-  const long long unit = static_cast<long long>(blockIdx.x) / p.z;        // (row, tile)
-  const int z = static_cast<int>(static_cast<long long>(blockIdx.x) - unit * p.z);
+  // (row, tile) unit and stripe split of this block: the first p.main_units units whole,
+  // the units after them in p.z splits each
+  long long unit;
+  int z, planes;
+  long long chunk;
+  {
+    const long long blk = static_cast<long long>(blockIdx.x);
+    const long long main_blocks = p.main_units * p.z_main;
+    if (blk < main_blocks) {
+      unit = blk / p.z_main;
+      z = static_cast<int>(blk - unit * p.z_main);
+      planes = p.z_main;
+      chunk = p.z_chunk_main;
+    } else {
+      const long long t = blk - main_blocks;
+      unit = p.main_units + t / p.z;
+      z = static_cast<int>(t - (unit - p.main_units) * p.z);
+      planes = p.z;
+      chunk = p.z_chunk;
+    }
+  }
   const long long row = unit / p.tiles;
   const long long tile = unit - row * p.tiles;
   const long long tile_c0 = tile * Shape::kCols;
@@ -362,9 +388,9 @@ tile_kernel(const SweepParams p) {
   if (wcols > Shape::kCols) wcols = Shape::kCols;
   const int pieces_per_stripe = static_cast<int>(wcols / Shape::kPerPiece);
   // stripe range of this block (the whole column unless stripes are split over blocks)
-  const long long l_begin = static_cast<long long>(z) * p.z_chunk;
-  long long l_end = l_begin + p.z_chunk;
-  if (l_end > p.l_full || z == p.z - 1) l_end = p.l_full;
+  const long long l_begin = static_cast<long long>(z) * chunk;
+  long long l_end = l_begin + chunk;
+  if (l_end > p.l_full || z == planes - 1) l_end = p.l_full;
 
   Q q[V];
 #pragma unroll
@@ -433,14 +459,14 @@ tile_kernel(const SweepParams p) {
   }
   if (!active) return;
   // ragged last stripe (b does not divide n): only columns < rem exist; it belongs to the last split
-  if (p.rem > 0 && z == p.z - 1) {
+  if (p.rem > 0 && z == planes - 1) {
     const T* last = xrow + p.l_full * p.stripe_stride + c0;
 #pragma unroll
     for (int e = 0; e < V; ++e)
       if (c0 + e < p.rem) q[e].push_tail(load_elem_bits<T>(last + e), static_cast<int>(p.l_full));
   }
   grid_launch_dependents();   // see sweep_kernel
-  sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z);
+  sweep_write_out<T, Q, J, V, PACKED_OUT>(p, q, xrow, row, c0, z, planes);
 }
 
 // Combine the z partial candidate planes written by a stripe-split sweep: a
@@ -495,15 +521,19 @@ template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(256)
 sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_vals,
                           const long long* __restrict__ part_idx, int z, int g /* lanes per bucket */,
-                          long long rows, long long b, void* __restrict__ out_vals, void* __restrict__ out_idx,
+                          long long rows, long long b, long long bucket_first /* first bucket to merge */,
+                          long long tail_begin /* buckets from here on have z planes, those before z_main */,
+                          int z_main, void* __restrict__ out_vals, void* __restrict__ out_idx,
                           long long out_row_stride, int out_format) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
   const int lane = threadIdx.x % g;            // g is a power of two <= 32, groups never straddle warps
   const long long unit = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / g;
-  const bool valid = unit < rows * b;          // whole warps stay for the shuffles
-  const long long row = valid ? unit / b : 0;
-  const long long c = valid ? unit - row * b : 0;
+  const long long nb = b - bucket_first;       // buckets to merge per row
+  const bool valid = unit < rows * nb;         // whole warps stay for the shuffles
+  const long long row = valid ? unit / nb : 0;
+  const long long c = valid ? bucket_first + unit - row * nb : 0;
+  if (c < tail_begin) z = z_main;
   const long long k0 = b * J;
   PlaneEntryQueue<T, J, FIRST> q;
   q.init();
@@ -641,6 +671,44 @@ inline long long tile_split(long long rows, long long tiles, long long l_full, i
   return z < 1 ? 1 : z;
 }
 
+// Which units of the tile kernel are split.  One row whose tiles fill the GPU at least
+// once: the tiles of the complete waves are scanned whole (no partial candidates, no
+// merge, every queue warms up once), and only the tiles left over for the last, partial
+// wave are split -- as many ways as fit that wave, so that it is full and short.
+// Otherwise every unit is split tile_split() ways.
+struct TilePlan {
+  long long main_units;   // units split z_main ways, first in the grid
+  long long z_main;
+  long long z;            // splits of each of the other units
+};
+inline TilePlan tile_plan(long long rows, long long tiles, long long l_full, int sm_count) {
+  TilePlan tp{0, 1, tile_split(rows, tiles, l_full, sm_count)};
+  const long long cap = 6ll * sm_count;                      // resident blocks of the tile kernel
+  long long zmax = l_full / 256;
+  if (zmax > 64) zmax = 64;
+  if (rows != 1 || cap <= 0 || zmax < 2) return tp;
+  // one full wave (or several) of equal blocks first ...
+  long long z1 = tiles >= cap ? 1 : (cap + tiles - 1) / tiles;
+  if (z1 > zmax) return tp;                                  // few tiles: every unit split as far as it goes
+  const long long main_units = tiles >= cap ? (tiles / cap) * cap : cap / z1;
+  const long long rest = tiles - main_units;
+  if (rest <= 0) {
+    tp.z = z1;
+    return tp;
+  }
+  // ... then the units left over, split as many ways as fill one more wave
+  long long z2 = cap / rest;
+  if (z2 > zmax) z2 = zmax;
+  if (z2 <= z1) {                                            // nothing to gain from shorter blocks at the end
+    tp.z = z1;
+    return tp;
+  }
+  tp.main_units = main_units;
+  tp.z_main = z1;
+  tp.z = z2;
+  return tp;
+}
+
 // Arguments of the typed launchers (one translation unit per element type).
 struct SweepLaunch {
   const void* x;
@@ -676,7 +744,8 @@ inline size_t sweep_workspace_bytes(int elem_size, long long rows, long long n, 
   if (elem_size == 2 || elem_size == 4) {
     // the shared-memory tile kernel (16-bit floats, float32) splits long columns too
     const long long tile_cols = elem_size == 2 ? 256 : 128;
-    const long long zt = tile_split(rows, (b + tile_cols - 1) / tile_cols, n / b, sm_count);
+    const TilePlan tp = tile_plan(rows, (b + tile_cols - 1) / tile_cols, n / b, sm_count);
+    const long long zt = tp.z > tp.z_main ? tp.z : tp.z_main;
     if (zt > planes) planes = zt;
   }
   if (planes <= 1) return 0;

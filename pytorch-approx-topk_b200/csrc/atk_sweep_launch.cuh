@@ -92,6 +92,9 @@ int launch_stage1(const SweepLaunch& a) {
   p.s = static_cast<int>(pl.S);
   p.z = static_cast<int>(pl.Z);
   p.z_chunk = pl.z_chunk;
+  p.main_units = 0;
+  p.z_main = 1;
+  p.z_chunk_main = pl.z_chunk;
   p.part_vals = nullptr;
   p.part_idx = nullptr;
   p.vec_part = 0;
@@ -125,7 +128,7 @@ int launch_stage1(const SweepLaunch& a) {
     const long long blocks = (a.rows * a.b * g + 255) / 256;
     if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     sweep_merge_planes_kernel<T, J, Q::kFirst><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
-        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, a.out_vals, a.out_idx,
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, 0ll, 0ll, 1, a.out_vals, a.out_idx,
         a.out_row_stride, a.out_format);
     note_launch();
     if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
@@ -189,21 +192,33 @@ int launch_tile_shared_j(const SweepLaunch& a) {
   p.cw = kTileThreads;
   p.s = 1;
   // stripe split over blocks: as many planes as wanted and as the caller's scratch holds
-  long long Z = a.out_keys != nullptr ? 1 : tile_split(a.rows, p.tiles, p.l_full, a.sm_count);
+  TilePlan tp{0, 1, 1};
+  if (a.out_keys == nullptr) tp = tile_plan(a.rows, p.tiles, p.l_full, a.sm_count);
+  long long Z = tp.z, Zm = tp.z_main;
   if (Z > 1) {
     const size_t per_z = static_cast<size_t>(a.rows) * k0 * (sizeof(Bits) + 8);
     long long fit = 0;
     if (a.workspace != nullptr && a.workspace_bytes > 256) fit = static_cast<long long>((a.workspace_bytes - 256) / per_z);
     if (fit < Z) Z = fit >= 2 ? fit : 1;
+    if (fit < Zm) Zm = fit >= 2 ? fit : 1;
   }
-  SweepPlan pl;
+  SweepPlan pl, plm;
   pl.S = 1;
   pl.Z = Z;
   set_chunks(pl, p.l_full);
+  plm.S = 1;
+  plm.Z = Zm;
+  set_chunks(plm, p.l_full);
+  const long long units = a.rows * p.tiles;
+  const long long main_units = pl.Z > plm.Z ? tp.main_units : 0;
+  const long long n_blocks = main_units * plm.Z + (units - main_units) * pl.Z;
   // half a wave of blocks at least; below that the sweep with its in-block splits takes over
-  if (a.rows * p.tiles * pl.Z < 3ll * a.sm_count) return a.out_keys != nullptr ? kPackedUnavailable : kTileDeclined;
+  if (n_blocks < 3ll * a.sm_count) return a.out_keys != nullptr ? kPackedUnavailable : kTileDeclined;
   p.z = static_cast<int>(pl.Z);
   p.z_chunk = pl.z_chunk;
+  p.main_units = main_units;
+  p.z_main = static_cast<int>(plm.Z);
+  p.z_chunk_main = plm.z_chunk;
   p.part_vals = nullptr;
   p.part_idx = nullptr;
   p.vec_part = 0;
@@ -213,10 +228,12 @@ int launch_tile_shared_j(const SweepLaunch& a) {
     p.part_idx = reinterpret_cast<long long*>(ws + align256(static_cast<size_t>(pl.Z) * a.rows * k0 * sizeof(Bits)));
     p.vec_part = (reinterpret_cast<uintptr_t>(ws) % 16 == 0) && ((k0 * sizeof(Bits)) % 16 == 0) && ((k0 * 8) % 16 == 0);
   }
-  if (a.rows * p.tiles * pl.Z >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
-  const dim3 grid(static_cast<unsigned>(a.rows * p.tiles * pl.Z));
+  if (n_blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
+  const dim3 grid(static_cast<unsigned>(n_blocks));
   const bool packed = a.out_keys != nullptr;
-  const long long per_block = pl.z_chunk < p.l_full ? pl.z_chunk : p.l_full;
+  // stripes a block walks (the whole column for the units that are not split)
+  const long long longest = main_units > 0 ? plm.z_chunk : pl.z_chunk;
+  const long long per_block = longest < p.l_full ? longest : p.l_full;
 #define ATK_LAUNCH_TILE(CH, BUFS)                                                                    \
   do {                                                                                               \
     const size_t smem = static_cast<size_t>(BUFS) * (CH) * kTileThreads * 4;                         \
@@ -249,11 +266,14 @@ int launch_tile_shared_j(const SweepLaunch& a) {
   if (pl.Z > 1) {
     int g = 1;                                   // lanes per bucket: about 8 planes per lane
     while (g < 32 && g * 8 < pl.Z) g *= 2;
-    const long long blocks = (a.rows * a.b * g + 255) / 256;
+    // only the buckets of the units that were split (one row when main_units > 0)
+    const long long tail_begin = main_units * Shape::kCols;
+    const long long bucket_first = p.z_main > 1 ? 0 : tail_begin;
+    const long long blocks = (a.rows * (a.b - bucket_first) * g + 255) / 256;
     if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     sweep_merge_planes_kernel<T, J, false><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
-        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, a.out_vals, a.out_idx,
-        a.out_row_stride, a.out_format);
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, bucket_first, tail_begin, p.z_main,
+        a.out_vals, a.out_idx, a.out_row_stride, a.out_format);
     note_launch();
     if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   }
