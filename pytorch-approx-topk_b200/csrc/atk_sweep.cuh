@@ -521,19 +521,19 @@ template <typename T, int J, bool FIRST>
 __global__ void __launch_bounds__(256)
 sweep_merge_planes_kernel(const typename ElemTraits<T>::Bits* __restrict__ part_vals,
                           const long long* __restrict__ part_idx, int z, int g /* lanes per bucket */,
-                          long long rows, long long b, long long bucket_first /* first bucket to merge */,
-                          long long tail_begin /* buckets from here on have z planes, those before z_main */,
+                          long long rows, long long b, long long tiles, int tile_cols,
+                          long long main_units /* (row, tile) units before this one have z_main planes */,
                           int z_main, void* __restrict__ out_vals, void* __restrict__ out_idx,
                           long long out_row_stride, int out_format) {
   using Tr = ElemTraits<T>;
   using Bits = typename Tr::Bits;
   const int lane = threadIdx.x % g;            // g is a power of two <= 32, groups never straddle warps
   const long long unit = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / g;
-  const long long nb = b - bucket_first;       // buckets to merge per row
-  const bool valid = unit < rows * nb;         // whole warps stay for the shuffles
-  const long long row = valid ? unit / nb : 0;
-  const long long c = valid ? bucket_first + unit - row * nb : 0;
-  if (c < tail_begin) z = z_main;
+  bool valid = unit < rows * b;                // whole warps stay for the shuffles
+  const long long row = valid ? unit / b : 0;
+  const long long c = valid ? unit - row * b : 0;
+  if (row * tiles + c / tile_cols < main_units) z = z_main;
+  valid = valid && z > 1;                      // a unit that was not split wrote its buckets itself
   const long long k0 = b * J;
   PlaneEntryQueue<T, J, FIRST> q;
   q.init();
@@ -671,11 +671,12 @@ inline long long tile_split(long long rows, long long tiles, long long l_full, i
   return z < 1 ? 1 : z;
 }
 
-// Which units of the tile kernel are split.  One row whose tiles fill the GPU at least
-// once: the tiles of the complete waves are scanned whole (no partial candidates, no
-// merge, every queue warms up once), and only the tiles left over for the last, partial
-// wave are split -- as many ways as fit that wave, so that it is full and short.
-// Otherwise every unit is split tile_split() ways.
+// Which (row, tile) units of the tile kernel are split, for columns long enough to split.
+// Enough units to fill the GPU at least once: the units of the complete waves are scanned
+// whole (no partial candidates, no merge, every queue warms up once), and only the units
+// left over for the last, partial wave are split -- as many ways as fit that wave, so that
+// it is full and short.  Fewer units: the first wave is units split ceil(capacity / units)
+// ways, the rest is split further.  Otherwise every unit is split tile_split() ways.
 struct TilePlan {
   long long main_units;   // units split z_main ways, first in the grid
   long long z_main;
@@ -684,14 +685,17 @@ struct TilePlan {
 inline TilePlan tile_plan(long long rows, long long tiles, long long l_full, int sm_count) {
   TilePlan tp{0, 1, tile_split(rows, tiles, l_full, sm_count)};
   const long long cap = 6ll * sm_count;                      // resident blocks of the tile kernel
+  const long long units = rows * tiles;                      // (row, tile) units, row-major
   long long zmax = l_full / 256;
   if (zmax > 64) zmax = 64;
-  if (rows != 1 || cap <= 0 || zmax < 2) return tp;
+  // columns of 1024 stripes and more: below that the blocks are short anyway and the merge
+  // launch costs more than the last wave gains (fp16 256 x 2^20, 512 stripes: 98 -> 105 us)
+  if (units <= 0 || cap <= 0 || zmax < 4) return tp;
   // one full wave (or several) of equal blocks first ...
-  long long z1 = tiles >= cap ? 1 : (cap + tiles - 1) / tiles;
-  if (z1 > zmax) return tp;                                  // few tiles: every unit split as far as it goes
-  const long long main_units = tiles >= cap ? (tiles / cap) * cap : cap / z1;
-  const long long rest = tiles - main_units;
+  long long z1 = units >= cap ? 1 : (cap + units - 1) / units;
+  if (z1 > zmax) return tp;                                  // few units: every one split as far as it goes
+  const long long main_units = units >= cap ? (units / cap) * cap : cap / z1;
+  const long long rest = units - main_units;
   if (rest <= 0) {
     tp.z = z1;
     return tp;

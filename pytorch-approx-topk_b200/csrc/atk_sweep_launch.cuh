@@ -128,8 +128,8 @@ int launch_stage1(const SweepLaunch& a) {
     const long long blocks = (a.rows * a.b * g + 255) / 256;
     if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     sweep_merge_planes_kernel<T, J, Q::kFirst><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
-        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, 0ll, 0ll, 1, a.out_vals, a.out_idx,
-        a.out_row_stride, a.out_format);
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, 1ll, 1, 0ll, 1, a.out_vals,
+        a.out_idx, a.out_row_stride, a.out_format);
     note_launch();
     if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   }
@@ -266,14 +266,11 @@ int launch_tile_shared_j(const SweepLaunch& a) {
   if (pl.Z > 1) {
     int g = 1;                                   // lanes per bucket: about 8 planes per lane
     while (g < 32 && g * 8 < pl.Z) g *= 2;
-    // only the buckets of the units that were split (one row when main_units > 0)
-    const long long tail_begin = main_units * Shape::kCols;
-    const long long bucket_first = p.z_main > 1 ? 0 : tail_begin;
-    const long long blocks = (a.rows * (a.b - bucket_first) * g + 255) / 256;
+    const long long blocks = (a.rows * a.b * g + 255) / 256;
     if (blocks >= (1ll << 31)) return ATK_ERR_TOO_LARGE;
     sweep_merge_planes_kernel<T, J, false><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
-        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, bucket_first, tail_begin, p.z_main,
-        a.out_vals, a.out_idx, a.out_row_stride, a.out_format);
+        static_cast<const Bits*>(p.part_vals), p.part_idx, p.z, g, a.rows, a.b, p.tiles, Shape::kCols, main_units,
+        p.z_main, a.out_vals, a.out_idx, a.out_row_stride, a.out_format);
     note_launch();
     if (cudaGetLastError() != cudaSuccess) return ATK_ERR_CUDA;
   }
