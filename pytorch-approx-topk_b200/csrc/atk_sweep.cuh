@@ -703,8 +703,13 @@ inline TilePlan tile_plan(long long rows, long long tiles, long long l_full, int
   // ... then the units left over, split as many ways as fill one more wave
   long long z2 = cap / rest;
   if (z2 > zmax) z2 = zmax;
-  if (z2 <= z1) {                                            // nothing to gain from shorter blocks at the end
-    tp.z = z1;
+  if (z2 <= z1) {
+    // The left-over units cannot be split further than the others (short columns): every
+    // unit the same number of ways, whichever of "just under one wave" and "just over" needs
+    // less time (waves x stripes per block).
+    const long long zf = cap / units;                        // 0 when there are more units than blocks
+    if (zf >= 1 && zf < z1 && z1 < zf * ((units * z1 + cap - 1) / cap)) tp.z = zf;   // 1 / zf < waves / z1
+    else tp.z = z1;
     return tp;
   }
   tp.main_units = main_units;
