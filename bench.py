@@ -556,7 +556,16 @@ def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, rep
     # that layout (the values are i.i.d., so the slab of a random row is a random slab).
     slab = make_input(dict(w, n=stripes * (c1 - c0)), 1, 77 + rank, dev).view(stripes, c1 - c0)
     exchange = exchange if world > 1 else "none"
-    plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev, exchange=exchange if world > 1 else "all_gather")
+    exchange_note = None
+    try:
+        plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev, exchange=exchange if world > 1 else "all_gather")
+    except RuntimeError as exc:
+        # the buffers could not be shared between the ranks (the error is the same on every
+        # rank): the collective exchange instead
+        if exchange != "push":
+            raise
+        exchange, exchange_note = "all_gather", f"push exchange unavailable: {exc}"[:300]
+        plan = atd.LongRowTopK(stripes, k, j, k_mult, dtype, dev, exchange="all_gather")
     if exchange == "push":
         steps += steps & 1        # the two candidate buffer sets alternate: a replayed graph holds an even number of steps
 
@@ -603,6 +612,7 @@ def long_row_record(rank: int, world: int, dev, stream, barrier, steps: int, rep
                                  "over NVLink (CUDA IPC mappings), then a one-element NCCL all-reduce orders the streams",
                          "all_gather": "one NCCL all-gather of the packed candidate blocks, two unpack copies",
                          "none": "single GPU: no exchange"}[exchange],
+            "exchange_note": exchange_note,
             "steps": steps, "replays": replays, "graph": used_graph,
             "timed_call": "approx_topk.distributed.LongRowTopK step (atk_stage1_slab, exchange, atk_select)"}
 

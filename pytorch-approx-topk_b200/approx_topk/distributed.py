@@ -159,26 +159,52 @@ class PeerBuffers:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         lib = _native.lib()
         own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
-        with torch.cuda.device(self.device):
-            _native.check(lib.atk_peer_alloc(nbytes, ctypes.byref(own), handle))
-        self._own = own.value
-        self.local = torch.as_tensor(_RawCudaBytes(self._own, nbytes), device=self.device)
-        handles: list = [None] * self.world
-        dist.all_gather_object(handles, (self.device.index, bytes(handle.raw)), group=group)
+        self._own, self.local = None, None
         self.ptrs: list[int] = []
         self._opened: list[int] = []
+        # A failure on any rank (no memory, a peer's GPU hidden from a process, no peer access)
+        # becomes the same RuntimeError on EVERY rank, after everything has been released: the
+        # ranks agree on the outcome of each step before the next.
+        problem = None
         with torch.cuda.device(self.device):
-            for r, (peer_device, raw) in enumerate(handles):
+            status = lib.atk_peer_alloc(nbytes, ctypes.byref(own), handle)
+        if status != _native.ATK_OK:
+            problem = f"cannot allocate {nbytes} bytes: {_native.strerror(status)}"
+        else:
+            self._own = own.value
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, (problem, self.device.index, bytes(handle.raw)), group=group)
+        self._raise_together([h[0] for h in handles])
+        with torch.cuda.device(self.device):
+            for r, (_, peer_device, raw) in enumerate(handles):
                 if r == self.rank:
                     self.ptrs.append(self._own)
                     continue
-                if not torch.cuda.can_device_access_peer(self.device.index, peer_device):
-                    raise RuntimeError(f"GPU {self.device.index} has no peer access to GPU {peer_device} (rank {r})")
                 mapped = ctypes.c_void_p()
-                _native.check(lib.atk_peer_open(ctypes.create_string_buffer(raw, 64), ctypes.byref(mapped)))
+                if peer_device == self.device.index:
+                    problem = f"rank {r} uses the same device index {peer_device}: the GPUs of all ranks must be visible to every rank"
+                elif not torch.cuda.can_device_access_peer(self.device.index, peer_device):
+                    problem = f"GPU {self.device.index} has no peer access to GPU {peer_device} (rank {r})"
+                else:
+                    status = lib.atk_peer_open(ctypes.create_string_buffer(raw, 64), ctypes.byref(mapped))
+                    if status != _native.ATK_OK:
+                        problem = f"cannot map the buffer of rank {r}: {_native.strerror(status)}"
+                if problem is not None:
+                    break
                 self.ptrs.append(mapped.value)
                 self._opened.append(mapped.value)
-        dist.barrier(group)
+        outcomes: list = [None] * self.world
+        dist.all_gather_object(outcomes, problem, group=group)
+        self._raise_together(outcomes)
+        self.local = torch.as_tensor(_RawCudaBytes(self._own, nbytes), device=self.device)
+
+    def _raise_together(self, problems: list) -> None:
+        """Every rank holds the same list: release and raise on all of them if any rank failed."""
+        failed = [(r, p) for r, p in enumerate(problems) if p is not None]
+        if not failed:
+            return
+        self._release()                       # every rank: it holds a barrier
+        raise RuntimeError("PeerBuffers: " + "; ".join(f"rank {r}: {p}" for r, p in failed))
 
     def close(self) -> None:
         """Collective: every rank unmaps its peers' buffers, then the owners free them."""
@@ -199,8 +225,9 @@ class PeerBuffers:
                     dist.barrier(self.group)          # no owner frees while a peer still maps its buffer
                 except Exception:                     # the group is already gone: nothing left to order
                     pass
-            lib.atk_peer_free(self._own)
-        self._own, self.local = None, None
+            if self._own is not None:
+                lib.atk_peer_free(self._own)
+        self._own, self.local, self.ptrs = None, None, []
 
 
 class LongRowTopK:

@@ -303,3 +303,19 @@ def test_push_exchange_argument_checks_need_no_gpu():
     assert lib.atk_peer_close(None) == _native.ATK_OK and lib.atk_peer_free(None) == _native.ATK_OK
     with pytest.raises(ValueError, match="exchange"):
         LongRowTopK(16, 8, 1, 1, torch.float32, torch.device("cpu"), exchange="carrier pigeon")
+
+
+def test_peer_buffer_failures_are_raised_on_every_rank_alike():
+    """PeerBuffers gathers every rank's outcome before it goes on: whichever rank failed, all
+    ranks release what they hold (the release holds a barrier, so all must enter it) and raise
+    the same error."""
+    from approx_topk.distributed import PeerBuffers
+
+    released = []
+    pb = object.__new__(PeerBuffers)
+    pb._release = lambda: released.append(True)
+    pb._raise_together([None, None, None])              # nobody failed: nothing happens
+    assert released == []
+    with pytest.raises(RuntimeError, match=r"rank 1: no peer access.*rank 2: cannot map"):
+        pb._raise_together([None, "no peer access", "cannot map"])
+    assert released == [True]
